@@ -1,0 +1,112 @@
+"""ctypes binding of libgptq_b200.so (declared in include/gptq_b200.h).
+
+There is no fallback: if the library is missing or a kernel cannot run, an exception is
+raised.  The library is built in-tree by `python -m gptq_triton_b200.build`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from pathlib import Path
+from typing import Dict, Optional, Tuple
+
+import torch
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / 'libgptq_b200.so'
+
+_lib: Optional[ctypes.CDLL] = None
+
+_P = c_void_p
+_SIGNATURES = {
+	'gptq_version': (c_int, []),
+	'gptq_error_string': (c_char_p, [c_int]),
+	'gptq_last_cuda_error': (c_int, []),
+	'gptq_workspace_bytes': (c_size_t, [c_int, c_int, c_int]),
+	'gptq_qmatmul': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P, c_size_t, _P]),
+	'gptq_gateup_silu': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P, c_size_t, _P]),
+	'gptq_qkv_rope': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64,
+							  c_int, c_int, c_int, c_int, c_int, c_int64, _P, c_size_t, _P]),
+	'gptq_unpack_qweight': (c_int, [_P, _P, c_int, c_int, _P]),
+	'gptq_unpack_qzeros': (c_int, [_P, _P, c_int, c_int, _P]),
+	'gptq_dequantize': (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),
+	'gptq_act_order_rows': (c_int, [_P, _P, _P, c_int, c_int, _P]),
+}
+# Entry points outside the header's stable surface (tuning hooks); bound when present.
+_OPTIONAL = {
+	'gptq_debug_force_splitk': (None, [c_int]),
+}
+
+
+def exported_symbols():
+	"""Names that include/gptq_b200.h declares."""
+	return list(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+	global _lib
+	if _lib is None:
+		if not LIB_PATH.exists():
+			raise ImportError(
+				f'{LIB_PATH} is missing: build it with `python -m gptq_triton_b200.build` '
+				'(needs nvcc with sm_100a support). There is no CPU or Triton fallback.')
+		l = ctypes.CDLL(str(LIB_PATH))
+		for name, (res, args) in _SIGNATURES.items():
+			fn = getattr(l, name)
+			fn.restype = res
+			fn.argtypes = args
+		for name, (res, args) in _OPTIONAL.items():
+			if hasattr(l, name):
+				fn = getattr(l, name)
+				fn.restype = res
+				fn.argtypes = args
+		_lib = l
+	return _lib
+
+
+class GptqB200Error(RuntimeError):
+	pass
+
+
+def check(code: int, what: str):
+	if code != 0:
+		l = lib()
+		msg = l.gptq_error_string(code).decode()
+		extra = f' (cudaError {l.gptq_last_cuda_error()})' if code == -5 else ''
+		err = ValueError if code in (-1, -2, -4) else GptqB200Error
+		raise err(f'{what}: {msg}{extra}')
+
+
+def ptr(t: Optional[torch.Tensor]):
+	return None if t is None else c_void_p(t.data_ptr())
+
+
+def stream_ptr(device) -> c_void_p:
+	return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def require_cuda(*tensors):
+	for t in tensors:
+		if t is not None and not t.is_cuda:
+			raise GptqB200Error('gptq_triton_b200 runs on CUDA tensors only; there is no CPU path')
+
+
+# One zero-initialised scratch buffer per (device, stream): split-K partial sums and the
+# arrival counters that the kernels leave zeroed after each launch.
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(device: torch.device, M: int, K: int, N: int) -> torch.Tensor:
+	need = lib().gptq_workspace_bytes(M, K, N)
+	key = (device.index if device.index is not None else torch.cuda.current_device(),
+		   torch.cuda.current_stream(device).cuda_stream)
+	ws = _workspaces.get(key)
+	if ws is None or ws.numel() < need:
+		if ws is not None:
+			_retired.append(ws)     # a captured CUDA graph may still point at it
+		ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+		_workspaces[key] = ws
+	return ws
+
+
+_retired = []

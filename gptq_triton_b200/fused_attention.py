@@ -1,0 +1,182 @@
+"""Fused QKV projection + rotary embedding, and the quantised LLaMA attention block.
+
+Mirrors src/gptq_triton/fused_attention.py of the reference: `make_quant_attn` (:10-45)
+concatenates the q/k/v packed tensors along N into one QuantLinear, `QuantLlamaAttention`
+(:48-153) runs one QKV matmul, rotary embedding, the KV-cache append, softmax attention
+and o_proj.  Here the rotary embedding is applied inside the QKV kernel's epilogue, which
+also scatters Q/K/V to [b, h, t, d] (or K/V straight into a static cache).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from .quant_linear import QuantLinear
+
+
+def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, device=None, dtype=torch.float16):
+	"""cos/sin [max_pos, head_dim], rotate-half convention, computed in fp32 and cast to the
+	activation dtype as the HF rotary module does."""
+	inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+	t = torch.arange(max_pos, dtype=torch.float32, device=device)
+	freqs = torch.outer(t, inv_freq)
+	emb = torch.cat([freqs, freqs], dim=-1)
+	return emb.cos().to(dtype).contiguous(), emb.sin().to(dtype).contiguous()
+
+
+def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin, position_ids, n_heads: int, head_dim: int,
+			 perm: Optional[torch.Tensor] = None, kv_cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+	"""One kernel: a x deq(Wqkv), rotary on Q and K, scatter to heads.
+
+	a: [b, t, K] fp16 contiguous; position_ids: [b, t] integer.
+	Without kv_cache returns (q, k, v) each [b, n_heads, t, head_dim] (k, v freshly allocated).
+	With kv_cache = (K, V) each [b, n_heads, max_seq, head_dim] contiguous, K/V rows are written
+	in place at their positions and (q, K, V) is returned.
+	"""
+	assert a.dim() == 3 and a.is_contiguous(), "A must be [b, t, K] and contiguous"
+	assert a.shape[-1] == qweight.shape[0] * 8
+	_lib.require_cuda(a, qweight, scales, qzeros, cos, sin, position_ids, perm)
+	b, t, K = a.shape
+	M = b * t
+	hidden = n_heads * head_dim
+	assert qweight.shape[1] == 3 * hidden
+	pos = position_ids.reshape(-1).to(torch.int32).contiguous()
+	assert pos.numel() == M
+	# Q is written as [b, t, h, d]; the [b, h, t, d] view is returned
+	q = torch.empty((b, t, n_heads, head_dim), device=a.device, dtype=torch.float16)
+	if kv_cache is None:
+		k = torch.empty((b, n_heads, t, head_dim), device=a.device, dtype=torch.float16)
+		v = torch.empty_like(k)
+		sb, st, sh, sp = n_heads * t * head_dim, head_dim, t * head_dim, 0
+	else:
+		k, v = kv_cache
+		assert k.is_contiguous() and v.is_contiguous() and k.shape == v.shape and k.shape[0] >= b and k.shape[1] == n_heads and k.shape[3] == head_dim
+		S = k.shape[2]
+		sb, st, sh, sp = n_heads * S * head_dim, 0, S * head_dim, head_dim
+	ws = _lib.workspace(a.device, M, K, 3 * hidden)
+	rc = _lib.lib().gptq_qkv_rope(
+		_lib.ptr(a), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), None, _lib.ptr(perm),
+		_lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), _lib.ptr(q), hidden, _lib.ptr(k), _lib.ptr(v), t, sb, st, sh, sp,
+		M, K, n_heads, head_dim, groupsize, K, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device))
+	_lib.check(rc, 'gptq_qkv_rope')
+	return q.transpose(1, 2), k, v
+
+
+def _is_llama_attention(m) -> bool:
+	return (not isinstance(m, QuantLlamaAttention)
+			and all(isinstance(getattr(m, n, None), QuantLinear) for n in ('q_proj', 'k_proj', 'v_proj', 'o_proj')))
+
+
+def make_quant_attn(model):
+	"""Replace every LLaMA attention module (one that owns quantised q/k/v/o projections) by
+	QuantLlamaAttention with the three projections fused (reference: fused_attention.py:10-45)."""
+	for name, m in list(model.named_modules()):
+		if not _is_llama_attention(m):
+			continue
+		q_proj, k_proj, v_proj = m.q_proj, m.k_proj, m.v_proj
+		qweights = torch.cat([q_proj.qweight, k_proj.qweight, v_proj.qweight], dim=1)
+		qzeros = torch.cat([q_proj.qzeros, k_proj.qzeros, v_proj.qzeros], dim=1)
+		scales = torch.cat([q_proj.scales, k_proj.scales, v_proj.scales], dim=1)
+		qkv_layer = QuantLinear(q_proj.bits, q_proj.groupsize, q_proj.infeatures,
+								q_proj.outfeatures + k_proj.outfeatures + v_proj.outfeatures, bias=False)
+		qkv_layer.qweight = qweights
+		qkv_layer.qzeros = qzeros
+		qkv_layer.scales = scales
+		qkv_layer.bias = None
+		gs = [p.g_idx for p in (q_proj, k_proj, v_proj)]
+		if any(g is not None for g in gs):
+			if any(g is None for g in gs) or not (torch.equal(gs[0], gs[1]) and torch.equal(gs[0], gs[2])):
+				raise ValueError('q_proj, k_proj and v_proj must share one g_idx to be fused')
+			qkv_layer.set_g_idx(gs[0])
+		attn = QuantLlamaAttention(m.config, qkv_layer, m.o_proj, getattr(m, 'rotary_emb', None))
+		if '.' in name:
+			parent_name, child_name = name.rsplit('.', 1)
+			parent = model.get_submodule(parent_name)
+		else:
+			parent, child_name = model, name
+		setattr(parent, child_name, attn)
+
+
+class QuantLlamaAttention(nn.Module):
+	"""LLaMA attention with fused QKV + rotary (reference: fused_attention.py:48-153).
+	`rotary_emb` is accepted for signature compatibility; the cos/sin tables are built from
+	the config (rope theta, max positions) in the module's dtype."""
+
+	def __init__(self, config, qkv_proj, o_proj, rotary_emb=None):
+		super().__init__()
+		self.config = config
+		self.hidden_size = config.hidden_size
+		self.num_heads = config.num_attention_heads
+		self.head_dim = self.hidden_size // self.num_heads
+		self.max_position_embeddings = config.max_position_embeddings
+		if (self.head_dim * self.num_heads) != self.hidden_size:
+			raise ValueError(
+				f"hidden_size must be divisible by num_heads (got `hidden_size`: {self.hidden_size}"
+				f" and `num_heads`: {self.num_heads}).")
+		self.qkv_proj = qkv_proj
+		self.o_proj = o_proj
+		self.rotary_emb = rotary_emb
+		self.rope_theta = float(getattr(config, 'rope_theta', 10000.0) or 10000.0)
+		self._tables = None
+
+	def _apply(self, fn, recurse=True):
+		self._tables = None
+		return super()._apply(fn, recurse)
+
+	def tables(self, device, need: int):
+		if self._tables is None or self._tables[0].device != device or self._tables[0].shape[0] < need:
+			n = max(need, self.max_position_embeddings)
+			self._tables = rope_tables(self.head_dim, n, self.rope_theta, device=device)
+		return self._tables
+
+	def project_qkv(self, hidden_states, position_ids, kv_cache=None):
+		qw, g_idx, perm = self.qkv_proj.kernel_operands()
+		if g_idx is not None:
+			raise NotImplementedError('fused QKV needs act-order groups of equal size')
+		bsz, q_len, _ = hidden_states.shape
+		if position_ids is None:
+			position_ids = torch.arange(q_len, device=hidden_states.device).unsqueeze(0).expand(bsz, q_len)
+		cos, sin = self.tables(hidden_states.device, 0)
+		return qkv_rope(self.qkv_proj.groupsize, hidden_states, qw, self.qkv_proj.scales, self.qkv_proj.qzeros, cos, sin,
+						position_ids, self.num_heads, self.head_dim, perm=perm, kv_cache=kv_cache)
+
+	def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+				position_ids: Optional[torch.LongTensor] = None, past_key_value: Optional[Tuple[torch.Tensor]] = None,
+				output_attentions: bool = False, use_cache: bool = False
+				) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[Tuple[torch.Tensor]]]:
+		"""Input shape: Batch x Time x Channel.  Same contract as the reference forward
+		(fused_attention.py:79-153): returns (attn_output, attn_weights or None, (K, V) or None)."""
+		bsz, q_len, _ = hidden_states.size()
+		hidden_states = hidden_states.contiguous()
+		if position_ids is None:
+			past = 0 if past_key_value is None else past_key_value[0].shape[-2]
+			position_ids = torch.arange(past, past + q_len, device=hidden_states.device).unsqueeze(0).expand(bsz, q_len)
+		query_states, key_states, value_states = self.project_qkv(hidden_states, position_ids)
+		if past_key_value is not None:
+			key_states = torch.cat([past_key_value[0], key_states], dim=2)
+			value_states = torch.cat([past_key_value[1], value_states], dim=2)
+		kv_seq_len = key_states.shape[-2]
+		past_key_value = (key_states, value_states) if use_cache else None
+
+		attn_weights = None
+		if output_attentions:
+			attn_weights = torch.matmul(query_states, key_states.transpose(2, 3)) / math.sqrt(self.head_dim)
+			if attention_mask is not None:
+				if attention_mask.size() != (bsz, 1, q_len, kv_seq_len):
+					raise ValueError(f"Attention mask should be of size {(bsz, 1, q_len, kv_seq_len)}, but is {attention_mask.size()}")
+				attn_weights = attn_weights + attention_mask
+				attn_weights = torch.max(attn_weights, torch.tensor(torch.finfo(attn_weights.dtype).min, device=attn_weights.device))
+			attn_weights = nn.functional.softmax(attn_weights, dim=-1, dtype=torch.float32).to(query_states.dtype)
+			attn_output = torch.matmul(attn_weights, value_states)
+		else:
+			if attention_mask is not None and attention_mask.size() != (bsz, 1, q_len, kv_seq_len):
+				raise ValueError(f"Attention mask should be of size {(bsz, 1, q_len, kv_seq_len)}, but is {attention_mask.size()}")
+			attn_output = nn.functional.scaled_dot_product_attention(query_states, key_states, value_states, attn_mask=attention_mask)
+
+		attn_output = attn_output.transpose(1, 2).reshape(bsz, q_len, self.hidden_size)
+		attn_output = self.o_proj(attn_output)
+		return attn_output, attn_weights, past_key_value

@@ -1,0 +1,139 @@
+/*
+ * gptq_b200.h — C ABI of libgptq_b200.so: 4-bit GPTQ quantised-linear hot path for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Every pointer is a DEVICE pointer unless a comment says otherwise.  All entry
+ * points that take a stream are asynchronous on that stream, never synchronise
+ * the host, never allocate and never free.  They return 0 on success and a
+ * negative GPTQ_ERR_* code otherwise; they never abort.  The caller owns every
+ * buffer; weights are only read.
+ *
+ * Tensor layouts (those of the reference checkpoint, src/gptq_triton/quant_linear.py:67-71):
+ *   qweight  int32 [K/8, N]   word r, nibble i (bit 4i, lowest first) = row 8r+i
+ *   qzeros   int32 [G, N/8]   word c, nibble i = column 8c+i, stored value = zero-1
+ *   scales   fp16  [G, N]
+ *   g_idx    int32 [K]        group of row k; NULL means k / groupsize
+ *   x        fp16  [M, K]     row stride ldx (elements)
+ *   y        fp16  [M, N]     row stride ldy (elements)
+ * decode:  w[k,n] = (q[k,n] - (qzeros[g,n] + 1)) * scales[g,n]        (README.md:93)
+ * groupsize == -1 is accepted and means groupsize = K (quant_linear.py:56).
+ */
+#ifndef GPTQ_B200_H
+#define GPTQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GPTQ_OK                 0
+#define GPTQ_ERR_INVALID       -1   /* null pointer, non-positive size, bad flag            */
+#define GPTQ_ERR_SHAPE         -2   /* shape violates a documented divisibility rule        */
+#define GPTQ_ERR_WORKSPACE     -3   /* workspace missing or smaller than gptq_workspace_bytes */
+#define GPTQ_ERR_ALIGN         -4   /* pointer or leading dimension not 16-byte aligned     */
+#define GPTQ_ERR_CUDA          -5   /* the CUDA runtime reported an error at launch         */
+#define GPTQ_ERR_UNSUPPORTED   -6   /* combination not implemented (e.g. head_dim != 128)   */
+
+typedef void *gptq_stream_t;       /* a cudaStream_t */
+
+/* Library/ABI version (major*100 + minor). */
+int gptq_version(void);
+
+/* Static, human-readable text for a GPTQ_ERR_* code.  Host pointer, never NULL. */
+const char *gptq_error_string(int code);
+
+/* After a GPTQ_ERR_CUDA return: the cudaError_t value seen by the calling thread. */
+int gptq_last_cuda_error(void);
+
+/*
+ * Bytes of scratch that gptq_qmatmul / gptq_gateup_silu / gptq_qkv_rope need for a
+ * problem of this size (split-K partial sums + per-tile arrival counters).  The
+ * caller allocates it once per stream, ZEROES it once, and hands it to every call;
+ * the kernels leave the counter area zeroed again.  Two calls that overlap on the
+ * GPU must not share one workspace.  Replaces the `torch.empty` + 1-D launch grid
+ * set-up of the reference wrapper (quant_linear.py:259-263).
+ */
+size_t gptq_workspace_bytes(int M, int K, int N);
+
+/*
+ * y = x · deq(W) (+ bias) (+ residual).  The C-ABI form of
+ * triton_matmul4(groupsize, a, qweight, scales, qzeros, bias)
+ * (src/gptq_triton/quant_linear.py:228-283) and of the kernel it launches (:125-225).
+ *   g_idx     optional int32 [K]: act-order group of each row, rows in checkpoint order.
+ *   perm      optional int32 [K]: qweight rows have been re-ordered by
+ *             gptq_act_order_rows so that groups are contiguous; perm[j] is the
+ *             original row (= index into x) of sorted row j.  g_idx must be NULL then.
+ *   bias      optional fp16 [N];  residual optional fp16 [M, N] with row stride ldr.
+ * Requirements: K % 8 == 0, N % 8 == 0, ldx % 8 == 0, ldy % 8 == 0, pointers 16-byte aligned.
+ * Fast kernels need N % 32 == 0, groupsize % 32 == 0, K % groupsize == 0 and no g_idx;
+ * anything else runs on a slower general kernel.
+ */
+int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales,
+                 const int32_t *g_idx, const int32_t *perm,
+                 const void *bias, const void *residual, int64_t ldr,
+                 void *y, int M, int K, int N, int groupsize, int64_t ldx, int64_t ldy,
+                 void *workspace, size_t workspace_bytes, gptq_stream_t stream);
+
+/*
+ * y = silu(x · deq(Wg)) * (x · deq(Wu)), fp32 until the single fp16 store.  The C-ABI form of
+ * triton_llama_mlp_4 (src/gptq_triton/fused_mlp.py:241-302) and llama_mlp_fused_4_kernel
+ * (:109-233).  Gate and up have identical shapes [K/8, N]; y is [M, N].
+ * perm: as in gptq_qmatmul, applies to both matrices.
+ */
+int gptq_gateup_silu(const void *x,
+                     const int32_t *gate_qweight, const int32_t *gate_qzeros, const void *gate_scales,
+                     const int32_t *up_qweight, const int32_t *up_qzeros, const void *up_scales,
+                     const int32_t *g_idx, const int32_t *perm,
+                     void *y, int M, int K, int N, int groupsize, int64_t ldx, int64_t ldy,
+                     void *workspace, size_t workspace_bytes, gptq_stream_t stream);
+
+/*
+ * Fused QKV projection + rotary embedding: the quantised matmul of
+ * QuantLlamaAttention.forward (src/gptq_triton/fused_attention.py:91) with N = 3*hidden,
+ * followed by the split into heads and apply_rotary_pos_emb on Q and K (:92-102),
+ * done in the epilogue from the fp32 accumulators.
+ *   cos, sin      fp16 [max_pos, head_dim] rotate-half tables
+ *   position_ids  int32 [M]  (row m = b*tokens_per_batch + t)
+ *   q_out         fp16, element (m, h, d) at  m*q_stride_m + h*head_dim + d
+ *   k_out, v_out  fp16, element (m, h, d) at
+ *                   (m / tokens_per_batch)*kv_stride_b + (m % tokens_per_batch)*kv_stride_t
+ *                   + h*kv_stride_h + position_ids[m]*kv_stride_pos + d
+ *                 — plain [M, hidden] output: stride_b = T*hidden, stride_t = hidden,
+ *                   stride_h = head_dim, stride_pos = 0;
+ *                 — writing straight into a [b, h, max_seq, d] cache: stride_b = h*max_seq*d,
+ *                   stride_t = 0, stride_h = max_seq*d, stride_pos = d.
+ * head_dim must be 128.
+ */
+int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales,
+                  const int32_t *g_idx, const int32_t *perm,
+                  const void *cos, const void *sin, const int32_t *position_ids,
+                  void *q_out, int64_t q_stride_m,
+                  void *k_out, void *v_out, int tokens_per_batch,
+                  int64_t kv_stride_b, int64_t kv_stride_t, int64_t kv_stride_h, int64_t kv_stride_pos,
+                  int M, int K, int n_heads, int head_dim, int groupsize, int64_t ldx,
+                  void *workspace, size_t workspace_bytes, gptq_stream_t stream);
+
+/* uint8 [K, N] <- qweight int32 [K/8, N].  Integer unpack for the bit-exact check of the
+ * layout written by pack_linear (quantize.py:262-271). */
+int gptq_unpack_qweight(const int32_t *qweight, uint8_t *out, int K, int N, gptq_stream_t stream);
+
+/* uint8 [G, N] <- qzeros int32 [G, N/8]; values as stored (zero point - 1) (quantize.py:275-289). */
+int gptq_unpack_qzeros(const int32_t *qzeros, uint8_t *out, int G, int N, gptq_stream_t stream);
+
+/* fp16 [K, N] <- (q - z - 1) * s, one rounding.  The dequantise half of the
+ * dequantise-then-matmul comparison path; g_idx optional. */
+int gptq_dequantize(const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
+                    void *w_out, int K, int N, int groupsize, gptq_stream_t stream);
+
+/* out[j] (int32 [K/8, N]) = packed rows of qweight taken in the order perm[0..K): the
+ * load-time re-ordering that makes act-order groups contiguous.  No reference
+ * counterpart (the reference refuses act-order with groups, quantize.py:41-42). */
+int gptq_act_order_rows(const int32_t *qweight, const int32_t *perm, int32_t *out, int K, int N,
+                        gptq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPTQ_B200_H */

@@ -1,0 +1,72 @@
+"""CPU-side checks of the C-ABI boundary: the library loads, exports every symbol the
+header declares, and its pure-host entry points answer.  No kernel is launched."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope='module')
+def lib():
+	from gptq_triton_b200 import build, _lib
+	build.build()
+	return _lib.lib()
+
+
+def declared_symbols():
+	text = (ROOT / 'include' / 'gptq_b200.h').read_text()
+	text = re.sub(r'/\*.*?\*/', '', text, flags=re.S)
+	return sorted(set(re.findall(r'\b(gptq_[a-z0-9_]+)\s*\(', text)))
+
+
+def test_header_symbols_exported(lib):
+	names = declared_symbols()
+	assert len(names) >= 10
+	for n in names:
+		assert hasattr(lib, n), f'{n} declared in include/gptq_b200.h but not exported'
+
+
+def test_binding_covers_header(lib):
+	from gptq_triton_b200 import _lib
+	assert sorted(_lib.exported_symbols()) == declared_symbols()
+
+
+def test_host_entry_points(lib):
+	assert lib.gptq_version() >= 100
+	assert lib.gptq_error_string(0) == b'ok'
+	for code in range(-6, 0):
+		assert len(lib.gptq_error_string(code)) > 3
+	assert lib.gptq_error_string(-99) == b'unknown error code'
+	small = lib.gptq_workspace_bytes(1, 4096, 4096)
+	big = lib.gptq_workspace_bytes(16, 4096, 22016)
+	assert 0 < small < big < (256 << 20)
+
+
+def test_argument_errors_before_any_launch(lib):
+	"""Invalid arguments are rejected on the host; nothing touches the GPU."""
+	fake = ctypes.c_void_p(0x1000)
+	args = lambda x=fake, M=1, K=256, N=256, gs=128, ldx=256: (
+		x, fake, fake, fake, None, None, None, None, 0, fake, M, K, N, gs, ldx, N, None, 0, None)
+	assert lib.gptq_qmatmul(*args(x=None)) == -1
+	assert lib.gptq_qmatmul(*args(K=12)) == -2
+	assert lib.gptq_qmatmul(*args(x=ctypes.c_void_p(0x1004))) == -4
+	assert lib.gptq_qmatmul(*args(ldx=100)) == -1
+	assert lib.gptq_qmatmul(*args(M=0)) == 0          # empty batch: nothing to do
+	assert lib.gptq_qmatmul(*args(gs=0)) == -1
+
+
+def test_python_ops_refuse_cpu_tensors():
+	import torch
+	import gptq_triton_b200 as g
+	from gptq_triton_b200._lib import GptqB200Error
+	x = torch.zeros(1, 256, dtype=torch.float16)
+	qw = torch.zeros(32, 256, dtype=torch.int32)
+	qz = torch.zeros(2, 32, dtype=torch.int32)
+	sc = torch.zeros(2, 256, dtype=torch.float16)
+	with pytest.raises(GptqB200Error):
+		g.triton_matmul4(128, x, qw, sc, qz)
+	with pytest.raises(AssertionError):
+		g.triton_matmul4(128, torch.zeros(1, 250, dtype=torch.float16), qw, sc, qz)
