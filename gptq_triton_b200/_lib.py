@@ -35,6 +35,7 @@ _SIGNATURES = {
 # Entry points outside the header's stable surface (tuning hooks); bound when present.
 _OPTIONAL = {
 	'gptq_debug_force_splitk': (None, [c_int]),
+	'gptq_debug_force_kw': (None, [c_int]),
 }
 
 

@@ -3,6 +3,8 @@
 #include <cstdlib>
 #include <mutex>
 
+#include <cuda.h>
+
 #include "common.cuh"
 #include "qmm_skinny.cuh"
 #include "qmm_tc.cuh"
@@ -12,6 +14,7 @@ namespace gptq {
 thread_local int g_last_cuda_error = 0;
 
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
+static int g_force_kw = 2;
 
 static int sm_count() {
 	static int cached[64] = {0};
@@ -80,12 +83,13 @@ __global__ void act_order_rows_kernel(const uint32_t *__restrict__ qw, const int
 }
 
 // ---- skinny-kernel planning ---------------------------------------------------------------
-constexpr int SK_KW = 4;
 constexpr int SK_MAX_SPLITK = 16;
 constexpr int SK_SMEM_LIMIT = 227 * 1024;
 
 static bool skinny_shape_ok(int K, int N, int groupsize, const int32_t *g_idx) {
-	return g_idx == nullptr && N % 32 == 0 && groupsize % 32 == 0 && K % groupsize == 0 && (N / SK_BN + 1) * 4 <= SK_TICKET_BYTES;
+	const bool gs_ok = groupsize == 32 || groupsize == 64 || groupsize % 128 == 0;
+	return g_idx == nullptr && N % 32 == 0 && K % 128 == 0 && gs_ok && K % groupsize == 0 &&
+		   (N / SK_BN + 2) * 4 <= SK_TICKET_BYTES - 4;
 }
 
 static size_t skinny_ws_bytes(int M, int N, int nstream) {
@@ -93,71 +97,166 @@ static size_t skinny_ws_bytes(int M, int N, int nstream) {
 	return SK_TICKET_BYTES + tiles * SK_MAX_SPLITK * nstream * (size_t)std::min(M, 16) * SK_BN * sizeof(float);
 }
 
-static void plan_skinny(SkinnyParams &p, int nstream, dim3 &grid, size_t &smem) {
-	const int rows = p.M <= 8 ? 8 : 16;
-	p.total_steps = p.K / 32;
-	const int spg = p.groupsize / 32;
-	int seg_steps;
-	if (p.groupsize == p.K) {
-		seg_steps = std::min(8, p.total_steps);
-	} else {
-		seg_steps = spg;
-		while (seg_steps > 16 && seg_steps % 2 == 0) seg_steps /= 2;
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+								  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+								  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn tensor_map_encoder() {
+	static EncodeTiledFn fn = nullptr;
+	static std::once_flag once;
+	std::call_once(once, [] {
+		void *ptr = nullptr;
+		cudaDriverEntryPointQueryResult q;
+		if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+			q == cudaDriverEntryPointSuccess)
+			fn = reinterpret_cast<EncodeTiledFn>(ptr);
+	});
+	return fn;
+}
+
+// Tensor map over packed weights int32 [K/8, N] with a box of 32 columns x 16 packed rows,
+// written to shared memory with the 128-byte swizzle.
+static int weight_tensor_map(const int32_t *qw, int K, int N, CUtensorMap *out) {
+	EncodeTiledFn enc = tensor_map_encoder();
+	if (!enc) return GPTQ_ERR_CUDA;
+	cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 8)};
+	cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+	cuuint32_t box[2] = {32, 16};
+	cuuint32_t estr[2] = {1, 1};
+	CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t *>(qw), dims, strides, box, estr,
+					 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+					 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	if (r != CUDA_SUCCESS) {
+		g_last_cuda_error = (int)r;
+		return GPTQ_ERR_CUDA;
 	}
-	p.seg_steps = seg_steps;
-	p.total_segs = (p.total_steps + seg_steps - 1) / seg_steps;
+	return GPTQ_OK;
+}
+
+// Chooses the split-K factor and the shared-memory layout.  The aim is one wave of
+// co-resident CTAs that covers (nearly) all SM slots with equal K-slices: the kernel is
+// HBM-bound, so what counts is bytes in flight across the whole chip and no tail wave.
+static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_t &smem) {
+	p.spg = p.groupsize / 32;
+	p.total_chunks = p.K / 128;
 	const int tiles = (p.N + SK_BN - 1) / SK_BN;
-	const int ring = SK_KW * 4 * SK_D * 32 * 16;
-	const int xbudget = SK_SMEM_LIMIT - ring - 2048;
-	const int ks_max = ((xbudget / rows) - 64) / 2;
-	const int segs_max = std::max(1, (ks_max / 32) / seg_steps);
-	const int min_split = (p.total_segs + segs_max - 1) / segs_max;
 	const int sms = sm_count();
-	int best = -1;
-	double best_cost = 0;
-	for (int sk = min_split; sk <= std::max(min_split, std::min(p.total_segs, SK_MAX_SPLITK)); ++sk) {
-		const int sps = (p.total_segs + sk - 1) / sk;
-		const int eff = (p.total_segs + sps - 1) / sps;
-		const int waves = (tiles * eff + sms - 1) / sms;
-		const double per_cta = (double)((sps + SK_KW - 1) / SK_KW) * seg_steps * nstream + 12.0 + 1.5 * eff;
-		const double cost = waves * per_cta;
-		if (best < 0 || cost < best_cost) {
-			best = sk;
-			best_cost = cost;
+	auto layout = [&](int sk, int kwarps, int nstage, int &cps, int &eff, int &xs_stride, int &xs_bytes, int &strip_groups) -> size_t {
+		cps = (p.total_chunks + sk - 1) / sk;
+		eff = (p.total_chunks + cps - 1) / cps;
+		const int ks = cps * 128;
+		xs_stride = ks * 2 + 16;      // = 16 mod 128: rows gid, gid+1 read disjoint banks
+		xs_bytes = (p.M * xs_stride + 127) / 128 * 128;
+		strip_groups = (ks + p.groupsize - 1) / p.groupsize + 1;
+		const size_t strips = (size_t)nstream * strip_groups * SK_BN * 2 * 2;
+		const size_t ring = (size_t)kwarps * 4 * nstage * SK_CHUNK_BYTES;
+		return ring + SK_BAR_BYTES + (size_t)xs_bytes + strips;
+	};
+	int best_sk = -1, best_kw = 2, best_stage = 4;
+	double best_score = -1e30;
+	for (int kwarps = 2; kwarps <= (p.spg < 4 ? 2 : 4); kwarps += 2) {
+		const int per_sm = 4 / kwarps;
+		const size_t cap = kwarps == 2 ? (size_t)113 * 1024 : (size_t)SK_SMEM_LIMIT - 2048;
+		const int slots = sms * per_sm;
+		for (int sk = 1; sk <= std::min(p.total_chunks, SK_MAX_SPLITK); ++sk) {
+			int cps, eff, a, b, c;
+			int nstage = 4;
+			while (nstage > 2 && layout(sk, kwarps, nstage, cps, eff, a, b, c) > cap) --nstage;
+			if (layout(sk, kwarps, nstage, cps, eff, a, b, c) > cap) continue;
+			if (eff != sk) continue;
+			const int ctas = tiles * eff;
+			const int waves = (ctas + slots - 1) / slots;
+			// fraction of the chip's slots kept busy, a strong preference for a single wave,
+			// a mild one for fewer splits (less reduction traffic) and deep rings
+			double score = (double)ctas / ((double)waves * slots);
+			score -= 0.35 * (waves - 1);
+			score -= 0.004 * eff;
+			score -= 0.02 * (4 - nstage);
+			if (cps < kwarps) score -= 0.25;
+			if (kwarps == 4) score -= 0.03;
+			if (score > best_score) {
+				best_score = score;
+				best_sk = sk;
+				best_kw = kwarps;
+				best_stage = nstage;
+			}
 		}
 	}
-	if (g_force_splitk > 0) best = std::max(min_split, std::min(g_force_splitk, p.total_segs));
-	p.segs_per_split = (p.total_segs + best - 1) / best;
-	p.splitk = (p.total_segs + p.segs_per_split - 1) / p.segs_per_split;
-	const int ks = p.segs_per_split * seg_steps * 32;
-	p.xs_stride = ks * 2 + (((ks * 2) % 128 == 0) ? 64 : 0);
-	p.xs_bytes = (rows * p.xs_stride + 127) / 128 * 128;
+	if (g_force_splitk > 0) {
+		best_sk = std::min(g_force_splitk, p.total_chunks);
+		best_kw = p.spg < 4 ? 2 : g_force_kw;
+		best_stage = 4;
+		int cps, eff, a, b, c;
+		const size_t cap = best_kw == 2 ? (size_t)113 * 1024 : (size_t)SK_SMEM_LIMIT - 2048;
+		while (best_stage > 2 && layout(best_sk, best_kw, best_stage, cps, eff, a, b, c) > cap) --best_stage;
+	}
+	if (best_sk < 0) { best_sk = std::min(p.total_chunks, SK_MAX_SPLITK); best_kw = 4; best_stage = 2; }
+	int cps, eff;
+	smem = layout(best_sk, best_kw, best_stage, cps, eff, p.xs_stride, p.xs_bytes, p.strip_groups);
+	p.chunks_per_split = cps;
+	p.splitk = eff;
+	p.nstage = best_stage;
+	kw = best_kw;
 	grid = dim3(tiles, p.splitk, 1);
-	smem = (size_t)p.xs_bytes + ring;
+}
+
+// Opt the kernel in to the full dynamic shared memory once per device.
+template <typename Kern>
+static int ensure_smem_attr(Kern k, bool (&ready)[64]) {
+	int dev = 0;
+	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GPTQ_ERR_CUDA;
+	if (!ready[dev]) {
+		cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_LIMIT - 1024);
+		if (e != cudaSuccess) return cuda_status(e);
+		ready[dev] = true;
+	}
+	return GPTQ_OK;
+}
+
+template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI>
+static int launch_skinny_inst(const CUtensorMap &tm0, const CUtensorMap &tm1, const SkinnyParams &p, dim3 grid, size_t smem,
+							  cudaStream_t stream) {
+	auto k = skinny_kernel<KW, NSTREAM, M8, SPG_T, EPI>;
+	static bool ready[64] = {false};
+	if (int rc = ensure_smem_attr(k, ready)) return rc;
+	k<<<grid, KW * 128, smem, stream>>>(tm0, tm1, p);
+	return cuda_status(cudaGetLastError());
 }
 
 template <int NSTREAM, int EPI>
-static int launch_skinny(SkinnyParams &p, void *workspace, size_t ws_bytes, cudaStream_t stream) {
+static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1, void *workspace, size_t ws_bytes,
+						 cudaStream_t stream) {
 	dim3 grid;
 	size_t smem;
-	plan_skinny(p, NSTREAM, grid, smem);
+	int kw;
+	plan_skinny(p, NSTREAM, kw, grid, smem);
+	if (smem > (size_t)SK_SMEM_LIMIT - 1024) return GPTQ_ERR_UNSUPPORTED;
 	const size_t need = skinny_ws_bytes(p.M, p.N, NSTREAM);
-	if (p.splitk > 1 && (workspace == nullptr || ws_bytes < need)) return GPTQ_ERR_WORKSPACE;
+	if (workspace == nullptr || ws_bytes < need) return GPTQ_ERR_WORKSPACE;
 	p.ws_ticket = reinterpret_cast<int *>(workspace);
 	p.ws_partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + SK_TICKET_BYTES);
-	cudaError_t e;
-	if (p.M <= 8) {
-		auto k = skinny_kernel<SK_KW, NSTREAM, true, EPI>;
-		e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-		if (e != cudaSuccess) return cuda_status(e);
-		k<<<grid, SK_KW * 128, smem, stream>>>(p);
+	alignas(64) CUtensorMap tm0, tm1;
+	if (int rc = weight_tensor_map(qw0, p.K, p.N, &tm0)) return rc;
+	if (NSTREAM == 2) {
+		if (int rc = weight_tensor_map(qw1, p.K, p.N, &tm1)) return rc;
 	} else {
-		auto k = skinny_kernel<SK_KW, NSTREAM, false, EPI>;
-		e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-		if (e != cudaSuccess) return cuda_status(e);
-		k<<<grid, SK_KW * 128, smem, stream>>>(p);
+		tm1 = tm0;
 	}
-	return cuda_status(cudaGetLastError());
+	const bool m8 = p.M <= 8;
+	if (p.spg == 1) {
+		return m8 ? launch_skinny_inst<2, NSTREAM, true, 1, EPI>(tm0, tm1, p, grid, smem, stream)
+				  : launch_skinny_inst<2, NSTREAM, false, 1, EPI>(tm0, tm1, p, grid, smem, stream);
+	}
+	if (p.spg == 2) {
+		return m8 ? launch_skinny_inst<2, NSTREAM, true, 2, EPI>(tm0, tm1, p, grid, smem, stream)
+				  : launch_skinny_inst<2, NSTREAM, false, 2, EPI>(tm0, tm1, p, grid, smem, stream);
+	}
+	if (kw == 2) {
+		return m8 ? launch_skinny_inst<2, NSTREAM, true, 0, EPI>(tm0, tm1, p, grid, smem, stream)
+				  : launch_skinny_inst<2, NSTREAM, false, 0, EPI>(tm0, tm1, p, grid, smem, stream);
+	}
+	return m8 ? launch_skinny_inst<4, NSTREAM, true, 0, EPI>(tm0, tm1, p, grid, smem, stream)
+			  : launch_skinny_inst<4, NSTREAM, false, 0, EPI>(tm0, tm1, p, grid, smem, stream);
 }
 
 static int check_common(const void *x, const void *qw, const void *qz, const void *sc, const void *y, int M, int K, int N,
@@ -198,6 +297,7 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 
 // Tuning / test hook: force the split-K factor of the decode kernel (0 restores the heuristic).
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
+void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
 
 size_t gptq_workspace_bytes(int M, int K, int N) {
 	(void)K;
@@ -218,12 +318,12 @@ int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, c
 	if (fast && M <= 16) {
 		SkinnyParams p = {};
 		p.x = (const __half *)x; p.ldx = ldx;
-		p.qw0 = qweight; p.qz0 = qzeros; p.sc0 = (const __half *)scales;
+		p.qz0 = qzeros; p.sc0 = (const __half *)scales;
 		p.perm = perm;
 		p.M = M; p.K = K; p.N = N; p.groupsize = groupsize;
 		p.bias = (const __half *)bias; p.residual = (const __half *)residual; p.ldr = ldr;
 		p.y = (__half *)y; p.ldy = ldy;
-		return launch_skinny<1, EPI_PLAIN>(p, workspace, workspace_bytes, st);
+		return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, workspace, workspace_bytes, st);
 	}
 	if (fast && tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};
@@ -255,12 +355,12 @@ int gptq_gateup_silu(const void *x, const int32_t *gate_qweight, const int32_t *
 	if (fast && M <= 16) {
 		SkinnyParams p = {};
 		p.x = (const __half *)x; p.ldx = ldx;
-		p.qw0 = gate_qweight; p.qz0 = gate_qzeros; p.sc0 = (const __half *)gate_scales;
-		p.qw1 = up_qweight; p.qz1 = up_qzeros; p.sc1 = (const __half *)up_scales;
+		p.qz0 = gate_qzeros; p.sc0 = (const __half *)gate_scales;
+		p.qz1 = up_qzeros; p.sc1 = (const __half *)up_scales;
 		p.perm = perm;
 		p.M = M; p.K = K; p.N = N; p.groupsize = groupsize;
 		p.y = (__half *)y; p.ldy = ldy;
-		return launch_skinny<2, EPI_SILU>(p, workspace, workspace_bytes, st);
+		return launch_skinny<2, EPI_SILU>(p, gate_qweight, up_qweight, workspace, workspace_bytes, st);
 	}
 	if (fast && tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};
@@ -301,14 +401,14 @@ int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, 
 	if (M <= 16) {
 		SkinnyParams p = {};
 		p.x = (const __half *)x; p.ldx = ldx;
-		p.qw0 = qweight; p.qz0 = qzeros; p.sc0 = (const __half *)scales;
+		p.qz0 = qzeros; p.sc0 = (const __half *)scales;
 		p.perm = perm;
 		p.M = M; p.K = K; p.N = N; p.groupsize = groupsize;
 		p.cos_t = (const __half *)cos; p.sin_t = (const __half *)sin; p.pos = position_ids;
 		p.q_out = (__half *)q_out; p.k_out = (__half *)k_out; p.v_out = (__half *)v_out;
 		p.q_stride_m = q_stride_m; p.kv_sb = kv_stride_b; p.kv_st = kv_stride_t; p.kv_sh = kv_stride_h;
 		p.kv_sp = kv_stride_pos; p.tokens_per_batch = tokens_per_batch; p.hidden = hidden;
-		return launch_skinny<1, EPI_ROPE>(p, workspace, workspace_bytes, st);
+		return launch_skinny<1, EPI_ROPE>(p, qweight, nullptr, workspace, workspace_bytes, st);
 	}
 	if (tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};

@@ -1,29 +1,31 @@
 // Decode-regime (M <= 16) quantised matmul for sm_100a: an HBM-bound skinny GEMM.
 //
 // Work split.  A CTA owns 128 output columns (4 warps x 32 columns) and one K-slice
-// (grid.y = split-K).  Inside the CTA, KW warp-rows split the slice further, segment by
-// segment; a segment is a run of 32-row steps that lies inside one quantisation group.
+// (grid.y = split-K); its KW warp-rows take contiguous parts of the slice.  The unit of
+// streaming is a chunk: 128 K-rows = 16 packed rows x 32 columns = 2 KB per warp.
 //
-// Weight stream.  In one step a warp reads 4 packed rows x 32 columns = 4 x 128
-// contiguous bytes: lane (gid = lane/4, tig = lane%4) fetches 16 bytes = 4 columns of
-// packed row 4*step + tig with cp.async into a private 8-deep ring in shared memory
-// (each lane reads back only what it fetched, so no barrier is involved).
+// Weight stream.  Every warp runs a private TMA pipeline: lane 0 issues one 2-D tiled bulk
+// copy (box 32 columns x 16 packed rows) per chunk into an NSTAGE-deep ring in shared
+// memory and all lanes wait on the stage's mbarrier.  No other warp touches the ring, so
+// stage reuse needs only a __syncwarp.  Lane (gid = lane/4, tig = lane%4) reads the 16
+// bytes that hold its 4 columns (4*gid..4*gid+3) of packed row 4*step + tig.
 //
-// Math.  The 8 nibbles of a word are the 8 K-values of one column.  Masking with
-// 0x000F000F / 0x00F000F0 yields the half2 pairs (k0,k4) (k1,k5) and, after >>8,
-// (k2,k6) (k3,k7) as 1024+q resp. 1024+16q; one sub / fma per pair turns them into the
-// exact integers q - zero.  These feed mma.sync.m16n8k16 as the B operand; the batch rows
-// of x are the A operand, staged in shared memory in the matching k order
-// [0,4,1,5,2,6,3,7].  The integer dot products accumulate in fp32 per segment and are
-// multiplied by the group's scale in fp32 at the segment end, so a weight is never
-// rounded to fp16: the result equals an fp32-accumulated (q-z-1)*s reference up to fp32
-// summation order.
+// Math.  The 8 nibbles of a word are 8 K-values of one column.  Masking with 0x000F000F /
+// 0x00F000F0 yields the half2 pairs (k0,k4) (k1,k5) and, after >>8, (k2,k6) (k3,k7) as
+// 1024+q resp. 1024+16q; one sub / fma per pair turns them into the exact integers
+// q - zero.  They are the A operand of mma.sync.m16n8k16 (16 weight columns x 16 k); the
+// batch rows of x are the B operand, staged in shared memory in the matching k order
+// [0,4,1,5,2,6,3,7].  Integer dot products accumulate in fp32 per group and are scaled by
+// the group's fp32 scale when the group ends, so no weight is ever rounded to fp16: the
+// result equals an fp32-accumulated (q-z-1)*s reference up to fp32 summation order.
 //
-// Reduction.  KW warp-rows reduce through shared memory; split-K CTAs write fp32
-// partials to the workspace and take a ticket; the last CTA of a tile sums the partials
-// in fixed order (deterministic) and runs the epilogue: bias/residual, SiLU(gate)*up,
-// or rotary embedding with a scatter into Q / K / V (or the KV cache).
+// Reduction.  Warp-rows reduce through shared memory; split-K CTAs write fp32 partials to
+// the workspace and take a ticket; the last CTA of a tile sums the partials in fixed order
+// (deterministic) and runs the epilogue: bias/residual, SiLU(gate)*up, or rotary embedding
+// with a scatter into Q / K / V (or the KV cache).
 #pragma once
+
+#include <cuda.h>
 
 #include "common.cuh"
 
@@ -31,25 +33,27 @@ namespace gptq {
 
 enum { EPI_PLAIN = 0, EPI_SILU = 1, EPI_ROPE = 2 };
 
-constexpr int SK_BN = 128;      // columns per CTA
-constexpr int SK_D = 8;         // cp.async ring depth (steps)
-constexpr int SK_TICKET_BYTES = 16384;
+constexpr int SK_BN = 128;                 // columns per CTA
+constexpr int SK_CHUNK_BYTES = 2048;       // one warp-chunk: 16 packed rows x 128 bytes
+constexpr int SK_BAR_BYTES = 1024;         // room for the per-warp, per-stage mbarriers
+constexpr int SK_TICKET_BYTES = 16384;     // arrival counters; the last int is a status word
+constexpr int SK_STATUS_SLOT = SK_TICKET_BYTES / 4 - 1;
 
 struct SkinnyParams {
 	const __half *x;
 	long long ldx;
-	const int32_t *qw0, *qw1;
 	const int32_t *qz0, *qz1;
 	const __half *sc0, *sc1;
 	const int32_t *perm;
 	int M, K, N, groupsize;
-	int seg_steps;        // steps (of 32 rows) per segment
-	int total_steps;      // K / 32
-	int total_segs;       // ceil(total_steps / seg_steps)
-	int segs_per_split;
+	int spg;               // 32-row steps per group (1, 2 or a multiple of 4)
+	int total_chunks;      // K / 128
+	int chunks_per_split;
 	int splitk;
-	int xs_stride;        // bytes between rows of the staged x slice
-	int xs_bytes;         // rows * xs_stride, rounded up to 128
+	int nstage;
+	int xs_stride;         // bytes between rows of the staged x slice
+	int xs_bytes;          // M * xs_stride rounded up to 128
+	int strip_groups;      // capacity (groups) of the zero / scale strips per stream
 	float *ws_partial;
 	int *ws_ticket;
 	// EPI_PLAIN / EPI_SILU
@@ -66,12 +70,15 @@ struct SkinnyParams {
 	int tokens_per_batch, hidden;
 };
 
-template <int KW, int NSTREAM, bool M8, int EPI>
-__global__ void __launch_bounds__(KW * 128, 1) skinny_kernel(const SkinnyParams p) {
-	extern __shared__ __align__(128) unsigned char smem[];
+// SPG_T: steps per group known at compile time (1 or 2), or 0 when a group spans whole chunks.
+template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI>
+__global__ void __launch_bounds__(KW * 128, 4 / KW)
+	skinny_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, const SkinnyParams p) {
+	extern __shared__ __align__(1024) unsigned char smem[];
 	constexpr int NT = KW * 128;
+	constexpr int NWARP = KW * 4;
 	constexpr int ROWS = M8 ? 8 : 16;
-	constexpr int D = SK_D;
+	constexpr int MB = M8 ? 1 : 2;             // batch-row blocks of 8
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int wn = warp & 3, kw = warp >> 2, gid = lane >> 2, tig = lane & 3;
@@ -79,170 +86,268 @@ __global__ void __launch_bounds__(KW * 128, 1) skinny_kernel(const SkinnyParams 
 	const int n0 = tile * SK_BN, n0w = n0 + wn * 32;
 	const bool warp_active = n0w < p.N;
 
-	unsigned char *xs = smem;
-	unsigned char *scratch = smem + p.xs_bytes;                        // ring, later the reduce buffer
-	uint4 *ring = reinterpret_cast<uint4 *>(scratch) + warp * (D * 32) + lane;
-	float *red = reinterpret_cast<float *>(scratch);
+	// shared memory: [ ring | mbarriers | x slice | zero strips | scale strips ]; the ring
+	// region is reused as the reduce buffer once the stream has drained
+	unsigned char *ring_all = smem;
+	const int ring_bytes = NWARP * p.nstage * SK_CHUNK_BYTES;
+	uint64_t *bars = reinterpret_cast<uint64_t *>(smem + ring_bytes);
+	unsigned char *xs = smem + ring_bytes + SK_BAR_BYTES;
+	__half *s_ze = reinterpret_cast<__half *>(xs + p.xs_bytes);                  // [stream][group][128] = 1024 + zero
+	__half *s_sc = s_ze + NSTREAM * p.strip_groups * SK_BN;                      // [stream][group][128]
+	float *red = reinterpret_cast<float *>(smem);
 	__shared__ int s_last;
 
-	const int seg0 = split * p.segs_per_split;
-	const int seg1 = min(seg0 + p.segs_per_split, p.total_segs);
-	const int step_lo = seg0 * p.seg_steps;                            // first step of this CTA's slice
-	const int step_hi = min(seg1 * p.seg_steps, p.total_steps);
+	const int c_lo = split * p.chunks_per_split;
+	const int c_hi = min(c_lo + p.chunks_per_split, p.total_chunks);
+	const int per_w = (c_hi - c_lo + KW - 1) / KW;
+	const int w_lo = min(c_lo + kw * per_w, c_hi);
+	const int w_hi = min(w_lo + per_w, c_hi);
+	const int nw = warp_active ? (w_hi - w_lo) : 0;      // chunks per stream for this warp
+	const int nload = nw * NSTREAM;
 
-	// number of steps this warp will consume
-	int nsteps = 0;
-	if (warp_active) {
-		for (int s = seg0 + kw; s < seg1; s += KW) nsteps += min(p.seg_steps, p.total_steps - s * p.seg_steps);
-		nsteps *= NSTREAM;
+	// ---- per-warp TMA pipeline -------------------------------------------------------
+	const uint32_t ring_w = smem_u32(ring_all + (size_t)warp * p.nstage * SK_CHUNK_BYTES);
+	const uint32_t bar_w = smem_u32(bars + warp * p.nstage);
+	if (lane == 0) {
+		for (int s = 0; s < p.nstage; ++s) mbar_init(bar_w + 8 * s, 1);
+		fence_mbar_init();
+		if (warp == 0) {
+			tma_prefetch_desc(&tm0);
+			if (NSTREAM == 2) tma_prefetch_desc(&tm1);
+		}
 	}
-
-	// ---- weight stream: issue side ------------------------------------------------
-	int is_seg = seg0 + kw, is_stream = 0, is_local = 0, issued = 0;
-	int is_len = min(p.seg_steps, p.total_steps - is_seg * p.seg_steps);
-	const size_t col_off = (size_t)(n0w + gid * 4);
-	auto issue = [&]() {
-		if (issued < nsteps) {
-			const int R = (is_seg * p.seg_steps + is_local) * 4 + tig;
-			const int32_t *base = (NSTREAM == 2 && is_stream) ? p.qw1 : p.qw0;
-			cp_async16(&ring[(issued & (D - 1)) * 32], base + (size_t)R * p.N + col_off);
-			++issued;
-			if (++is_local == is_len) {
-				is_local = 0;
-				if (++is_stream == NSTREAM) {
-					is_stream = 0;
-					is_seg += KW;
-					is_len = min(p.seg_steps, p.total_steps - is_seg * p.seg_steps);
-				}
+	__syncwarp();
+	int pr_j = 0, pr_chunk = w_lo, pr_stream = 0, pr_stage = 0;
+	auto produce = [&]() {
+		if (pr_j < nload) {
+			if (lane == 0) {
+				const uint32_t bar = bar_w + 8 * pr_stage;
+				fence_proxy_async();
+				mbar_arrive_expect_tx(bar, SK_CHUNK_BYTES);
+				tma_load_2d(ring_w + pr_stage * SK_CHUNK_BYTES, (NSTREAM == 2 && pr_stream) ? &tm1 : &tm0, n0w, pr_chunk * 16, bar);
+			}
+			++pr_j;
+			if (++pr_stage == p.nstage) pr_stage = 0;
+			if (++pr_chunk == w_hi) {
+				pr_chunk = w_lo;
+				++pr_stream;
 			}
 		}
-		cp_async_commit();
 	};
-#pragma unroll
-	for (int i = 0; i < D - 1; ++i) issue();
+	for (int s = 0; s < p.nstage; ++s) produce();
 
-	// ---- stage the x slice: [row][unit of 8 k] in k order 0,4,1,5,2,6,3,7 -----------
+	// ---- stage zero / scale strips and the x slice ---------------------------------------
+	const int g_lo = (c_lo * 128) / p.groupsize;
 	{
-		const int units = (step_hi - step_lo) * 4;
-		for (int idx = tid; idx < ROWS * units; idx += NT) {
-			const int row = idx / units, unit = idx - row * units;
-			const int k = (step_lo * 4 + unit) * 8;
-			uint4 v = make_uint4(0u, 0u, 0u, 0u);
-			if (row < p.M) {
-				const __half *xr = p.x + (size_t)row * p.ldx;
-				if (p.perm == nullptr) {
-					v = *reinterpret_cast<const uint4 *>(xr + k);
-				} else {
-					const int4 pa = *reinterpret_cast<const int4 *>(p.perm + k);
-					const int4 pb = *reinterpret_cast<const int4 *>(p.perm + k + 4);
-					const uint32_t h0 = __half_as_ushort(xr[pa.x]), h1 = __half_as_ushort(xr[pa.y]);
-					const uint32_t h2 = __half_as_ushort(xr[pa.z]), h3 = __half_as_ushort(xr[pa.w]);
-					const uint32_t h4 = __half_as_ushort(xr[pb.x]), h5 = __half_as_ushort(xr[pb.y]);
-					const uint32_t h6 = __half_as_ushort(xr[pb.z]), h7 = __half_as_ushort(xr[pb.w]);
-					v = make_uint4(h0 | (h1 << 16), h2 | (h3 << 16), h4 | (h5 << 16), h6 | (h7 << 16));
+		const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
+		const int nz = p.N >> 3;
+		for (int idx = tid; idx < NSTREAM * ng * 16; idx += NT) {
+			const int s = idx / (ng * 16), r = idx - s * (ng * 16);
+			const int gi = r >> 4, c = r & 15;              // 8 columns per item
+			if (n0 + c * 8 < p.N) {
+				const int32_t *qz = (NSTREAM == 2 && s) ? p.qz1 : p.qz0;
+				const __half *sc = (NSTREAM == 2 && s) ? p.sc1 : p.sc0;
+				const uint32_t z = (uint32_t)__ldg(qz + (size_t)(g_lo + gi) * nz + (n0 >> 3) + c);
+				const uint4 sv = __ldg(reinterpret_cast<const uint4 *>(sc + (size_t)(g_lo + gi) * p.N + n0 + c * 8));
+				uint4 ze;       // half(1024 + zero) = 0x6400 + (stored + 1), two per word
+				ze.x = 0x64016401u + ((z & 0xFu) | ((z & 0xF0u) << 12));
+				ze.y = 0x64016401u + (((z >> 8) & 0xFu) | (((z >> 8) & 0xF0u) << 12));
+				ze.z = 0x64016401u + (((z >> 16) & 0xFu) | (((z >> 16) & 0xF0u) << 12));
+				ze.w = 0x64016401u + (((z >> 24) & 0xFu) | (((z >> 24) & 0xF0u) << 12));
+				const size_t o = (size_t)(s * p.strip_groups + gi) * SK_BN + c * 8;
+				*reinterpret_cast<uint4 *>(s_ze + o) = ze;
+				*reinterpret_cast<uint4 *>(s_sc + o) = sv;
+			}
+		}
+		// x slice: [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7.  Loads of a batch of
+		// items are issued together so that their latencies overlap.
+		const int units = (c_hi - c_lo) * 16;
+		const int nitem = p.M * units;
+		constexpr int XB = 4;
+		for (int base = tid; base < nitem; base += NT * XB) {
+			uint4 v[XB];
+			if (p.perm == nullptr) {
+#pragma unroll
+				for (int j = 0; j < XB; ++j) {
+					const int idx = base + j * NT;
+					if (idx < nitem) {
+						const int row = idx / units, unit = idx - row * units;
+						v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)row * p.ldx + (c_lo * 16 + unit) * 8));
+					}
+				}
+			} else {
+				int4 pa[XB], pb[XB];
+#pragma unroll
+				for (int j = 0; j < XB; ++j) {
+					const int idx = base + j * NT;
+					if (idx < nitem) {
+						const int unit = idx % units;
+						const int k = (c_lo * 16 + unit) * 8;
+						pa[j] = __ldg(reinterpret_cast<const int4 *>(p.perm + k));
+						pb[j] = __ldg(reinterpret_cast<const int4 *>(p.perm + k + 4));
+					}
+				}
+#pragma unroll
+				for (int j = 0; j < XB; ++j) {
+					const int idx = base + j * NT;
+					if (idx < nitem) {
+						const unsigned short *xr = reinterpret_cast<const unsigned short *>(p.x) + (size_t)(idx / units) * p.ldx;
+						const uint32_t h0 = __ldg(xr + pa[j].x), h1 = __ldg(xr + pa[j].y), h2 = __ldg(xr + pa[j].z), h3 = __ldg(xr + pa[j].w);
+						const uint32_t h4 = __ldg(xr + pb[j].x), h5 = __ldg(xr + pb[j].y), h6 = __ldg(xr + pb[j].z), h7 = __ldg(xr + pb[j].w);
+						v[j] = make_uint4(h0 | (h1 << 16), h2 | (h3 << 16), h4 | (h5 << 16), h6 | (h7 << 16));
+					}
 				}
 			}
-			uint4 o;
-			o.x = __byte_perm(v.x, v.z, 0x5410);    // (x0, x4)
-			o.y = __byte_perm(v.x, v.z, 0x7632);    // (x1, x5)
-			o.z = __byte_perm(v.y, v.w, 0x5410);    // (x2, x6)
-			o.w = __byte_perm(v.y, v.w, 0x7632);    // (x3, x7)
-			*reinterpret_cast<uint4 *>(xs + (size_t)row * p.xs_stride + unit * 16) = o;
+#pragma unroll
+			for (int j = 0; j < XB; ++j) {
+				const int idx = base + j * NT;
+				if (idx < nitem) {
+					const int row = idx / units, unit = idx - row * units;
+					uint4 o;
+					o.x = __byte_perm(v[j].x, v[j].z, 0x5410);    // (x0, x4)
+					o.y = __byte_perm(v[j].x, v[j].z, 0x7632);    // (x1, x5)
+					o.z = __byte_perm(v[j].y, v[j].w, 0x5410);    // (x2, x6)
+					o.w = __byte_perm(v[j].y, v[j].w, 0x7632);    // (x3, x7)
+					*reinterpret_cast<uint4 *>(xs + (size_t)row * p.xs_stride + unit * 16) = o;
+				}
+			}
 		}
 	}
 	__syncthreads();
 
 	// ---- main loop ---------------------------------------------------------------------
-	float acc[NSTREAM][4][4];
+	// acc[stream][column 0..3 of this lane][batch row 2*tig + {0,1} (+8 for the second block)]
+	float acc[NSTREAM][MB][4][2];
 #pragma unroll
 	for (int s = 0; s < NSTREAM; ++s)
 #pragma unroll
-		for (int c = 0; c < 4; ++c)
+		for (int b = 0; b < MB; ++b)
 #pragma unroll
-			for (int e = 0; e < 4; ++e) acc[s][c][e] = 0.f;
+			for (int c = 0; c < 4; ++c) acc[s][b][c][0] = acc[s][b][c][1] = 0.f;
 
-	if (warp_active) {
-		const unsigned char *xa_base = xs + (size_t)gid * p.xs_stride + (size_t)tig * 16;
-		const int zcol = (n0w >> 3) + (gid >> 1);
-		const int zsh = (gid & 1) * 16;
-		const int nz = p.N >> 3;
-		int consumed = 0;
-		for (int seg = seg0 + kw; seg < seg1; seg += KW) {
-			const int len = min(p.seg_steps, p.total_steps - seg * p.seg_steps);
-			const int g = (seg * p.seg_steps * 32) / p.groupsize;
+	bool failed = false;
+	if (nw > 0) {
+		const bool have_row0 = gid < p.M, have_row1 = gid + 8 < p.M;
+		// In step l of a chunk this lane works on packed row 2*tig + (l&1) + 8*(l>>1); the ring
+		// is written by TMA with the 128-byte swizzle (16-byte unit index ^= row & 7), which
+		// makes the quarter-warp reads below conflict-free.
+		// (With 32-row groups a step must stay inside one group, so there the rows are
+		// 4*l + tig; that variant has 2-way conflicts.)
+		constexpr bool LIN = (SPG_T == 1);
+		const int row_a = LIN ? tig : 2 * tig, row_b = LIN ? 4 + tig : 2 * tig + 1;    // steps 0/2 and 1/3
+		const unsigned char *xrow0 = xs + (size_t)gid * p.xs_stride + tig * (LIN ? 16 : 32);
+		const unsigned char *xrow1 = xs + (size_t)(gid + 8) * p.xs_stride + tig * (LIN ? 16 : 32);
+		const uint32_t ring_even = ring_w + row_a * 128 + ((gid ^ row_a) << 4);
+		const uint32_t ring_odd = ring_w + row_b * 128 + ((gid ^ row_b) << 4);
+		const int strip_col = wn * 32 + gid * 4;
+		int stage = 0;
+		uint32_t parity = 0;
 #pragma unroll
-			for (int s = 0; s < NSTREAM; ++s) {
-				const int32_t *qz = (NSTREAM == 2 && s) ? p.qz1 : p.qz0;
-				const __half *sc = (NSTREAM == 2 && s) ? p.sc1 : p.sc0;
-				const uint32_t zw = ((uint32_t)__ldg(qz + (size_t)g * nz + zcol)) >> zsh;
-				const uint4 sraw = __ldg(reinterpret_cast<const uint4 *>(sc + (size_t)g * p.N + n0w + 8 * tig));
-				uint32_t ZE[4], ZO[4];
+		for (int s = 0; s < NSTREAM; ++s) {
+			const __half *ze_s = s_ze + (size_t)s * p.strip_groups * SK_BN + strip_col;
+			const __half *sc_s = s_sc + (size_t)s * p.strip_groups * SK_BN + strip_col;
+			float gacc[MB][4][2];
+			uint32_t ZE[4], ZO[4];
+			auto load_zero = [&](int gi) {
+				const uint2 zr = *reinterpret_cast<const uint2 *>(ze_s + (size_t)gi * SK_BN);
+				ZE[0] = __byte_perm(zr.x, zr.x, 0x1010);
+				ZE[1] = __byte_perm(zr.x, zr.x, 0x3232);
+				ZE[2] = __byte_perm(zr.y, zr.y, 0x1010);
+				ZE[3] = __byte_perm(zr.y, zr.y, 0x3232);
 #pragma unroll
 				for (int c = 0; c < 4; ++c) {
-					const uint32_t zz = ((zw >> (4 * c)) & 0xFu) + 1u;
-					ZE[c] = (0x6400u + zz) * 0x00010001u;            // half2(1024 + zz)
-					ZO[c] = (0xD400u + (zz << 4)) * 0x00010001u;     // half2(-(64 + zz))
+					ZO[c] = h2_sub(0x63806380u, ZE[c]);      // 960 - (1024 + z) = -(64 + z)
+#pragma unroll
+					for (int b = 0; b < MB; ++b) gacc[b][c][0] = gacc[b][c][1] = 0.f;
 				}
-				float gacc[4][4];
+			};
+			auto flush = [&](int gi) {
+				const uint2 sr = *reinterpret_cast<const uint2 *>(sc_s + (size_t)gi * SK_BN);
+				const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.x));
+				const float2 s23 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.y));
+				const float sf[4] = {s01.x, s01.y, s23.x, s23.y};
 #pragma unroll
-				for (int c = 0; c < 4; ++c)
+				for (int b = 0; b < MB; ++b)
 #pragma unroll
-					for (int e = 0; e < 4; ++e) gacc[c][e] = 0.f;
-
-				const unsigned char *xa_ptr = xa_base + (size_t)((seg * p.seg_steps - step_lo) * 4) * 16;
-				for (int l = 0; l < len; ++l) {
-					cp_async_wait<D - 2>();
-					const uint4 q = ring[(consumed & (D - 1)) * 32];
-					issue();
-					++consumed;
-					const uint4 xa = *reinterpret_cast<const uint4 *>(xa_ptr);
-					uint4 xb = make_uint4(0u, 0u, 0u, 0u);
-					if (!M8) xb = *reinterpret_cast<const uint4 *>(xa_ptr + (size_t)8 * p.xs_stride);
-					xa_ptr += 64;
+					for (int c = 0; c < 4; ++c) {
+						acc[s][b][c][0] = fmaf(sf[c], gacc[b][c][0], acc[s][b][c][0]);
+						acc[s][b][c][1] = fmaf(sf[c], gacc[b][c][1], acc[s][b][c][1]);
+					}
+			};
+			for (int chunk = w_lo; chunk < w_hi; ++chunk) {
+				if (!mbar_wait_bounded(bar_w + 8 * stage, parity)) {
+					failed = true;
+					break;
+				}
+				const int step0 = chunk * 4;
+				if (SPG_T == 0) {
+					if (chunk == w_lo || (step0 % p.spg) == 0) load_zero(step0 / p.spg - g_lo);
+				}
+				const uint32_t st_off = stage * SK_CHUNK_BYTES;
+				const int xoff = (chunk - c_lo) * 256;
+#pragma unroll
+				for (int l = 0; l < 4; ++l) {
+					if (SPG_T != 0 && (l % (SPG_T ? SPG_T : 1)) == 0) load_zero((step0 + l) / (SPG_T ? SPG_T : 1) - g_lo);
+					uint4 q;
+					asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+								 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+								 : "r"(((l & 1) ? ring_odd : ring_even) + st_off + (l >> 1) * 1024));
+					const int xo = xoff + (LIN ? l * 64 : ((l & 1) + 8 * (l >> 1)) * 16);
+					uint4 xb0 = make_uint4(0u, 0u, 0u, 0u), xb1 = make_uint4(0u, 0u, 0u, 0u);
+					if (have_row0) xb0 = *reinterpret_cast<const uint4 *>(xrow0 + xo);
+					if (!M8 && have_row1) xb1 = *reinterpret_cast<const uint4 *>(xrow1 + xo);
 					const uint32_t qv[4] = {q.x, q.y, q.z, q.w};
+					uint32_t a04[4], a15[4], a26[4], a37[4];
 #pragma unroll
 					for (int c = 0; c < 4; ++c) {
 						const uint32_t w = qv[c], w8 = w >> 8;
-						const uint32_t b0 = h2_sub(lop3_and_or(w, MASK_LO, MAGIC_1024), ZE[c]);
-						const uint32_t b1 = h2_fma(lop3_and_or(w, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[c]);
-						const uint32_t b2 = h2_sub(lop3_and_or(w8, MASK_LO, MAGIC_1024), ZE[c]);
-						const uint32_t b3 = h2_fma(lop3_and_or(w8, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[c]);
-						mma16816(gacc[c], xa.x, xb.x, xa.y, xb.y, b0, b1);
-						mma16816(gacc[c], xa.z, xb.z, xa.w, xb.w, b2, b3);
+						a04[c] = h2_sub(lop3_and_or(w, MASK_LO, MAGIC_1024), ZE[c]);
+						a15[c] = h2_fma(lop3_and_or(w, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[c]);
+						a26[c] = h2_sub(lop3_and_or(w8, MASK_LO, MAGIC_1024), ZE[c]);
+						a37[c] = h2_fma(lop3_and_or(w8, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[c]);
 					}
-				}
-				// scale the segment's integer dot products: columns n0w + 8*tig + {c, 4+c}
-				const __half2 *sh = reinterpret_cast<const __half2 *>(&sraw);
-				const float2 s01 = __half22float2(sh[0]), s23 = __half22float2(sh[1]);
-				const float2 s45 = __half22float2(sh[2]), s67 = __half22float2(sh[3]);
-				const float slo[4] = {s01.x, s01.y, s23.x, s23.y};
-				const float shi[4] = {s45.x, s45.y, s67.x, s67.y};
+					// A rows (gid, gid+8) = lane columns (2pr, 2pr+1); B = x rows; D = (column, batch row)
 #pragma unroll
-				for (int c = 0; c < 4; ++c) {
-					acc[s][c][0] = fmaf(slo[c], gacc[c][0], acc[s][c][0]);
-					acc[s][c][1] = fmaf(shi[c], gacc[c][1], acc[s][c][1]);
-					acc[s][c][2] = fmaf(slo[c], gacc[c][2], acc[s][c][2]);
-					acc[s][c][3] = fmaf(shi[c], gacc[c][3], acc[s][c][3]);
+					for (int pr = 0; pr < 2; ++pr) {
+						float(&d0)[4] = *reinterpret_cast<float(*)[4]>(&gacc[0][2 * pr][0]);
+						mma16816(d0, a04[2 * pr], a04[2 * pr + 1], a15[2 * pr], a15[2 * pr + 1], xb0.x, xb0.y);
+						mma16816(d0, a26[2 * pr], a26[2 * pr + 1], a37[2 * pr], a37[2 * pr + 1], xb0.z, xb0.w);
+						if (!M8) {
+							float(&d1)[4] = *reinterpret_cast<float(*)[4]>(&gacc[MB - 1][2 * pr][0]);
+							mma16816(d1, a04[2 * pr], a04[2 * pr + 1], a15[2 * pr], a15[2 * pr + 1], xb1.x, xb1.y);
+							mma16816(d1, a26[2 * pr], a26[2 * pr + 1], a37[2 * pr], a37[2 * pr + 1], xb1.z, xb1.w);
+						}
+					}
+					if (SPG_T != 0 && ((l + 1) % (SPG_T ? SPG_T : 1)) == 0) flush((step0 + l) / (SPG_T ? SPG_T : 1) - g_lo);
+				}
+				if (SPG_T == 0) {
+					if (chunk + 1 == w_hi || ((step0 + 4) % p.spg) == 0) flush(step0 / p.spg - g_lo);
+				}
+				__syncwarp();
+				produce();
+				if (++stage == p.nstage) {
+					stage = 0;
+					parity ^= 1u;
 				}
 			}
+			if (failed) break;
 		}
 	}
-	cp_async_wait<0>();
+	if (failed && lane == 0) atomicExch(p.ws_ticket + SK_STATUS_SLOT, 1);          // a TMA load never completed
+	if (tid == 0 && (smem_u32(smem) & 1023u) != 0) atomicExch(p.ws_ticket + SK_STATUS_SLOT, 2);   // swizzle needs 1 KB alignment
 	__syncthreads();            // every warp is done with its ring: the region becomes `red`
 
 	// ---- reduce the KW warp-rows ---------------------------------------------------------
-	// red[kw][stream][row][128]
+	// red[kw][stream][row][128]; this lane holds columns wn*32 + 4*gid + 0..3 of rows 2*tig + {0,1} (+8)
 #pragma unroll
-	for (int s = 0; s < NSTREAM; ++s) {
-		float *r = red + ((size_t)(kw * NSTREAM + s) * ROWS + gid) * SK_BN + wn * 32 + 8 * tig;
-		*reinterpret_cast<float4 *>(r) = make_float4(acc[s][0][0], acc[s][1][0], acc[s][2][0], acc[s][3][0]);
-		*reinterpret_cast<float4 *>(r + 4) = make_float4(acc[s][0][1], acc[s][1][1], acc[s][2][1], acc[s][3][1]);
-		if (!M8) {
-			r += 8 * SK_BN;
-			*reinterpret_cast<float4 *>(r) = make_float4(acc[s][0][2], acc[s][1][2], acc[s][2][2], acc[s][3][2]);
-			*reinterpret_cast<float4 *>(r + 4) = make_float4(acc[s][0][3], acc[s][1][3], acc[s][2][3], acc[s][3][3]);
-		}
-	}
+	for (int s = 0; s < NSTREAM; ++s)
+#pragma unroll
+		for (int b = 0; b < MB; ++b)
+#pragma unroll
+			for (int h = 0; h < 2; ++h) {
+				float *r = red + ((size_t)(kw * NSTREAM + s) * ROWS + (b * 8 + 2 * tig + h)) * SK_BN + wn * 32 + gid * 4;
+				*reinterpret_cast<float4 *>(r) = make_float4(acc[s][b][0][h], acc[s][b][1][h], acc[s][b][2][h], acc[s][b][3][h]);
+			}
 	__syncthreads();
 
 	// tile sums land in red[0][stream][row][col] (slot of warp-row 0); with split-K they are

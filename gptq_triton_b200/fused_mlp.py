@@ -52,6 +52,8 @@ def gateup_silu(groupsize: int, a: torch.Tensor, gate_qweight, gate_scales, gate
 	M, K = x.shape
 	N = gate_qweight.shape[1]
 	c = torch.empty((M, N), device=a.device, dtype=torch.float16)
+	if M == 0:
+		return c.view(a.shape[:-1] + (N,))
 	ws = _lib.workspace(a.device, M, K, N)
 	rc = _lib.lib().gptq_gateup_silu(
 		_lib.ptr(x), _lib.ptr(gate_qweight), _lib.ptr(gate_qzeros), _lib.ptr(gate_scales),

@@ -80,6 +80,8 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 	M, K = x.shape
 	N = qweight.shape[1]
 	c = torch.empty((M, N), device=a.device, dtype=torch.float16)
+	if M == 0:
+		return c.view(a.shape[:-1] + (N,))
 	res = None
 	if residual is not None:
 		assert residual.is_contiguous() and residual.numel() == M * N
