@@ -36,6 +36,7 @@ _SIGNATURES = {
 _OPTIONAL = {
 	'gptq_debug_force_splitk': (None, [c_int]),
 	'gptq_debug_force_kw': (None, [c_int]),
+	'gptq_debug_allow_cluster': (None, [c_int]),
 }
 
 

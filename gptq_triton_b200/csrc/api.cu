@@ -15,6 +15,10 @@ thread_local int g_last_cuda_error = 0;
 
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
 static int g_force_kw = 2;
+static int g_allow_cluster = 0;   // cluster (DSMEM) split-K reduction: opt-in, see gptq_debug_allow_cluster
+#ifdef GPTQ_SK_TIMING
+static long long *g_dbg = nullptr;
+#endif
 
 static int sm_count() {
 	static int cached[64] = {0};
@@ -148,7 +152,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 		xs_stride = ks * 2 + 16;      // = 16 mod 128: rows gid, gid+1 read disjoint banks
 		xs_bytes = (p.M * xs_stride + 127) / 128 * 128;
 		strip_groups = (ks + p.groupsize - 1) / p.groupsize + 1;
-		const size_t strips = (size_t)nstream * strip_groups * SK_BN * 2 * 2;
+		const size_t strips = (size_t)nstream * strip_groups * SK_BN * 2 * 2 + (size_t)strip_groups * 16 * 8;
 		const size_t ring = (size_t)kwarps * 4 * nstage * SK_CHUNK_BYTES;
 		return ring + SK_BAR_BYTES + (size_t)xs_bytes + strips;
 	};
@@ -158,7 +162,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 		const int per_sm = 4 / kwarps;
 		const size_t cap = kwarps == 2 ? (size_t)113 * 1024 : (size_t)SK_SMEM_LIMIT - 2048;
 		const int slots = sms * per_sm;
-		for (int sk = 1; sk <= std::min(p.total_chunks, SK_MAX_SPLITK); ++sk) {
+		for (int sk = 1; sk <= std::min(p.total_chunks, g_allow_cluster ? 8 : SK_MAX_SPLITK); ++sk) {
 			int cps, eff, a, b, c;
 			int nstage = 4;
 			while (nstage > 2 && layout(sk, kwarps, nstage, cps, eff, a, b, c) > cap) --nstage;
@@ -195,6 +199,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 	smem = layout(best_sk, best_kw, best_stage, cps, eff, p.xs_stride, p.xs_bytes, p.strip_groups);
 	p.chunks_per_split = cps;
 	p.splitk = eff;
+	p.cluster = (g_allow_cluster && eff > 1 && eff <= 8) ? 1 : 0;
 	p.nstage = best_stage;
 	kw = best_kw;
 	grid = dim3(tiles, p.splitk, 1);
@@ -219,6 +224,21 @@ static int launch_skinny_inst(const CUtensorMap &tm0, const CUtensorMap &tm1, co
 	auto k = skinny_kernel<KW, NSTREAM, M8, SPG_T, EPI>;
 	static bool ready[64] = {false};
 	if (int rc = ensure_smem_attr(k, ready)) return rc;
+	if (p.cluster) {
+		cudaLaunchConfig_t cfg = {};
+		cfg.gridDim = grid;
+		cfg.blockDim = dim3(KW * 128, 1, 1);
+		cfg.dynamicSmemBytes = smem;
+		cfg.stream = stream;
+		cudaLaunchAttribute attr[1];
+		attr[0].id = cudaLaunchAttributeClusterDimension;
+		attr[0].val.clusterDim.x = 1;
+		attr[0].val.clusterDim.y = (unsigned)p.splitk;
+		attr[0].val.clusterDim.z = 1;
+		cfg.attrs = attr;
+		cfg.numAttrs = 1;
+		return cuda_status(cudaLaunchKernelEx(&cfg, k, tm0, tm1, p));
+	}
 	k<<<grid, KW * 128, smem, stream>>>(tm0, tm1, p);
 	return cuda_status(cudaGetLastError());
 }
@@ -233,6 +253,11 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	if (smem > (size_t)SK_SMEM_LIMIT - 1024) return GPTQ_ERR_UNSUPPORTED;
 	const size_t need = skinny_ws_bytes(p.M, p.N, NSTREAM);
 	if (workspace == nullptr || ws_bytes < need) return GPTQ_ERR_WORKSPACE;
+#ifdef GPTQ_SK_TIMING
+	p.dbg = g_dbg;
+	p.raw0 = qw0;
+	p.raw1 = qw1 ? qw1 : qw0;
+#endif
 	p.ws_ticket = reinterpret_cast<int *>(workspace);
 	p.ws_partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + SK_TICKET_BYTES);
 	alignas(64) CUtensorMap tm0, tm1;
@@ -298,6 +323,10 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 // Tuning / test hook: force the split-K factor of the decode kernel (0 restores the heuristic).
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
 void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
+void gptq_debug_allow_cluster(int on) { g_allow_cluster = on ? 1 : 0; }
+#ifdef GPTQ_SK_TIMING
+void gptq_debug_set_timing(long long *buf) { g_dbg = buf; }
+#endif
 
 size_t gptq_workspace_bytes(int M, int K, int N) {
 	(void)K;

@@ -11,13 +11,19 @@
 // bytes that hold its 4 columns (4*gid..4*gid+3) of packed row 4*step + tig.
 //
 // Math.  The 8 nibbles of a word are 8 K-values of one column.  Masking with 0x000F000F /
-// 0x00F000F0 yields the half2 pairs (k0,k4) (k1,k5) and, after >>8, (k2,k6) (k3,k7) as
-// 1024+q resp. 1024+16q; one sub / fma per pair turns them into the exact integers
-// q - zero.  They are the A operand of mma.sync.m16n8k16 (16 weight columns x 16 k); the
-// batch rows of x are the B operand, staged in shared memory in the matching k order
-// [0,4,1,5,2,6,3,7].  Integer dot products accumulate in fp32 per group and are scaled by
-// the group's fp32 scale when the group ends, so no weight is ever rounded to fp16: the
-// result equals an fp32-accumulated (q-z-1)*s reference up to fp32 summation order.
+// 0x00F000F0 (and the same after >>8) and OR-ing 0x6400 into each half gives the half2
+// pairs (k0,k4) (k2,k6) as 1024+q and (k1,k5) (k3,k7) as 1024+16q: five integer
+// instructions per 8 weights and nothing else.  These raw values are the A operand of
+// mma.sync.m16n8k16 (16 weight columns x 16 k); the batch rows of x are the B operand,
+// staged in shared memory in the matching k order [0,4,1,5,2,6,3,7] with the (k1,k5,k3,k7)
+// entries multiplied by 1/16.  Per group the MMA therefore accumulates, in fp32,
+//     D = sum x*q + 1024*(SXe + SXo'),   SXe = sum of the unscaled x, SXo' = sum of the x/16,
+// the scale is applied in fp32 when the group ends, and the zero point and the 1024-offsets
+// are removed once per CTA from the group sums of x:
+//     sum x*(q - z) = D - 1024*(SXe + SXo') - z*(SXe + 16*SXo').
+// No weight is ever rounded to fp16: the result equals an fp32-accumulated (q-z-1)*s
+// reference up to fp32 summation order (x/16 is exact unless |x| < 2^-10, where the
+// deviation is below 2^-21 absolute).
 //
 // Reduction.  Warp-rows reduce through shared memory; split-K CTAs write fp32 partials to
 // the workspace and take a ticket; the last CTA of a tile sums the partials in fixed order
@@ -25,6 +31,7 @@
 // with a scatter into Q / K / V (or the KV cache).
 #pragma once
 
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
@@ -54,6 +61,7 @@ struct SkinnyParams {
 	int xs_stride;         // bytes between rows of the staged x slice
 	int xs_bytes;          // M * xs_stride rounded up to 128
 	int strip_groups;      // capacity (groups) of the zero / scale strips per stream
+	int cluster;           // 1: the split-K CTAs of a tile form a thread-block cluster and reduce over DSMEM
 	float *ws_partial;
 	int *ws_ticket;
 	// EPI_PLAIN / EPI_SILU
@@ -68,7 +76,26 @@ struct SkinnyParams {
 	__half *q_out, *k_out, *v_out;
 	long long q_stride_m, kv_sb, kv_st, kv_sh, kv_sp;
 	int tokens_per_batch, hidden;
+#ifdef GPTQ_SK_TIMING
+	long long *dbg;        // [cta][8] phase timestamps (debug builds only)
+	const int32_t *raw0, *raw1;
+#endif
 };
+
+#ifdef GPTQ_SK_TIMING
+#define SK_STAMP(i)                                                                                         \
+	do {                                                                                                    \
+		if (p.dbg && threadIdx.x == 0) {                                                                    \
+			long long t_;                                                                                   \
+			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                          \
+			p.dbg[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = t_;                            \
+		}                                                                                                   \
+	} while (0)
+#else
+#define SK_STAMP(i) \
+	do {            \
+	} while (0)
+#endif
 
 // SPG_T: steps per group known at compile time (1 or 2), or 0 when a group spans whole chunks.
 template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI>
@@ -83,6 +110,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int wn = warp & 3, kw = warp >> 2, gid = lane >> 2, tig = lane & 3;
 	const int tile = blockIdx.x, split = blockIdx.y;
+	SK_STAMP(0);
 	const int n0 = tile * SK_BN, n0w = n0 + wn * 32;
 	const bool warp_active = n0w < p.N;
 
@@ -92,8 +120,9 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	const int ring_bytes = NWARP * p.nstage * SK_CHUNK_BYTES;
 	uint64_t *bars = reinterpret_cast<uint64_t *>(smem + ring_bytes);
 	unsigned char *xs = smem + ring_bytes + SK_BAR_BYTES;
-	__half *s_ze = reinterpret_cast<__half *>(xs + p.xs_bytes);                  // [stream][group][128] = 1024 + zero
-	__half *s_sc = s_ze + NSTREAM * p.strip_groups * SK_BN;                      // [stream][group][128]
+	__half *s_zz = reinterpret_cast<__half *>(xs + p.xs_bytes);                  // [stream][group][128] zero point (stored + 1)
+	__half *s_sc = s_zz + NSTREAM * p.strip_groups * SK_BN;                      // [stream][group][128] scale
+	float2 *s_cs = reinterpret_cast<float2 *>(s_sc + NSTREAM * p.strip_groups * SK_BN);   // [group][16 rows] (C, S) of x
 	float *red = reinterpret_cast<float *>(smem);
 	__shared__ int s_last;
 
@@ -122,9 +151,19 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		if (pr_j < nload) {
 			if (lane == 0) {
 				const uint32_t bar = bar_w + 8 * pr_stage;
-				fence_proxy_async();
 				mbar_arrive_expect_tx(bar, SK_CHUNK_BYTES);
+#ifdef GPTQ_SK_BULK1D
+				{
+					const unsigned char *src = reinterpret_cast<const unsigned char *>((NSTREAM == 2 && pr_stream) ? p.raw1 : p.raw0) +
+											   ((size_t)(tile * 4 + wn) * p.total_chunks + pr_chunk) * SK_CHUNK_BYTES;
+					asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+									 ring_w + pr_stage * SK_CHUNK_BYTES),
+								 "l"(src), "r"(SK_CHUNK_BYTES), "r"(bar)
+								 : "memory");
+				}
+#else
 				tma_load_2d(ring_w + pr_stage * SK_CHUNK_BYTES, (NSTREAM == 2 && pr_stream) ? &tm1 : &tm0, n0w, pr_chunk * 16, bar);
+#endif
 			}
 			++pr_j;
 			if (++pr_stage == p.nstage) pr_stage = 0;
@@ -134,89 +173,159 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			}
 		}
 	};
-	for (int s = 0; s < p.nstage; ++s) produce();
 
 	// ---- stage zero / scale strips and the x slice ---------------------------------------
+	// The first batch of these small loads is issued BEFORE the TMA prologue so that it does
+	// not queue behind 100+ KB of weight prefetch per SM; the values are stored afterwards.
 	const int g_lo = (c_lo * 128) / p.groupsize;
-	{
-		const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
+	const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
+	const int n_strip = NSTREAM * ng * 16;              // items of 8 columns
+	const int units = (c_hi - c_lo) * 16;               // 16-byte units per x row
+	const int n_x = p.M * units;
+	constexpr int SB = 2, XB = 4;
+	auto strip_load = [&](int base, uint32_t(&z)[SB], uint4(&sv)[SB]) {
 		const int nz = p.N >> 3;
-		for (int idx = tid; idx < NSTREAM * ng * 16; idx += NT) {
-			const int s = idx / (ng * 16), r = idx - s * (ng * 16);
-			const int gi = r >> 4, c = r & 15;              // 8 columns per item
-			if (n0 + c * 8 < p.N) {
-				const int32_t *qz = (NSTREAM == 2 && s) ? p.qz1 : p.qz0;
-				const __half *sc = (NSTREAM == 2 && s) ? p.sc1 : p.sc0;
-				const uint32_t z = (uint32_t)__ldg(qz + (size_t)(g_lo + gi) * nz + (n0 >> 3) + c);
-				const uint4 sv = __ldg(reinterpret_cast<const uint4 *>(sc + (size_t)(g_lo + gi) * p.N + n0 + c * 8));
-				uint4 ze;       // half(1024 + zero) = 0x6400 + (stored + 1), two per word
-				ze.x = 0x64016401u + ((z & 0xFu) | ((z & 0xF0u) << 12));
-				ze.y = 0x64016401u + (((z >> 8) & 0xFu) | (((z >> 8) & 0xF0u) << 12));
-				ze.z = 0x64016401u + (((z >> 16) & 0xFu) | (((z >> 16) & 0xF0u) << 12));
-				ze.w = 0x64016401u + (((z >> 24) & 0xFu) | (((z >> 24) & 0xF0u) << 12));
-				const size_t o = (size_t)(s * p.strip_groups + gi) * SK_BN + c * 8;
-				*reinterpret_cast<uint4 *>(s_ze + o) = ze;
-				*reinterpret_cast<uint4 *>(s_sc + o) = sv;
+#pragma unroll
+		for (int j = 0; j < SB; ++j) {
+			const int idx = base + j * NT;
+			if (idx < n_strip) {
+				const int s = idx / (ng * 16), r = idx - s * (ng * 16);
+				const int gi = r >> 4, c = r & 15;
+				if (n0 + c * 8 < p.N) {
+					const int32_t *qz = (NSTREAM == 2 && s) ? p.qz1 : p.qz0;
+					const __half *sc = (NSTREAM == 2 && s) ? p.sc1 : p.sc0;
+					z[j] = (uint32_t)__ldg(qz + (size_t)(g_lo + gi) * nz + (n0 >> 3) + c);
+					sv[j] = __ldg(reinterpret_cast<const uint4 *>(sc + (size_t)(g_lo + gi) * p.N + n0 + c * 8));
+				}
 			}
 		}
-		// x slice: [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7.  Loads of a batch of
-		// items are issued together so that their latencies overlap.
-		const int units = (c_hi - c_lo) * 16;
-		const int nitem = p.M * units;
-		constexpr int XB = 4;
-		for (int base = tid; base < nitem; base += NT * XB) {
-			uint4 v[XB];
-			if (p.perm == nullptr) {
+	};
+	auto strip_store = [&](int base, const uint32_t(&z)[SB], const uint4(&sv)[SB]) {
 #pragma unroll
-				for (int j = 0; j < XB; ++j) {
-					const int idx = base + j * NT;
-					if (idx < nitem) {
-						const int row = idx / units, unit = idx - row * units;
-						v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)row * p.ldx + (c_lo * 16 + unit) * 8));
-					}
+		for (int j = 0; j < SB; ++j) {
+			const int idx = base + j * NT;
+			if (idx < n_strip) {
+				const int s = idx / (ng * 16), r = idx - s * (ng * 16);
+				const int gi = r >> 4, c = r & 15;
+				if (n0 + c * 8 < p.N) {
+					// zero point (stored + 1) as fp16, two per word: (0x6401 + nibble) - 1024
+					const uint32_t zv = z[j];
+					uint4 ze;
+					ze.x = h2_sub(0x64016401u + ((zv & 0xFu) | ((zv & 0xF0u) << 12)), MAGIC_1024);
+					ze.y = h2_sub(0x64016401u + (((zv >> 8) & 0xFu) | (((zv >> 8) & 0xF0u) << 12)), MAGIC_1024);
+					ze.z = h2_sub(0x64016401u + (((zv >> 16) & 0xFu) | (((zv >> 16) & 0xF0u) << 12)), MAGIC_1024);
+					ze.w = h2_sub(0x64016401u + (((zv >> 24) & 0xFu) | (((zv >> 24) & 0xF0u) << 12)), MAGIC_1024);
+					const size_t o = (size_t)(s * p.strip_groups + gi) * SK_BN + c * 8;
+					*reinterpret_cast<uint4 *>(s_zz + o) = ze;
+					*reinterpret_cast<uint4 *>(s_sc + o) = sv[j];
 				}
-			} else {
-				int4 pa[XB], pb[XB];
+			}
+		}
+	};
+	auto x_load = [&](int base, uint4(&v)[XB]) {
+		if (p.perm == nullptr) {
 #pragma unroll
-				for (int j = 0; j < XB; ++j) {
-					const int idx = base + j * NT;
-					if (idx < nitem) {
-						const int unit = idx % units;
-						const int k = (c_lo * 16 + unit) * 8;
-						pa[j] = __ldg(reinterpret_cast<const int4 *>(p.perm + k));
-						pb[j] = __ldg(reinterpret_cast<const int4 *>(p.perm + k + 4));
-					}
+			for (int j = 0; j < XB; ++j) {
+				const int idx = base + j * NT;
+				if (idx < n_x) {
+					const int row = idx / units, unit = idx - row * units;
+					v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)row * p.ldx + (c_lo * 16 + unit) * 8));
 				}
+			}
+		} else {
+			int4 pa[XB], pb[XB];
 #pragma unroll
-				for (int j = 0; j < XB; ++j) {
-					const int idx = base + j * NT;
-					if (idx < nitem) {
-						const unsigned short *xr = reinterpret_cast<const unsigned short *>(p.x) + (size_t)(idx / units) * p.ldx;
-						const uint32_t h0 = __ldg(xr + pa[j].x), h1 = __ldg(xr + pa[j].y), h2 = __ldg(xr + pa[j].z), h3 = __ldg(xr + pa[j].w);
-						const uint32_t h4 = __ldg(xr + pb[j].x), h5 = __ldg(xr + pb[j].y), h6 = __ldg(xr + pb[j].z), h7 = __ldg(xr + pb[j].w);
-						v[j] = make_uint4(h0 | (h1 << 16), h2 | (h3 << 16), h4 | (h5 << 16), h6 | (h7 << 16));
-					}
+			for (int j = 0; j < XB; ++j) {
+				const int idx = base + j * NT;
+				if (idx < n_x) {
+					const int k = (c_lo * 16 + idx % units) * 8;
+					pa[j] = __ldg(reinterpret_cast<const int4 *>(p.perm + k));
+					pb[j] = __ldg(reinterpret_cast<const int4 *>(p.perm + k + 4));
 				}
 			}
 #pragma unroll
 			for (int j = 0; j < XB; ++j) {
 				const int idx = base + j * NT;
-				if (idx < nitem) {
-					const int row = idx / units, unit = idx - row * units;
-					uint4 o;
-					o.x = __byte_perm(v[j].x, v[j].z, 0x5410);    // (x0, x4)
-					o.y = __byte_perm(v[j].x, v[j].z, 0x7632);    // (x1, x5)
-					o.z = __byte_perm(v[j].y, v[j].w, 0x5410);    // (x2, x6)
-					o.w = __byte_perm(v[j].y, v[j].w, 0x7632);    // (x3, x7)
-					*reinterpret_cast<uint4 *>(xs + (size_t)row * p.xs_stride + unit * 16) = o;
+				if (idx < n_x) {
+					const unsigned short *xr = reinterpret_cast<const unsigned short *>(p.x) + (size_t)(idx / units) * p.ldx;
+					const uint32_t h0 = __ldg(xr + pa[j].x), h1 = __ldg(xr + pa[j].y), h2 = __ldg(xr + pa[j].z), h3 = __ldg(xr + pa[j].w);
+					const uint32_t h4 = __ldg(xr + pb[j].x), h5 = __ldg(xr + pb[j].y), h6 = __ldg(xr + pb[j].z), h7 = __ldg(xr + pb[j].w);
+					v[j] = make_uint4(h0 | (h1 << 16), h2 | (h3 << 16), h4 | (h5 << 16), h6 | (h7 << 16));
 				}
 			}
+		}
+	};
+	auto x_store = [&](int base, const uint4(&v)[XB]) {
+		// [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7, the (1,5) and (3,7) pairs divided by 16
+#pragma unroll
+		for (int j = 0; j < XB; ++j) {
+			const int idx = base + j * NT;
+			if (idx < n_x) {
+				const int row = idx / units, unit = idx - row * units;
+				uint4 o;
+				o.x = __byte_perm(v[j].x, v[j].z, 0x5410);                          // (x0, x4)
+				o.y = h2_mul(__byte_perm(v[j].x, v[j].z, 0x7632), 0x2C002C00u);    // (x1, x5) / 16
+				o.z = __byte_perm(v[j].y, v[j].w, 0x5410);                          // (x2, x6)
+				o.w = h2_mul(__byte_perm(v[j].y, v[j].w, 0x7632), 0x2C002C00u);    // (x3, x7) / 16
+				*reinterpret_cast<uint4 *>(xs + (size_t)row * p.xs_stride + unit * 16) = o;
+			}
+		}
+	};
+	{
+		uint32_t z0[SB];
+		uint4 sv0[SB], v0[XB];
+		strip_load(tid, z0, sv0);
+		x_load(tid, v0);
+		for (int s = 0; s < p.nstage; ++s) produce();        // weight prefetch: nstage chunks per warp
+		SK_STAMP(1);
+		strip_store(tid, z0, sv0);
+		x_store(tid, v0);
+		for (int base = tid + NT * SB; base < n_strip; base += NT * SB) {
+			strip_load(base, z0, sv0);
+			strip_store(base, z0, sv0);
+		}
+		for (int base = tid + NT * XB; base < n_x; base += NT * XB) {
+			x_load(base, v0);
+			x_store(base, v0);
 		}
 	}
 	__syncthreads();
 
+	// ---- group sums of the staged x: C = 1024*(SXe + SXo'), S = SXe + 16*SXo' per (group, row) ----
+	// four lanes per (group, row); fixed summation order
+	{
+		const int k_lo = c_lo * 128, k_hi = c_hi * 128;
+		const int sub = lane & 3;
+		const int total = ng * p.M;
+		for (int it0 = 0; it0 < total; it0 += NWARP * 8) {       // uniform trip count: shuffles below
+			const int item = it0 + warp * 8 + (lane >> 2);
+			const bool valid = item < total;
+			const int gi = valid ? item / p.M : 0, row = valid ? item - gi * p.M : 0;
+			const int ka = max((g_lo + gi) * p.groupsize, k_lo), kb = min((g_lo + gi + 1) * p.groupsize, k_hi);
+			float e = 0.f, o = 0.f;
+			if (valid) {
+				for (int u = (ka - k_lo) / 8 + sub; u < (kb - k_lo) / 8; u += 4) {
+					const uint4 v = *reinterpret_cast<const uint4 *>(xs + (size_t)row * p.xs_stride + u * 16);
+					const float2 a0 = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
+					const float2 a1 = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
+					const float2 a2 = __half22float2(*reinterpret_cast<const __half2 *>(&v.z));
+					const float2 a3 = __half22float2(*reinterpret_cast<const __half2 *>(&v.w));
+					e += (a0.x + a0.y) + (a2.x + a2.y);
+					o += (a1.x + a1.y) + (a3.x + a3.y);
+				}
+			}
+			e += __shfl_xor_sync(0xffffffffu, e, 1);
+			o += __shfl_xor_sync(0xffffffffu, o, 1);
+			e += __shfl_xor_sync(0xffffffffu, e, 2);
+			o += __shfl_xor_sync(0xffffffffu, o, 2);
+			if (valid && sub == 0) s_cs[gi * 16 + row] = make_float2(1024.f * (e + o), e + 16.f * o);
+		}
+	}
+	__syncthreads();
+	SK_STAMP(2);
+
 	// ---- main loop ---------------------------------------------------------------------
-	// acc[stream][column 0..3 of this lane][batch row 2*tig + {0,1} (+8 for the second block)]
+	// acc[stream][batch block][column 0..3 of this lane][batch row 2*tig + {0,1}]
 	float acc[NSTREAM][MB][4][2];
 #pragma unroll
 	for (int s = 0; s < NSTREAM; ++s)
@@ -226,13 +335,16 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			for (int c = 0; c < 4; ++c) acc[s][b][c][0] = acc[s][b][c][1] = 0.f;
 
 	bool failed = false;
+#ifdef GPTQ_SK_TIMING
+	long long wait_cycles = 0, math_cycles = 0, tail_cycles = 0;
+#endif
 	if (nw > 0) {
 		const bool have_row0 = gid < p.M, have_row1 = gid + 8 < p.M;
 		// In step l of a chunk this lane works on packed row 2*tig + (l&1) + 8*(l>>1); the ring
 		// is written by TMA with the 128-byte swizzle (16-byte unit index ^= row & 7), which
-		// makes the quarter-warp reads below conflict-free.
-		// (With 32-row groups a step must stay inside one group, so there the rows are
-		// 4*l + tig; that variant has 2-way conflicts.)
+		// makes the quarter-warp reads below conflict-free.  (With 32-row groups a step must
+		// stay inside one group, so there the rows are 4*l + tig; that variant has 2-way
+		// conflicts.)
 		constexpr bool LIN = (SPG_T == 1);
 		const int row_a = LIN ? tig : 2 * tig, row_b = LIN ? 4 + tig : 2 * tig + 1;    // steps 0/2 and 1/3
 		const unsigned char *xrow0 = xs + (size_t)gid * p.xs_stride + tig * (LIN ? 16 : 32);
@@ -242,26 +354,20 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		const int strip_col = wn * 32 + gid * 4;
 		int stage = 0;
 		uint32_t parity = 0;
+		bool first = true;
 #pragma unroll
 		for (int s = 0; s < NSTREAM; ++s) {
-			const __half *ze_s = s_ze + (size_t)s * p.strip_groups * SK_BN + strip_col;
 			const __half *sc_s = s_sc + (size_t)s * p.strip_groups * SK_BN + strip_col;
-			float gacc[MB][4][2];
-			uint32_t ZE[4], ZO[4];
-			auto load_zero = [&](int gi) {
-				const uint2 zr = *reinterpret_cast<const uint2 *>(ze_s + (size_t)gi * SK_BN);
-				ZE[0] = __byte_perm(zr.x, zr.x, 0x1010);
-				ZE[1] = __byte_perm(zr.x, zr.x, 0x3232);
-				ZE[2] = __byte_perm(zr.y, zr.y, 0x1010);
-				ZE[3] = __byte_perm(zr.y, zr.y, 0x3232);
+			// Two accumulator sets: while the MMAs of one group are still in the tensor pipe, the
+			// finished set of the previous group is scaled and added, so nothing waits for a drain.
+			float gA[MB][4][2], gB[MB][4][2];
+			auto clear = [&](float(&g)[MB][4][2]) {
 #pragma unroll
-				for (int c = 0; c < 4; ++c) {
-					ZO[c] = h2_sub(0x63806380u, ZE[c]);      // 960 - (1024 + z) = -(64 + z)
+				for (int b = 0; b < MB; ++b)
 #pragma unroll
-					for (int b = 0; b < MB; ++b) gacc[b][c][0] = gacc[b][c][1] = 0.f;
-				}
+					for (int c = 0; c < 4; ++c) g[b][c][0] = g[b][c][1] = 0.f;
 			};
-			auto flush = [&](int gi) {
+			auto flush = [&](float(&g)[MB][4][2], int gi) {
 				const uint2 sr = *reinterpret_cast<const uint2 *>(sc_s + (size_t)gi * SK_BN);
 				const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.x));
 				const float2 s23 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.y));
@@ -270,72 +376,139 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 				for (int b = 0; b < MB; ++b)
 #pragma unroll
 					for (int c = 0; c < 4; ++c) {
-						acc[s][b][c][0] = fmaf(sf[c], gacc[b][c][0], acc[s][b][c][0]);
-						acc[s][b][c][1] = fmaf(sf[c], gacc[b][c][1], acc[s][b][c][1]);
+						acc[s][b][c][0] = fmaf(sf[c], g[b][c][0], acc[s][b][c][0]);
+						acc[s][b][c][1] = fmaf(sf[c], g[b][c][1], acc[s][b][c][1]);
 					}
+				clear(g);
 			};
-			for (int chunk = w_lo; chunk < w_hi; ++chunk) {
-				if (!mbar_wait_bounded(bar_w + 8 * stage, parity)) {
-					failed = true;
-					break;
-				}
-				const int step0 = chunk * 4;
-				if (SPG_T == 0) {
-					if (chunk == w_lo || (step0 % p.spg) == 0) load_zero(step0 / p.spg - g_lo);
-				}
-				const uint32_t st_off = stage * SK_CHUNK_BYTES;
-				const int xoff = (chunk - c_lo) * 256;
+			// one step: 2 shared loads, 20 integer ops, 4 (or 8) MMAs
+			auto step = [&](float(&g)[MB][4][2], uint32_t ring_addr, const unsigned char *x0, const unsigned char *x1) {
+				uint4 q;
+				asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(ring_addr));
+				uint4 xb0 = make_uint4(0u, 0u, 0u, 0u), xb1 = make_uint4(0u, 0u, 0u, 0u);
+				if (have_row0) xb0 = *reinterpret_cast<const uint4 *>(x0);
+				if (!M8 && have_row1) xb1 = *reinterpret_cast<const uint4 *>(x1);
+#ifdef GPTQ_SK_NOMATH
+				g[0][0][0] += __uint_as_float((q.x ^ q.y ^ q.z ^ q.w ^ xb0.x ^ xb1.x) & 0x3fffffu);
+				return;
+#endif
+				const uint32_t qv[4] = {q.x, q.y, q.z, q.w};
+				uint32_t a04[4], a15[4], a26[4], a37[4];
 #pragma unroll
-				for (int l = 0; l < 4; ++l) {
-					if (SPG_T != 0 && (l % (SPG_T ? SPG_T : 1)) == 0) load_zero((step0 + l) / (SPG_T ? SPG_T : 1) - g_lo);
-					uint4 q;
-					asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-								 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-								 : "r"(((l & 1) ? ring_odd : ring_even) + st_off + (l >> 1) * 1024));
-					const int xo = xoff + (LIN ? l * 64 : ((l & 1) + 8 * (l >> 1)) * 16);
-					uint4 xb0 = make_uint4(0u, 0u, 0u, 0u), xb1 = make_uint4(0u, 0u, 0u, 0u);
-					if (have_row0) xb0 = *reinterpret_cast<const uint4 *>(xrow0 + xo);
-					if (!M8 && have_row1) xb1 = *reinterpret_cast<const uint4 *>(xrow1 + xo);
-					const uint32_t qv[4] = {q.x, q.y, q.z, q.w};
-					uint32_t a04[4], a15[4], a26[4], a37[4];
+				for (int c = 0; c < 4; ++c) {
+					const uint32_t w = qv[c], w8 = w >> 8;
+					a04[c] = lop3_and_or(w, MASK_LO, MAGIC_1024);       // 1024 + q      (k0, k4)
+					a15[c] = lop3_and_or(w, MASK_HI, MAGIC_1024);       // 1024 + 16 q   (k1, k5)
+					a26[c] = lop3_and_or(w8, MASK_LO, MAGIC_1024);      // 1024 + q      (k2, k6)
+					a37[c] = lop3_and_or(w8, MASK_HI, MAGIC_1024);      // 1024 + 16 q   (k3, k7)
+				}
+				// A rows (gid, gid+8) = lane columns (2pr, 2pr+1); B = x rows; D = (column, batch row)
 #pragma unroll
-					for (int c = 0; c < 4; ++c) {
-						const uint32_t w = qv[c], w8 = w >> 8;
-						a04[c] = h2_sub(lop3_and_or(w, MASK_LO, MAGIC_1024), ZE[c]);
-						a15[c] = h2_fma(lop3_and_or(w, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[c]);
-						a26[c] = h2_sub(lop3_and_or(w8, MASK_LO, MAGIC_1024), ZE[c]);
-						a37[c] = h2_fma(lop3_and_or(w8, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[c]);
+				for (int pr = 0; pr < 2; ++pr) {
+					float(&d0)[4] = *reinterpret_cast<float(*)[4]>(&g[0][2 * pr][0]);
+					mma16816(d0, a04[2 * pr], a04[2 * pr + 1], a15[2 * pr], a15[2 * pr + 1], xb0.x, xb0.y);
+					mma16816(d0, a26[2 * pr], a26[2 * pr + 1], a37[2 * pr], a37[2 * pr + 1], xb0.z, xb0.w);
+					if (!M8) {
+						float(&d1)[4] = *reinterpret_cast<float(*)[4]>(&g[MB - 1][2 * pr][0]);
+						mma16816(d1, a04[2 * pr], a04[2 * pr + 1], a15[2 * pr], a15[2 * pr + 1], xb1.x, xb1.y);
+						mma16816(d1, a26[2 * pr], a26[2 * pr + 1], a37[2 * pr], a37[2 * pr + 1], xb1.z, xb1.w);
 					}
-					// A rows (gid, gid+8) = lane columns (2pr, 2pr+1); B = x rows; D = (column, batch row)
-#pragma unroll
-					for (int pr = 0; pr < 2; ++pr) {
-						float(&d0)[4] = *reinterpret_cast<float(*)[4]>(&gacc[0][2 * pr][0]);
-						mma16816(d0, a04[2 * pr], a04[2 * pr + 1], a15[2 * pr], a15[2 * pr + 1], xb0.x, xb0.y);
-						mma16816(d0, a26[2 * pr], a26[2 * pr + 1], a37[2 * pr], a37[2 * pr + 1], xb0.z, xb0.w);
-						if (!M8) {
-							float(&d1)[4] = *reinterpret_cast<float(*)[4]>(&gacc[MB - 1][2 * pr][0]);
-							mma16816(d1, a04[2 * pr], a04[2 * pr + 1], a15[2 * pr], a15[2 * pr + 1], xb1.x, xb1.y);
-							mma16816(d1, a26[2 * pr], a26[2 * pr + 1], a37[2 * pr], a37[2 * pr + 1], xb1.z, xb1.w);
-						}
-					}
-					if (SPG_T != 0 && ((l + 1) % (SPG_T ? SPG_T : 1)) == 0) flush((step0 + l) / (SPG_T ? SPG_T : 1) - g_lo);
 				}
-				if (SPG_T == 0) {
-					if (chunk + 1 == w_hi || ((step0 + 4) % p.spg) == 0) flush(step0 / p.spg - g_lo);
-				}
+			};
+			// begin(): refill the stage drained one iteration ago, then wait for this chunk's data
+			auto begin = [&]() -> bool {
+				if (!first) produce();
+				first = false;
+#ifdef GPTQ_SK_TIMING
+				const long long tw0 = clock64();
+#endif
+				const bool ok = mbar_wait_bounded(bar_w + 8 * stage, parity);
+#ifdef GPTQ_SK_TIMING
+				wait_cycles += clock64() - tw0;
+#endif
+				return ok;
+			};
+			auto end = [&]() {
 				__syncwarp();
-				produce();
 				if (++stage == p.nstage) {
 					stage = 0;
 					parity ^= 1u;
+				}
+			};
+			auto xoff_of = [&](int chunk, int l) { return (chunk - c_lo) * 256 + (LIN ? l * 64 : ((l & 1) + 8 * (l >> 1)) * 16); };
+			auto ring_of = [&](int l) { return ((l & 1) ? ring_odd : ring_even) + stage * SK_CHUNK_BYTES + (l >> 1) * 1024; };
+			clear(gA);
+			clear(gB);
+
+			if (SPG_T == 0 && p.spg == 4) {
+				// one group per chunk: chunks alternate between the two accumulator sets
+				int chunk = w_lo;
+				for (; chunk + 1 < w_hi; chunk += 2) {
+					if (!begin()) { failed = true; break; }
+#pragma unroll
+					for (int l = 0; l < 4; ++l) step(gA, ring_of(l), xrow0 + xoff_of(chunk, l), xrow1 + xoff_of(chunk, l));
+					if (chunk > w_lo) flush(gB, chunk - 1 - g_lo);
+					end();
+					if (!begin()) { failed = true; break; }
+#pragma unroll
+					for (int l = 0; l < 4; ++l) step(gB, ring_of(l), xrow0 + xoff_of(chunk + 1, l), xrow1 + xoff_of(chunk + 1, l));
+					flush(gA, chunk - g_lo);
+					end();
+				}
+				if (!failed && chunk < w_hi) {          // odd chunk count: one more on set A
+					if (begin()) {
+#pragma unroll
+						for (int l = 0; l < 4; ++l) step(gA, ring_of(l), xrow0 + xoff_of(chunk, l), xrow1 + xoff_of(chunk, l));
+						if (chunk > w_lo) flush(gB, chunk - 1 - g_lo);
+						end();
+						flush(gA, chunk - g_lo);
+					} else {
+						failed = true;
+					}
+				} else if (!failed && w_hi > w_lo) {
+					flush(gB, w_hi - 1 - g_lo);
+				}
+			} else if (SPG_T == 0) {
+				// groups span several chunks: flushes are rare, a single accumulator set is enough
+				int gi = (w_lo * 4) / p.spg - g_lo;
+				int left = p.spg - (w_lo * 4) % p.spg;          // steps left in the current group
+				for (int chunk = w_lo; chunk < w_hi; ++chunk) {
+					if (!begin()) { failed = true; break; }
+#pragma unroll
+					for (int l = 0; l < 4; ++l) step(gA, ring_of(l), xrow0 + xoff_of(chunk, l), xrow1 + xoff_of(chunk, l));
+					left -= 4;
+					if (left == 0 || chunk + 1 == w_hi) {
+						flush(gA, gi);
+						if (left == 0) {
+							++gi;
+							left = p.spg;
+						}
+					}
+					end();
+				}
+			} else {
+				// 32- or 64-row groups: SPG_T steps per group, flushes at compile-time positions
+				constexpr int SP = SPG_T ? SPG_T : 1;
+				for (int chunk = w_lo; chunk < w_hi; ++chunk) {
+					if (!begin()) { failed = true; break; }
+#pragma unroll
+					for (int l = 0; l < 4; ++l) {
+						step(gA, ring_of(l), xrow0 + xoff_of(chunk, l), xrow1 + xoff_of(chunk, l));
+						if ((l + 1) % SP == 0) flush(gA, (chunk * 4 + l) / SP - g_lo);
+					}
+					end();
 				}
 			}
 			if (failed) break;
 		}
 	}
+#ifdef GPTQ_SK_TIMING
+	if (p.dbg && tid == 0) p.dbg[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + 7] = wait_cycles | (math_cycles << 20) | (tail_cycles << 40);
+#endif
 	if (failed && lane == 0) atomicExch(p.ws_ticket + SK_STATUS_SLOT, 1);          // a TMA load never completed
 	if (tid == 0 && (smem_u32(smem) & 1023u) != 0) atomicExch(p.ws_ticket + SK_STATUS_SLOT, 2);   // swizzle needs 1 KB alignment
 	__syncthreads();            // every warp is done with its ring: the region becomes `red`
+	SK_STAMP(3);
 
 	// ---- reduce the KW warp-rows ---------------------------------------------------------
 	// red[kw][stream][row][128]; this lane holds columns wn*32 + 4*gid + 0..3 of rows 2*tig + {0,1} (+8)
@@ -360,12 +533,24 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		float v = 0.f;
 #pragma unroll
 		for (int k = 0; k < KW; ++k) v += red[((size_t)(k * NSTREAM + s) * ROWS + row) * SK_BN + col];
-		if (p.splitk == 1)
+		{
+			// remove the 1024-offsets and the zero points of this CTA's K-slice
+			const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
+			const __half *zz = s_zz + (size_t)s * p.strip_groups * SK_BN + col;
+			const __half *sc = s_sc + (size_t)s * p.strip_groups * SK_BN + col;
+			float corr = 0.f;
+			for (int gi = 0; gi < ng; ++gi) {
+				const float2 cs = s_cs[gi * 16 + row];
+				corr = fmaf(__half2float(sc[(size_t)gi * SK_BN]), fmaf(__half2float(zz[(size_t)gi * SK_BN]), cs.y, cs.x), corr);
+			}
+			v -= corr;
+		}
+		if (p.splitk == 1 || p.cluster)
 			red[((size_t)s * ROWS + row) * SK_BN + col] = v;
 		else
 			__stcg(wsp + e, v);
 	}
-	if (p.splitk > 1) {
+	if (p.splitk > 1 && !p.cluster) {
 		__threadfence();
 		__syncthreads();
 		if (tid == 0) {
@@ -375,27 +560,72 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			s_last = last;
 		}
 		__syncthreads();
+		SK_STAMP(4);
 		if (!s_last) return;
 		__threadfence();
 		const float *wt = p.ws_partial + (size_t)tile * p.splitk * nelem;
 		for (int e = tid; e < nelem; e += NT) {
 			const int s = e / (p.M * SK_BN), rc = e - s * (p.M * SK_BN);
 			const int row = rc >> 7, col = rc & 127;
+			float part[16];       // split-K <= 16; loads first, then a fixed-order sum
+#pragma unroll
+			for (int k = 0; k < 16; ++k) part[k] = (k < p.splitk) ? __ldcg(wt + (size_t)k * nelem + e) : 0.f;
 			float v = 0.f;
-			for (int k = 0; k < p.splitk; ++k) v += __ldcg(wt + (size_t)k * nelem + e);
+#pragma unroll
+			for (int k = 0; k < 16; ++k) v += part[k];
 			red[((size_t)s * ROWS + row) * SK_BN + col] = v;
 		}
 	}
 	__syncthreads();
 
+	// ---- cluster mode: every CTA of the cluster finishes a share of the tile.  It sums the
+	// partials of all ranks over distributed shared memory, in rank order (deterministic).
+	const int epi_n = (EPI == EPI_ROPE) ? p.M * 64 : p.M * SK_BN;
+	int e_lo = 0, e_hi = epi_n;
+	const float *fin = red;
+	if (p.cluster) {
+		namespace cg = cooperative_groups;
+		cg::cluster_group cluster = cg::this_cluster();
+		cluster.sync();
+		SK_STAMP(4);
+		const int per = (((epi_n + p.splitk - 1) / p.splitk) + 31) & ~31;
+		e_lo = min(split * per, epi_n);
+		e_hi = min(e_lo + per, epi_n);
+		float *finw = red + (size_t)NSTREAM * ROWS * SK_BN;       // slot of warp-row 1: free by now
+		for (int e = e_lo + tid; e < e_hi; e += NT) {
+			int idx[2];
+			int cnt;
+			if (EPI == EPI_ROPE) {
+				idx[0] = (e >> 6) * SK_BN + (e & 63);
+				idx[1] = idx[0] + 64;
+				cnt = 2;
+			} else {
+				idx[0] = (e >> 7) * SK_BN + (e & 127);
+				idx[1] = idx[0] + ROWS * SK_BN;                       // the second stream (SiLU epilogue)
+				cnt = NSTREAM;
+			}
+			for (int j = 0; j < cnt; ++j) {
+				float part[8];
+#pragma unroll
+				for (int r = 0; r < 8; ++r) part[r] = (r < p.splitk) ? *(cluster.map_shared_rank(red, r) + idx[j]) : 0.f;
+				float v = 0.f;
+#pragma unroll
+				for (int r = 0; r < 8; ++r) v += part[r];
+				finw[idx[j]] = v;
+			}
+		}
+		fin = finw;
+	}
+
+	SK_STAMP(5);
 	// ---- epilogue from shared memory ---------------------------------------------------------
 	if (EPI == EPI_PLAIN || EPI == EPI_SILU) {
-		for (int e = tid; e < p.M * SK_BN; e += NT) {
+		for (int e = e_lo + tid; e < e_hi; e += NT) {
 			const int row = e >> 7, col = e & 127, n = n0 + col;
 			if (n >= p.N) continue;
-			float v = red[(size_t)row * SK_BN + col];
+			float v = fin[(size_t)row * SK_BN + col];
 			if (EPI == EPI_SILU) {
-				v = silu_f32(v) * red[((size_t)ROWS + row) * SK_BN + col];
+				v = silu_f32(v) * fin[((size_t)ROWS + row) * SK_BN + col];
 			} else {
 				if (p.bias) v += __half2float(p.bias[n]);
 				if (p.residual) v += __half2float(p.residual[(size_t)row * p.ldr + n]);
@@ -405,9 +635,9 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	} else {
 		// rotary: the tile is exactly one head (head_dim == 128) of section Q, K or V
 		const int section = n0 / p.hidden, head = (n0 - section * p.hidden) >> 7;
-		for (int e = tid; e < p.M * 64; e += NT) {
+		for (int e = e_lo + tid; e < e_hi; e += NT) {
 			const int row = e >> 6, d = e & 63;
-			const float a = red[(size_t)row * SK_BN + d], b = red[(size_t)row * SK_BN + d + 64];
+			const float a = fin[(size_t)row * SK_BN + d], b = fin[(size_t)row * SK_BN + d + 64];
 			const int pos = p.pos[row];
 			float o1 = a, o2 = b;
 			if (section < 2) {
@@ -427,6 +657,8 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			dst[d + 64] = __float2half_rn(o2);
 		}
 	}
+	if (p.cluster) cooperative_groups::this_cluster().sync();     // peers may still be reading this CTA's partials
+	SK_STAMP(6);
 }
 
 // ---- general kernel: any M, any g_idx, N % 8 == 0, K % 8 == 0 ---------------------------
