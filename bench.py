@@ -1,0 +1,303 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: greedy decode of a LLaMA-7B-architecture model with 4-bit g128
+GPTQ weights (synthetic, random-init) at batch 1 after a 2048-token prompt.
+
+One "step" is one decode step (one token): 32 x (fused QKV+rotary, o_proj, fused gate/up,
+down_proj quantised matmuls + attention over the KV cache) + fp16 lm_head + argmax.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line (rank 0).  `value` is device-timed (CUDA-graph replays, inputs resident
+in HBM); `e2e` goes through the public DecodeEngine.step() API with the token fed from pinned
+host memory and the result read back every step.  `roofline` is the dominant kernel (fused
+gate/up decode kernel) timed live with CUDA events while rotating over all 32 layers' weights
+(1.4 GB, larger than L2).  `--impl reference` times the CPU dequantise-then-matmul oracle on the
+host cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = 'decode tokens/s (7B-arch, 4-bit g128, 2k ctx)'
+UNIT = 'tokens/s'
+WORKLOAD = 'llama7b-arch 4-bit g128 greedy decode, batch 1, 2048-token prompt'
+PROMPT = 2048
+GROUPSIZE = 128
+
+
+def measured_peaks():
+	p = ROOT / 'MEASURED_PEAKS.json'
+	if p.exists():
+		d = json.load(open(p))
+		return float(d['hbm_gbs']), 'measured'
+	return 6650.0, 'fallback'
+
+
+def quantised_bytes(K, N, g=GROUPSIZE):
+	return K * N // 2 + (K // g) * N * 2 + (K // g) * N // 2
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle's dequantise-then-matmul path on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_sample_seconds(reps: int):
+	"""Times one 4096x4096 g128 projection at M=1 through the CPU oracle (unpack + dequantise to
+	fp16 + torch.matmul).  Returns (median seconds, cores)."""
+	import torch
+	from gptq_triton_b200 import synth
+	from oracle import gptq_oracle as O
+	cores = os.cpu_count() or 1
+	torch.set_num_threads(cores)
+	t = synth.quant_tensors(4096, 4096, GROUPSIZE, seed=0)
+	x = synth.activations((1, 4096), seed=1)
+	times = []
+	for _ in range(reps):
+		t0 = time.perf_counter()
+		O.qmatmul_r16(x, t['qweight'], t['qzeros'], t['scales'], GROUPSIZE)
+		times.append(time.perf_counter() - t0)
+	times.sort()
+	return times[len(times) // 2], cores
+
+
+def decode_step_weight_elems():
+	h, i, L = 4096, 11008, 32
+	return L * (3 * h * h + h * h + 2 * h * i + i * h)
+
+
+def reference_arm(args):
+	rank = int(os.environ.get('RANK', '0'))
+	if rank != 0:
+		return
+	reps = max(1, args.steps)
+	for _ in range(max(0, min(args.warmup, 2))):
+		cpu_sample_seconds(1)
+	sec, cores = cpu_sample_seconds(reps)
+	scale = decode_step_weight_elems() / (4096 * 4096)
+	tok_s = 1.0 / (sec * scale)
+	sample = 'one 4096x4096 g128 projection at M=1 (1/%.0f of the quantised weights of a decode step), median of %d' % (scale, reps)
+	line = {
+		'impl': 'reference', 'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
+		'ms_per_step': 1e3 / tok_s, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f16',
+		'data': 'synthetic', 'config': {'workload': WORKLOAD, 'path': 'CPU oracle: unpack + dequantise + torch.matmul fp16'},
+		'cpu_baseline': {'value': tok_s, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': sample},
+		'e2e': {'value': tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+	}
+	print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+	Q = 'index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap'
+
+	def __init__(self, gpu_index: int):
+		self.idx = gpu_index
+		self.proc = None
+		self.lines = []
+
+	def start(self):
+		try:
+			self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.idx), '--query-gpu=' + self.Q, '--format=csv,noheader,nounits', '-lms', '100'],
+										 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+			self.thread = threading.Thread(target=self._read, daemon=True)
+			self.thread.start()
+		except Exception:
+			self.proc = None
+
+	def _read(self):
+		for line in self.proc.stdout:
+			self.lines.append(line.strip())
+
+	def stop(self):
+		if self.proc is None:
+			return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+		self.proc.terminate()
+		try:
+			self.proc.wait(timeout=2)
+		except Exception:
+			self.proc.kill()
+		sm, mx, reasons = [], None, set()
+		names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+		for l in self.lines:
+			f = [x.strip() for x in l.split(',')]
+			if len(f) < 9:
+				continue
+			try:
+				sm.append(float(f[1])); mx = float(f[2])
+			except ValueError:
+				continue
+			for n, v in zip(names, f[5:9]):
+				if v.lower().startswith('active'):
+					reasons.add(n)
+		sm.sort()
+		return {'sm_mhz': sm[len(sm) // 2] if sm else None, 'sm_max_mhz': mx, 'samples': len(sm), 'reasons': sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def gpu_arm(args):
+	import torch
+	import torch.distributed as dist
+
+	rank = int(os.environ.get('RANK', '0'))
+	local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+	world = int(os.environ.get('WORLD_SIZE', '1'))
+	if not torch.cuda.is_available():
+		raise SystemExit('bench.py needs a CUDA device (B200); there is no CPU path for the product kernels')
+	torch.cuda.set_device(local_rank)
+	dev = torch.device('cuda', local_rank)
+	if world > 1:
+		dist.init_process_group('nccl', device_id=dev)
+
+	import gptq_triton_b200 as G
+	from gptq_triton_b200 import _lib
+	from gptq_triton_b200.llama import LlamaConfig
+
+	cfg = LlamaConfig.llama_7b()
+	if args.layers:
+		cfg.num_hidden_layers = args.layers            # debugging aid only; the default is the full model
+	model = G.synthetic_quantized_llama(cfg, groupsize=GROUPSIZE, seed=1234 + rank, device=dev)
+	max_seq = PROMPT + args.warmup + 2 * args.steps + 16
+	engine = G.DecodeEngine(model, batch=1, max_seq=max_seq, use_graph=True)
+	gen = torch.Generator().manual_seed(99 + rank)
+	prompt = torch.randint(0, cfg.vocab_size, (1, PROMPT), generator=gen).to(dev)
+	engine.prefill(prompt)
+	torch.cuda.synchronize()
+
+	def barrier():
+		torch.cuda.synchronize()
+		if world > 1:
+			dist.barrier()
+		torch.cuda.synchronize()
+
+	# ---- device-timed: K graph replays -------------------------------------------------------
+	for _ in range(args.warmup):
+		engine.step()
+	sampler = ClockSampler(local_rank)
+	barrier()
+	if rank == 0:
+		sampler.start()
+	e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+	e0.record()
+	for _ in range(args.steps):
+		engine.step()
+	e1.record()
+	barrier()
+	ms = e0.elapsed_time(e1)
+	clocks = sampler.stop() if rank == 0 else None
+	t = torch.tensor([ms], device=dev)
+	if world > 1:
+		dist.all_reduce(t, op=dist.ReduceOp.MAX)
+	ms = float(t.item())
+	tok_s = world * args.steps / (ms / 1e3)
+
+	# ---- end to end through DecodeEngine.step(): token in from pinned host memory, token out ----
+	host_tok = torch.zeros((1, 1), dtype=torch.int64).pin_memory()
+	host_out = torch.zeros((1, 1), dtype=torch.int64).pin_memory()
+	host_tok.copy_(engine.tok.cpu())
+	barrier()
+	t0 = time.perf_counter()
+	for _ in range(args.steps):
+		engine.tok.copy_(host_tok, non_blocking=True)       # H2D: the token chosen on the host side
+		out = engine.step()
+		host_out.copy_(out, non_blocking=True)              # D2H: the next token
+		torch.cuda.current_stream().synchronize()
+		host_tok.copy_(host_out)
+	e2e_s = time.perf_counter() - t0
+	t = torch.tensor([e2e_s], device=dev)
+	if world > 1:
+		dist.all_reduce(t, op=dist.ReduceOp.MAX)
+	e2e_tok_s = world * args.steps / float(t.item())
+
+	# ---- roofline of the dominant kernel: fused gate/up decode kernel, live, rotating weights ----
+	roof = None
+	status = None
+	if rank == 0:
+		layers = model.model.layers
+		x = torch.randn((1, 1, cfg.hidden_size), device=dev, dtype=torch.float16)
+		for l in layers[:4]:
+			l.mlp.intermediate(x)
+		torch.cuda.synchronize()
+		reps = max(1, 256 // len(layers))
+		k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+		g = torch.cuda.CUDAGraph()
+		s = torch.cuda.Stream()
+		s.wait_stream(torch.cuda.current_stream())
+		with torch.cuda.stream(s):
+			for l in layers:
+				l.mlp.intermediate(x)
+			s.synchronize()
+			with torch.cuda.graph(g, stream=s):
+				for l in layers:
+					l.mlp.intermediate(x)
+			g.replay()
+			s.synchronize()
+			k0.record(s)
+			for _ in range(reps):
+				g.replay()
+			k1.record(s)
+			s.synchronize()
+		us = k0.elapsed_time(k1) * 1e3 / (reps * len(layers))
+		K, N = cfg.hidden_size, cfg.intermediate_size
+		alg = 2 * quantised_bytes(K, N) + 2 * K + 2 * N           # two weight streams + x + y at M=1
+		peak, which = measured_peaks()
+		ach = alg / us / 1e3
+		roof = {'bound': 'hbm', 'kernel': 'skinny_kernel<gate/up, SiLU epilogue> M=1 K=4096 N=11008', 'achieved': ach, 'peak': peak, 'unit': 'GB/s',
+				'frac': ach / peak, 'peak_source': which, 'us_per_launch': us, 'algorithmic_bytes': alg, 'traffic': 46.9e6}
+		status = _lib.kernel_status(dev)
+
+	# ---- CPU baseline (rank 0, N=1 only) -----------------------------------------------------------
+	cpu = None
+	if rank == 0 and world == 1 and not args.no_cpu_baseline:
+		sec, cores = cpu_sample_seconds(5)
+		scale = decode_step_weight_elems() / (4096 * 4096)
+		cpu = {'value': 1.0 / (sec * scale), 'unit': UNIT, 'cores': cores, 'kind': 'port',
+			   'sample': 'one 4096x4096 g128 projection at M=1 through the CPU oracle (1/%.0f of the quantised weights of a decode step), median of 5' % scale}
+
+	if rank == 0:
+		launches_per_step = 4 * cfg.num_hidden_layers
+		line = {
+			'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+			'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f16',
+			'data': 'synthetic',
+			'config': {'workload': WORKLOAD, 'layers': cfg.num_hidden_layers, 'hidden': cfg.hidden_size, 'groupsize': GROUPSIZE,
+					   'parallelism': 'replicas x%d' % world if world > 1 else 'single GPU',
+					   'l2': 'inputs larger than L2: 3.6 GB of weights + KV cache are streamed every step'},
+			'e2e': {'value': e2e_tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 8, 'd2h_bytes_per_step': 8},
+			'gpu_launches': launches_per_step * args.steps,
+			'roofline': roof, 'cpu_baseline': cpu, 'clocks': clocks, 'kernel_status': status,
+		}
+		print(json.dumps(line))
+	if world > 1:
+		dist.destroy_process_group()
+
+
+def main():
+	ap = argparse.ArgumentParser()
+	ap.add_argument('--gpus', type=int, default=1)
+	ap.add_argument('--steps', type=int, default=64)
+	ap.add_argument('--warmup', type=int, default=8)
+	ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+	ap.add_argument('--layers', type=int, default=0, help='debug: fewer decoder layers')
+	ap.add_argument('--no-cpu-baseline', action='store_true')
+	args = ap.parse_args()
+	if args.impl == 'reference':
+		reference_arm(args)
+	else:
+		gpu_arm(args)
+
+
+if __name__ == '__main__':
+	main()

@@ -112,3 +112,13 @@ def workspace(device: torch.device, M: int, K: int, N: int) -> torch.Tensor:
 
 
 _retired = []
+
+
+def kernel_status(device=None) -> int:
+	"""OR of the status words that the decode kernels keep in their workspaces (0 = healthy;
+	1 = a TMA load never completed within the bounded wait; 2 = shared memory misaligned)."""
+	st = 0
+	for (dev, _), ws in _workspaces.items():
+		if device is None or dev == (device.index if isinstance(device, torch.device) else device):
+			st |= int(ws[16384 - 4:16384].view(torch.int32).item())
+	return st

@@ -57,6 +57,24 @@ def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin,
 		assert k.is_contiguous() and v.is_contiguous() and k.shape == v.shape and k.shape[0] >= b and k.shape[1] == n_heads and k.shape[3] == head_dim
 		S = k.shape[2]
 		sb, st, sh, sp = n_heads * S * head_dim, 0, S * head_dim, head_dim
+	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available
+	if M > DECODE_MAX_M and not prefill_kernel_available(M, K, 3 * hidden, groupsize):
+		y = dequant_matmul(a.view(M, K), groupsize, qweight, scales, qzeros, None, perm).float().view(b, t, 3, n_heads, head_dim)
+		c = cos[pos.long()].float().view(b, t, 1, head_dim)
+		s = sin[pos.long()].float().view(b, t, 1, head_dim)
+		rot = lambda z: torch.cat([-z[..., head_dim // 2:], z[..., :head_dim // 2]], dim=-1)
+		qf, kf, vf = y[:, :, 0], y[:, :, 1], y[:, :, 2]
+		qf = qf * c + rot(qf) * s
+		kf = kf * c + rot(kf) * s
+		q.copy_(qf.half())
+		if kv_cache is None:
+			k.copy_(kf.half().transpose(1, 2))
+			v.copy_(vf.half().transpose(1, 2))
+		else:
+			bi = torch.arange(b, device=a.device).view(b, 1).expand(b, t)
+			k[bi, :, pos.view(b, t).long()] = kf.half()
+			v[bi, :, pos.view(b, t).long()] = vf.half()
+		return q.transpose(1, 2), k, v
 	ws = _lib.workspace(a.device, M, K, 3 * hidden)
 	rc = _lib.lib().gptq_qkv_rope(
 		_lib.ptr(a), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), None, _lib.ptr(perm),

@@ -54,6 +54,12 @@ def gateup_silu(groupsize: int, a: torch.Tensor, gate_qweight, gate_scales, gate
 	c = torch.empty((M, N), device=a.device, dtype=torch.float16)
 	if M == 0:
 		return c.view(a.shape[:-1] + (N,))
+	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available
+	if M > DECODE_MAX_M and not prefill_kernel_available(M, K, N, groupsize):
+		g = dequant_matmul(x, groupsize, gate_qweight, gate_scales, gate_qzeros, g_idx, perm).float()
+		u = dequant_matmul(x, groupsize, up_qweight, up_scales, up_qzeros, g_idx, perm).float()
+		c = (torch.nn.functional.silu(g) * u).half()
+		return c.view(a.shape[:-1] + (N,))
 	ws = _lib.workspace(a.device, M, K, N)
 	rc = _lib.lib().gptq_gateup_silu(
 		_lib.ptr(x), _lib.ptr(gate_qweight), _lib.ptr(gate_qzeros), _lib.ptr(gate_scales),

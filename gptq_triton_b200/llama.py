@@ -1,0 +1,278 @@
+"""A self-contained LLaMA decoder whose module tree and state-dict keys match the HF
+LlamaForCausalLM that the reference builds in load_quant (src/gptq_triton/__init__.py:43-52),
+so that make_quant / make_quant_attn / make_fused_mlp and reference checkpoints apply
+unchanged, without depending on transformers internals.
+
+Two ways to run it:
+  * `forward(input_ids, past_key_values=..., use_cache=...)`: the reference-style path with
+    concatenated (K, V) tuples per layer;
+  * `DecodeEngine`: static KV cache written in place by the QKV kernel, residual adds fused
+    into the o_proj / down_proj epilogues, greedy sampling on the device, the whole decode
+    step captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .fused_attention import QuantLlamaAttention
+from .fused_mlp import QuantLlamaMLP
+
+
+@dataclass
+class LlamaConfig:
+	hidden_size: int = 4096
+	intermediate_size: int = 11008
+	num_hidden_layers: int = 32
+	num_attention_heads: int = 32
+	vocab_size: int = 32000
+	rms_norm_eps: float = 1e-6
+	rope_theta: float = 10000.0
+	max_position_embeddings: int = 2048
+
+	@classmethod
+	def from_json(cls, path):
+		import json
+		d = json.load(open(path))
+		keys = cls.__dataclass_fields__.keys()
+		return cls(**{k: d[k] for k in keys if k in d})
+
+	@classmethod
+	def llama_7b(cls):
+		return cls()
+
+	@classmethod
+	def llama_65b(cls):
+		return cls(hidden_size=8192, intermediate_size=22016, num_hidden_layers=80, num_attention_heads=64)
+
+
+class LlamaRMSNorm(nn.Module):
+	def __init__(self, hidden_size, eps=1e-6):
+		super().__init__()
+		self.weight = nn.Parameter(torch.ones(hidden_size))
+		self.variance_epsilon = eps
+
+	def forward(self, x):
+		v = x.float().pow(2).mean(-1, keepdim=True)
+		return self.weight * (x.float() * torch.rsqrt(v + self.variance_epsilon)).to(x.dtype)
+
+
+class LlamaMLP(nn.Module):
+	def __init__(self, config: LlamaConfig):
+		super().__init__()
+		self.gate_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=False)
+		self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=False)
+		self.up_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=False)
+
+	def forward(self, x):
+		return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+class LlamaAttention(nn.Module):
+	"""Unfused attention; only a container until make_quant_attn replaces it, but it also
+	runs (fp16 nn.Linear or QuantLinear children) for comparisons."""
+
+	def __init__(self, config: LlamaConfig):
+		super().__init__()
+		self.config = config
+		h = config.hidden_size
+		self.num_heads = config.num_attention_heads
+		self.head_dim = h // self.num_heads
+		self.q_proj = nn.Linear(h, h, bias=False)
+		self.k_proj = nn.Linear(h, h, bias=False)
+		self.v_proj = nn.Linear(h, h, bias=False)
+		self.o_proj = nn.Linear(h, h, bias=False)
+		self._tables = None
+
+	def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None, output_attentions=False, use_cache=False):
+		from .fused_attention import rope_tables
+		b, t, h = hidden_states.shape
+		q = self.q_proj(hidden_states).view(b, t, self.num_heads, self.head_dim).transpose(1, 2)
+		k = self.k_proj(hidden_states).view(b, t, self.num_heads, self.head_dim).transpose(1, 2)
+		v = self.v_proj(hidden_states).view(b, t, self.num_heads, self.head_dim).transpose(1, 2)
+		if self._tables is None or self._tables[0].device != q.device:
+			self._tables = rope_tables(self.head_dim, self.config.max_position_embeddings, self.config.rope_theta, device=q.device, dtype=q.dtype)
+		cos, sin = self._tables
+		c, s = cos[position_ids].unsqueeze(1), sin[position_ids].unsqueeze(1)
+		rot = lambda x: torch.cat([-x[..., x.shape[-1] // 2:], x[..., :x.shape[-1] // 2]], dim=-1)
+		q, k = q * c + rot(q) * s, k * c + rot(k) * s
+		if past_key_value is not None:
+			k = torch.cat([past_key_value[0], k], dim=2)
+			v = torch.cat([past_key_value[1], v], dim=2)
+		present = (k, v) if use_cache else None
+		o = F.scaled_dot_product_attention(q, k, v, attn_mask=attention_mask)
+		return self.o_proj(o.transpose(1, 2).reshape(b, t, h)), None, present
+
+
+class LlamaDecoderLayer(nn.Module):
+	def __init__(self, config: LlamaConfig):
+		super().__init__()
+		self.self_attn = LlamaAttention(config)
+		self.mlp = LlamaMLP(config)
+		self.input_layernorm = LlamaRMSNorm(config.hidden_size, config.rms_norm_eps)
+		self.post_attention_layernorm = LlamaRMSNorm(config.hidden_size, config.rms_norm_eps)
+
+	def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None, use_cache=False):
+		r = hidden_states
+		a, _, present = self.self_attn(self.input_layernorm(hidden_states), attention_mask=attention_mask, position_ids=position_ids,
+									   past_key_value=past_key_value, use_cache=use_cache)
+		hidden_states = r + a
+		hidden_states = hidden_states + self.mlp(self.post_attention_layernorm(hidden_states))
+		return hidden_states, present
+
+
+class LlamaModel(nn.Module):
+	def __init__(self, config: LlamaConfig):
+		super().__init__()
+		self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size)
+		self.layers = nn.ModuleList([LlamaDecoderLayer(config) for _ in range(config.num_hidden_layers)])
+		self.norm = LlamaRMSNorm(config.hidden_size, config.rms_norm_eps)
+
+
+def causal_mask(t: int, past: int, device, dtype=torch.float16):
+	m = torch.full((t, past + t), float('-inf'), device=device, dtype=dtype)
+	m = torch.triu(m, diagonal=past + 1)
+	return m[None, None]
+
+
+class LlamaForCausalLM(nn.Module):
+	def __init__(self, config: LlamaConfig):
+		super().__init__()
+		self.config = config
+		self.model = LlamaModel(config)
+		self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+
+	@torch.no_grad()
+	def forward(self, input_ids, past_key_values: Optional[List[Tuple[torch.Tensor, torch.Tensor]]] = None, use_cache: bool = False):
+		b, t = input_ids.shape
+		past = 0 if past_key_values is None else past_key_values[0][0].shape[2]
+		pos = torch.arange(past, past + t, device=input_ids.device).unsqueeze(0).expand(b, t)
+		mask = causal_mask(t, past, input_ids.device) if t > 1 else None
+		h = self.model.embed_tokens(input_ids)
+		presents = []
+		for i, layer in enumerate(self.model.layers):
+			h, present = layer(h, attention_mask=mask, position_ids=pos,
+							   past_key_value=None if past_key_values is None else past_key_values[i], use_cache=use_cache)
+			presents.append(present)
+		logits = self.lm_head(self.model.norm(h))
+		return logits, (presents if use_cache else None)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+	v = x.float().pow(2).mean(-1, keepdim=True)
+	return (x.float() * torch.rsqrt(v + eps)).to(x.dtype) * weight
+
+
+class DecodeEngine:
+	"""Greedy decoding with a static KV cache for a model whose attention and MLP blocks have
+	been fused (QuantLlamaAttention / QuantLlamaMLP).  One decode step = 32 x (RMSNorm, fused
+	QKV+rotary writing K/V into the cache, attention over the cache, o_proj + residual, RMSNorm,
+	fused gate/up, down_proj + residual), final norm, fp16 lm_head, argmax."""
+
+	def __init__(self, model: LlamaForCausalLM, batch: int, max_seq: int, use_graph: bool = True):
+		self.model = model
+		cfg = model.config
+		self.cfg = cfg
+		dev = model.lm_head.weight.device
+		self.device = dev
+		self.batch, self.max_seq = batch, max_seq
+		H, D = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads
+		for layer in model.model.layers:
+			assert isinstance(layer.self_attn, QuantLlamaAttention), 'run make_quant_attn first'
+		self.kcache = [torch.zeros((batch, H, max_seq, D), dtype=torch.float16, device=dev) for _ in model.model.layers]
+		self.vcache = [torch.zeros((batch, H, max_seq, D), dtype=torch.float16, device=dev) for _ in model.model.layers]
+		self.pos = torch.zeros((batch, 1), dtype=torch.int32, device=dev)          # position of the token being fed
+		self.tok = torch.zeros((batch, 1), dtype=torch.int64, device=dev)          # token being fed
+		self.mask = torch.full((batch, 1, 1, max_seq), float('-inf'), dtype=torch.float16, device=dev)
+		self.use_graph = use_graph
+		self.graph = None
+		self.launches_per_step = None
+
+	# -- one layer on hidden states h [b, t, hidden]; K/V go to the cache at `pos` --------------
+	def _layer(self, i, h, pos, attn_mask, kv_len):
+		layer = self.model.model.layers[i]
+		attn: QuantLlamaAttention = layer.self_attn
+		x = rmsnorm(h, layer.input_layernorm.weight, layer.input_layernorm.variance_epsilon)
+		q, _, _ = attn.project_qkv(x, pos, kv_cache=(self.kcache[i], self.vcache[i]))
+		b = h.shape[0]
+		k = self.kcache[i][:b, :, :kv_len]
+		v = self.vcache[i][:b, :, :kv_len]
+		o = F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask)
+		o = o.transpose(1, 2).reshape(h.shape)
+		h = attn.o_proj(o, residual=h)
+		x = rmsnorm(h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.variance_epsilon)
+		mlp = layer.mlp
+		if isinstance(mlp, QuantLlamaMLP):
+			h = mlp(x, residual=h)
+		else:
+			h = h + mlp(x)
+		return h
+
+	@torch.no_grad()
+	def prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
+		"""Runs the prompt [b, t], fills the cache, returns the first generated token [b, 1]."""
+		b, t = input_ids.shape
+		assert b == self.batch and t < self.max_seq
+		pos = torch.arange(t, device=self.device, dtype=torch.int32).unsqueeze(0).expand(b, t).contiguous()
+		mask = causal_mask(t, 0, self.device)
+		h = self.model.model.embed_tokens(input_ids)
+		for i in range(len(self.model.model.layers)):
+			h = self._layer(i, h, pos, mask, t)
+		h = rmsnorm(h[:, -1:, :], self.model.model.norm.weight, self.model.model.norm.variance_epsilon)
+		logits = self.model.lm_head(h)
+		self.tok.copy_(logits.argmax(-1))
+		self.pos.fill_(t)
+		self.mask.fill_(float('-inf'))
+		self.mask[..., :t + 1] = 0
+		return self.tok.clone()
+
+	def _step_body(self):
+		h = self.model.model.embed_tokens(self.tok)
+		for i in range(len(self.model.model.layers)):
+			h = self._layer(i, h, self.pos, self.mask, self.max_seq)
+		h = rmsnorm(h, self.model.model.norm.weight, self.model.model.norm.variance_epsilon)
+		logits = self.model.lm_head(h)
+		self.logits = logits
+		nxt = logits.argmax(-1)
+		# advance: next token, next position, unmask one more cache slot
+		self.tok.copy_(nxt)
+		self.pos.add_(1)
+		self.mask.scatter_(3, self.pos.view(self.batch, 1, 1, 1).to(torch.int64), 0.0)
+
+	@torch.no_grad()
+	def step(self) -> torch.Tensor:
+		"""Feeds self.tok at self.pos, returns the next token [b, 1] (device tensor)."""
+		if not self.use_graph:
+			self._step_body()
+			return self.tok
+		if self.graph is None:
+			# warm up on a side stream (allocations, workspaces), then capture
+			saved = (self.tok.clone(), self.pos.clone(), self.mask.clone())
+			s = torch.cuda.Stream()
+			s.wait_stream(torch.cuda.current_stream())
+			with torch.cuda.stream(s):
+				for _ in range(2):
+					self._step_body()
+					self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
+				s.synchronize()
+				g = torch.cuda.CUDAGraph()
+				with torch.cuda.graph(g, stream=s):
+					self._step_body()
+			torch.cuda.current_stream().wait_stream(s)
+			# capture does not execute: state is still the saved one
+			self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
+			self.graph = g
+		self.graph.replay()
+		return self.tok
+
+	@torch.no_grad()
+	def generate(self, input_ids: torch.Tensor, steps: int) -> torch.Tensor:
+		"""Greedy generation: returns [b, steps] token ids (the first comes from the prefill)."""
+		out = [self.prefill(input_ids)]
+		for _ in range(steps - 1):
+			out.append(self.step().clone())
+		return torch.cat(out, dim=1)

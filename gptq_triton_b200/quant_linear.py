@@ -60,6 +60,24 @@ def act_order_rows(qweight: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
 	return out
 
 
+DECODE_MAX_M = 16
+
+
+def prefill_kernel_available(M: int, K: int, N: int, groupsize: int) -> bool:
+	"""True when the tensor-core (tcgen05) kernel of the library covers this shape."""
+	return False
+
+
+def dequant_matmul(x2d: torch.Tensor, groupsize: int, qweight, scales, qzeros, g_idx=None, perm=None) -> torch.Tensor:
+	"""Dequantise-then-matmul on the GPU: the library's dequantise kernel followed by a cuBLAS
+	fp16 matmul.  Serves prefill-sized inputs (M > 16) for shapes the tensor-core kernel does not
+	cover, and is the comparison path of the tests."""
+	w = dequantize(groupsize, qweight, scales, qzeros, g_idx)
+	if perm is not None:
+		x2d = x2d[:, perm.long()]
+	return x2d @ w
+
+
 def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor,
 			bias: Optional[torch.Tensor] = None, g_idx: Optional[torch.Tensor] = None, perm: Optional[torch.Tensor] = None,
 			residual: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -86,6 +104,13 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 	if residual is not None:
 		assert residual.is_contiguous() and residual.numel() == M * N
 		res = residual.view(M, N)
+	if M > DECODE_MAX_M and not prefill_kernel_available(M, K, N, groupsize):
+		c = dequant_matmul(x, groupsize, qweight, scales, qzeros, g_idx, perm)
+		if bias is not None:
+			c = c + bias
+		if res is not None:
+			c = c + res
+		return c.view(a.shape[:-1] + (N,))
 	ws = _lib.workspace(a.device, M, K, N)
 	rc = _lib.lib().gptq_qmatmul(
 		_lib.ptr(x), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), _lib.ptr(g_idx), _lib.ptr(perm),
