@@ -284,6 +284,32 @@ def gpu_arm(args):
 		dist.destroy_process_group()
 
 
+def kernel_case(args):
+	"""Small stand-alone case for profilers: a few launches of one decode kernel over rotating
+	weight copies (larger than L2 together), nothing else.  `--kernel-case gateup|qkv|o|down`."""
+	import torch
+	import gptq_triton_b200 as G
+	from gptq_triton_b200 import synth
+	dev = torch.device('cuda', 0)
+	M = args.m
+	if args.kernel_case == 'gateup':
+		K, N = 4096, 11008
+		g, u = synth.quant_tensors(K, N, GROUPSIZE, seed=2), synth.quant_tensors(K, N, GROUPSIZE, seed=3)
+		copies = [tuple(t.to(dev).clone() for t in (g['qweight'], g['scales'], g['qzeros'], u['qweight'], u['scales'], u['qzeros'])) for _ in range(4)]
+		x = synth.activations((M, K), seed=1).to(dev)
+		for i in range(8):
+			G.gateup_silu(GROUPSIZE, x, *copies[i % 4])
+	else:
+		K, N = {'qkv': (4096, 12288), 'o': (4096, 4096), 'down': (11008, 4096)}[args.kernel_case]
+		t = synth.quant_tensors(K, N, GROUPSIZE, seed=2)
+		copies = [tuple(v.to(dev).clone() for v in (t['qweight'], t['scales'], t['qzeros'])) for _ in range(8)]
+		x = synth.activations((M, K), seed=1).to(dev)
+		for i in range(8):
+			G.qmatmul(GROUPSIZE, x, *copies[i % 8])
+	torch.cuda.synchronize()
+	print(json.dumps({'kernel_case': args.kernel_case, 'M': M, 'launches': 8}))
+
+
 def main():
 	ap = argparse.ArgumentParser()
 	ap.add_argument('--gpus', type=int, default=1)
@@ -292,8 +318,12 @@ def main():
 	ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
 	ap.add_argument('--layers', type=int, default=0, help='debug: fewer decoder layers')
 	ap.add_argument('--no-cpu-baseline', action='store_true')
+	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down'], help='profiling aid: run 8 launches of one decode kernel and exit')
+	ap.add_argument('--m', type=int, default=1, help='batch rows for --kernel-case')
 	args = ap.parse_args()
-	if args.impl == 'reference':
+	if args.kernel_case:
+		kernel_case(args)
+	elif args.impl == 'reference':
 		reference_arm(args)
 	else:
 		gpu_arm(args)
