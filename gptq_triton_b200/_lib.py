@@ -31,6 +31,8 @@ _SIGNATURES = {
 	'gptq_unpack_qzeros': (c_int, [_P, _P, c_int, c_int, _P]),
 	'gptq_dequantize': (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),
 	'gptq_act_order_rows': (c_int, [_P, _P, _P, c_int, c_int, _P]),
+	'gptq_qmatmul_noalloc': (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P]),
+	'gptq_noalloc_scratch_bytes': (c_size_t, [c_int, c_int, c_int, c_int]),
 }
 # Entry points outside the header's stable surface (tuning hooks); bound when present.
 _OPTIONAL = {

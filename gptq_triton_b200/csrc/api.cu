@@ -297,6 +297,31 @@ static int check_common(const void *x, const void *qw, const void *qz, const voi
 	return GPTQ_OK;
 }
 
+// ---- scratch for the allocation-free entry point -------------------------------------------
+// Lives in the library image; one copy per GPU that loads the library.  In host code the name
+// is only a handle: the device address comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[GPTQ_NOALLOC_SCRATCH_BYTES];
+
+static int noalloc_scratch_ptr(void **out) {
+	static void *cached[64] = {nullptr};
+	int dev = 0;
+	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GPTQ_ERR_CUDA;
+	if (cached[dev] == nullptr) {
+		void *ptr = nullptr;
+		cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+		if (e != cudaSuccess || ptr == nullptr) return cuda_status(e == cudaSuccess ? cudaErrorInvalidSymbol : e);
+		cached[dev] = ptr;
+	}
+	*out = cached[dev];
+	return GPTQ_OK;
+}
+
+// bytes of the array a planned launch touches: counters + [tile][split][row < M][128] fp32
+static size_t noalloc_need(const SkinnyParams &p) {
+	const size_t tiles = (size_t)(p.N + SK_BN - 1) / SK_BN;
+	return SK_TICKET_BYTES + tiles * p.splitk * (size_t)p.M * SK_BN * sizeof(float);
+}
+
 }   // namespace gptq
 
 using namespace gptq;
@@ -310,7 +335,7 @@ const char *gptq_error_string(int code) {
 		case GPTQ_OK: return "ok";
 		case GPTQ_ERR_INVALID: return "invalid argument (null pointer, non-positive size or bad leading dimension)";
 		case GPTQ_ERR_SHAPE: return "shape not supported: K and N must be multiples of 8";
-		case GPTQ_ERR_WORKSPACE: return "workspace missing or smaller than gptq_workspace_bytes()";
+		case GPTQ_ERR_WORKSPACE: return "workspace missing or smaller than gptq_workspace_bytes(), or the problem needs more than the built-in scratch of gptq_qmatmul_noalloc";
 		case GPTQ_ERR_ALIGN: return "pointers must be 16-byte aligned and leading dimensions multiples of 8";
 		case GPTQ_ERR_CUDA: return "CUDA runtime error at launch (see gptq_last_cuda_error)";
 		case GPTQ_ERR_UNSUPPORTED: return "combination not implemented";
@@ -367,6 +392,48 @@ int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, c
 										  nullptr, g_idx, perm, (const __half *)bias, (const __half *)residual, ldr,
 										  (__half *)y, ldy, M, K, N, groupsize);
 	return cuda_status(cudaGetLastError());
+}
+
+size_t gptq_noalloc_scratch_bytes(int M, int K, int N, int groupsize) {
+	if (M <= 0 || M > 16 || K <= 0 || N <= 0) return 0;
+	if (groupsize == -1) groupsize = K;
+	if (groupsize <= 0 || !skinny_shape_ok(K, N, groupsize, nullptr)) return 0;
+	SkinnyParams p = {};
+	p.M = M; p.K = K; p.N = N; p.groupsize = groupsize;
+	dim3 grid;
+	size_t smem;
+	int kw;
+	plan_skinny(p, 1, kw, grid, smem);
+	return noalloc_need(p);
+}
+
+int gptq_qmatmul_noalloc(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *perm,
+						 const void *bias, const void *residual, int64_t ldr, void *y, int M, int K, int N, int groupsize,
+						 int64_t ldx, int64_t ldy, gptq_stream_t stream) {
+	int rc = check_common(x, qweight, qzeros, scales, y, M, K, N, groupsize, ldx, ldy);
+	if (rc != GPTQ_OK) return rc;
+	if (residual && ldr < N) return GPTQ_ERR_INVALID;
+	if (M == 0) return GPTQ_OK;
+	if (M > 16 || !skinny_shape_ok(K, N, groupsize, nullptr) || (perm && !aligned16(perm))) return GPTQ_ERR_UNSUPPORTED;
+	if (gptq_noalloc_scratch_bytes(M, K, N, groupsize) > GPTQ_NOALLOC_SCRATCH_BYTES) return GPTQ_ERR_WORKSPACE;
+	void *scratch = nullptr;
+	rc = noalloc_scratch_ptr(&scratch);          // first call on a device: resolves the array's device address
+	if (rc != GPTQ_OK) return rc;
+	cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+	// the arrival counters must start at zero; partial sums need no clearing (every slot that is
+	// read is written first by this launch)
+	cudaError_t e = cudaMemsetAsync(scratch, 0, SK_TICKET_BYTES, st);
+	if (e != cudaSuccess) return cuda_status(e);
+	SkinnyParams p = {};
+	p.x = (const __half *)x; p.ldx = ldx;
+	p.qz0 = qzeros; p.sc0 = (const __half *)scales;
+	p.perm = perm;
+	p.M = M; p.K = K; p.N = N; p.groupsize = groupsize;
+	p.bias = (const __half *)bias; p.residual = (const __half *)residual; p.ldr = ldr;
+	p.y = (__half *)y; p.ldy = ldy;
+	// launch_skinny only checks that the buffer is at least as large as the generic upper bound;
+	// the array was checked against the exact need above, so pass that bound as the size
+	return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, scratch, skinny_ws_bytes(M, N, 1), st);
 }
 
 int gptq_gateup_silu(const void *x, const int32_t *gate_qweight, const int32_t *gate_qzeros, const void *gate_scales,

@@ -133,6 +133,37 @@ int gptq_dequantize(const int32_t *qweight, const int32_t *qzeros, const void *s
 int gptq_act_order_rows(const int32_t *qweight, const int32_t *perm, int32_t *out, int K, int N,
                         gptq_stream_t stream);
 
+/*
+ * Allocation-free form of gptq_qmatmul for the decode regime (M <= 16).  No counterpart in the
+ * reference.  It exists for callers that cannot provide or obtain scratch memory: a host that has
+ * given the whole device to its own memory pool, or a latency-critical serving loop in which
+ * cudaMalloc (which synchronises the device) must never run.  The split-K scratch lives in an array
+ * that is part of the library image: GPTQ_NOALLOC_SCRATCH_BYTES (4 MiB) per GPU that loads the
+ * library, held until the process exits.  The call itself performs no cudaMalloc / cudaFree and
+ * calls no allocating routine.
+ *
+ *   - Shapes: the fast decode path only (M <= 16, N % 32 == 0, K % 128 == 0, groupsize 32, 64 or a
+ *     multiple of 128 dividing K, no g_idx; perm is allowed).  Other shapes: GPTQ_ERR_UNSUPPORTED.
+ *   - Problems whose split-K partial sums do not fit the array are rejected with
+ *     GPTQ_ERR_WORKSPACE (see gptq_noalloc_scratch_bytes for the requirement of a shape).
+ *   - The first call on a device looks up the device address of the array (once per device, with
+ *     that device current); make that first call before any stream capture.
+ *   - All calls on a device share the one array.  The arrival counters are cleared on `stream` at
+ *     the start of every call; partial sums of the previous call are simply overwritten.  Two of
+ *     these calls that overlap on the GPU (e.g. issued on different streams) race on the array:
+ *     keep them on one stream or order them with events.  Calls of the workspace form
+ *     (gptq_qmatmul) do not touch the array and may run concurrently with one of these.
+ */
+#define GPTQ_NOALLOC_SCRATCH_BYTES (4u << 20)
+int gptq_qmatmul_noalloc(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales,
+                         const int32_t *perm, const void *bias, const void *residual, int64_t ldr,
+                         void *y, int M, int K, int N, int groupsize, int64_t ldx, int64_t ldy,
+                         gptq_stream_t stream);
+
+/* Scratch bytes gptq_qmatmul_noalloc would use for this shape on the current device (0 when the
+ * shape is not served by it).  Host-only arithmetic. */
+size_t gptq_noalloc_scratch_bytes(int M, int K, int N, int groupsize);
+
 #ifdef __cplusplus
 }
 #endif
