@@ -31,6 +31,9 @@ _SIGNATURES = {
 	'gptq_unpack_qzeros': (c_int, [_P, _P, c_int, c_int, _P]),
 	'gptq_dequantize': (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),
 	'gptq_act_order_rows': (c_int, [_P, _P, _P, c_int, c_int, _P]),
+	'gptq_attn_workspace_bytes': (c_size_t, [c_int, c_int]),
+	'gptq_attn_decode': (c_int, [_P, c_int64, _P, _P, c_int64, c_int64, _P, _P, c_int64, c_int, c_int, c_int, c_int, ctypes.c_float, _P, c_size_t, _P]),
+	'gptq_rmsnorm': (c_int, [_P, c_int64, _P, _P, c_int64, c_int, c_int, ctypes.c_float, _P]),
 	'gptq_qmatmul_noalloc': (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P]),
 	'gptq_noalloc_scratch_bytes': (c_size_t, [c_int, c_int, c_int, c_int]),
 }
@@ -100,8 +103,8 @@ def require_cuda(*tensors):
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 
 
-def workspace(device: torch.device, M: int, K: int, N: int) -> torch.Tensor:
-	need = lib().gptq_workspace_bytes(M, K, N)
+def workspace(device: torch.device, M: int, K: int, N: int, min_bytes: int = 0) -> torch.Tensor:
+	need = max(lib().gptq_workspace_bytes(M, K, N), min_bytes)
 	key = (device.index if device.index is not None else torch.cuda.current_device(),
 		   torch.cuda.current_stream(device).cuda_stream)
 	ws = _workspaces.get(key)

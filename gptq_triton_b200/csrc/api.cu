@@ -6,6 +6,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "attn_decode.cuh"
 #include "qmm_skinny.cuh"
 #include "qmm_tc.cuh"
 
@@ -391,6 +392,45 @@ int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, c
 	general_kernel<1><<<grid, 128, 0, st>>>((const __half *)x, ldx, qweight, qzeros, (const __half *)scales, nullptr, nullptr,
 										  nullptr, g_idx, perm, (const __half *)bias, (const __half *)residual, ldr,
 										  (__half *)y, ldy, M, K, N, groupsize);
+	return cuda_status(cudaGetLastError());
+}
+
+size_t gptq_attn_workspace_bytes(int batch, int heads) {
+	if (batch <= 0 || heads <= 0) return AT_TICKET_BYTES;
+	return AT_TICKET_BYTES + (size_t)batch * heads * AT_MAX_SPLITS * 130 * sizeof(float);
+}
+
+int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, const void *vcache, int64_t kv_stride_b,
+					 int64_t kv_stride_h, const int32_t *pos, void *out, int64_t out_stride_b, int batch, int heads, int head_dim,
+					 int len_hint, float scale, void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+	if (!q || !kcache || !vcache || !pos || !out) return GPTQ_ERR_INVALID;
+	if (batch < 0 || heads <= 0 || len_hint <= 0) return GPTQ_ERR_INVALID;
+	if (head_dim != AT_D) return GPTQ_ERR_UNSUPPORTED;
+	if (!aligned16(q) || !aligned16(kcache) || !aligned16(vcache) || q_stride_b % 8 || kv_stride_b % 8 || kv_stride_h % 8)
+		return GPTQ_ERR_ALIGN;
+	if (batch == 0) return GPTQ_OK;
+	if ((size_t)batch * heads * 4 > (size_t)AT_TICKET_BYTES - 8) return GPTQ_ERR_UNSUPPORTED;
+	int splits = (4 * sm_count() + batch * heads - 1) / (batch * heads);
+	splits = std::max(1, std::min(splits, std::min(AT_MAX_SPLITS, (len_hint + 63) / 64)));
+	if (splits > 1 && (!workspace || workspace_bytes < gptq_attn_workspace_bytes(batch, heads))) return GPTQ_ERR_WORKSPACE;
+	AttnParams p = {};
+	p.q = (const __half *)q; p.q_stride_b = q_stride_b;
+	p.kc = (const __half *)kcache; p.vc = (const __half *)vcache;
+	p.kv_stride_b = kv_stride_b; p.kv_stride_h = kv_stride_h;
+	p.pos = pos; p.out = (__half *)out; p.out_stride_b = out_stride_b;
+	p.scale = scale; p.heads = heads; p.splits = splits;
+	p.ws_ticket = reinterpret_cast<int *>(workspace);
+	p.ws_partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + AT_TICKET_BYTES);
+	attn_decode_kernel<<<dim3(splits, heads, batch), AT_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+	return cuda_status(cudaGetLastError());
+}
+
+int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_t ldy, int M, int K, float eps, gptq_stream_t stream) {
+	if (!x || !weight || !y || M < 0 || K <= 0) return GPTQ_ERR_INVALID;
+	if (K % 8 != 0) return GPTQ_ERR_SHAPE;
+	if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || ldx % 8 || ldy % 8) return GPTQ_ERR_ALIGN;
+	if (M == 0) return GPTQ_OK;
+	rmsnorm_kernel<<<M, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((const __half *)x, ldx, (const __half *)weight, (__half *)y, ldy, K, eps);
 	return cuda_status(cudaGetLastError());
 }
 

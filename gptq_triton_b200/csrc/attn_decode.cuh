@@ -1,0 +1,215 @@
+// Single-query (decode) attention over a static fp16 KV cache: softmax(q·K^T / sqrt(d)) · V
+// for one new token per sequence.  HBM-bound: K and V of every cached position are read once.
+//
+// Grid (splits, heads, batch).  A CTA of 4 warps takes a contiguous range of cache positions;
+// 8 lanes share one key (16 head dims = two 16-byte loads each, a key row is 256 contiguous
+// bytes), so a warp handles 4 keys per step and a CTA 16.  Each 8-lane group keeps an online
+// softmax (running max, running sum, 16 output dims in fp32).  Groups, warps and splits are
+// merged with the usual log-sum-exp rescaling; the last CTA of a (batch, head) to arrive
+// (ticket in the workspace) merges the split partials in fixed order and writes fp16.
+#pragma once
+
+#include "common.cuh"
+
+namespace gptq {
+
+constexpr int AT_D = 128;              // head dim
+constexpr int AT_THREADS = 128;
+constexpr int AT_MAX_SPLITS = 32;
+constexpr int AT_TICKET_BYTES = 16384;
+
+struct AttnParams {
+	const __half *q;          // [b, heads, 128] (row stride q_stride_b)
+	long long q_stride_b;
+	const __half *kc, *vc;    // [b, heads, max_seq, 128]
+	long long kv_stride_b, kv_stride_h;
+	const int32_t *pos;       // [b]: index of the newest token; positions 0..pos are attended
+	__half *out;              // [b, heads*128]
+	long long out_stride_b;
+	float scale;
+	int heads, splits;
+	float *ws_partial;        // [b*heads][splits][130]
+	int *ws_ticket;           // [b*heads]
+};
+
+__global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParams p) {
+	const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	const int grp = lane >> 3, sub = lane & 7;           // 4 key groups per warp, 8 lanes per key
+	const int len = p.pos[b] + 1;
+	const int per = (len + p.splits - 1) / p.splits;
+	const int k_lo = split * per, k_hi = min(k_lo + per, len);
+
+	__shared__ float s_m[16], s_l[16], s_acc[16][AT_D];
+	__shared__ int s_last;
+
+	// this lane's 16 query dims, pre-scaled
+	float qf[16];
+	{
+		const __half *qp = p.q + (size_t)b * p.q_stride_b + head * AT_D + sub * 16;
+		const uint4 a = *reinterpret_cast<const uint4 *>(qp), c = *reinterpret_cast<const uint4 *>(qp + 8);
+		const __half2 *ha = reinterpret_cast<const __half2 *>(&a), *hc = reinterpret_cast<const __half2 *>(&c);
+#pragma unroll
+		for (int i = 0; i < 4; ++i) {
+			const float2 f = __half22float2(ha[i]), g = __half22float2(hc[i]);
+			qf[2 * i] = f.x * p.scale;
+			qf[2 * i + 1] = f.y * p.scale;
+			qf[8 + 2 * i] = g.x * p.scale;
+			qf[8 + 2 * i + 1] = g.y * p.scale;
+		}
+	}
+	const __half *kbase = p.kc + (size_t)b * p.kv_stride_b + (size_t)head * p.kv_stride_h + sub * 16;
+	const __half *vbase = p.vc + (size_t)b * p.kv_stride_b + (size_t)head * p.kv_stride_h + sub * 16;
+
+	float m = -INFINITY, l = 0.f, acc[16];
+#pragma unroll
+	for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+
+	constexpr int UNROLL = 4;          // keys in flight per 8-lane group
+	for (int base = k_lo + warp * 4; base < k_hi; base += 16 * UNROLL) {      // trip count uniform within the warp
+		const int k0 = base + grp;
+		uint4 kr[UNROLL][2], vr[UNROLL][2];
+#pragma unroll
+		for (int u = 0; u < UNROLL; ++u) {
+			const int key = k0 + u * 16;
+			if (key < k_hi) {
+				const __half *kp = kbase + (size_t)key * AT_D, *vp = vbase + (size_t)key * AT_D;
+				kr[u][0] = ld_nc_v4(kp);
+				kr[u][1] = ld_nc_v4(kp + 8);
+				vr[u][0] = ld_nc_v4(vp);
+				vr[u][1] = ld_nc_v4(vp + 8);
+			}
+		}
+#pragma unroll
+		for (int u = 0; u < UNROLL; ++u) {
+			const int key = k0 + u * 16;
+			const bool valid = key < k_hi;            // uniform within an 8-lane group
+			float s = 0.f;
+			if (valid) {
+				const __half2 *h0 = reinterpret_cast<const __half2 *>(&kr[u][0]), *h1 = reinterpret_cast<const __half2 *>(&kr[u][1]);
+#pragma unroll
+				for (int i = 0; i < 4; ++i) {
+					const float2 f = __half22float2(h0[i]), g = __half22float2(h1[i]);
+					s = fmaf(qf[2 * i], f.x, s);
+					s = fmaf(qf[2 * i + 1], f.y, s);
+					s = fmaf(qf[8 + 2 * i], g.x, s);
+					s = fmaf(qf[8 + 2 * i + 1], g.y, s);
+				}
+			}
+			// all 32 lanes take part in the shuffles; the xor pattern stays inside the 8-lane group
+			s += __shfl_xor_sync(0xffffffffu, s, 1);
+			s += __shfl_xor_sync(0xffffffffu, s, 2);
+			s += __shfl_xor_sync(0xffffffffu, s, 4);
+			if (valid) {
+				const float mn = fmaxf(m, s);
+				const float corr = __expf(m - mn), pw = __expf(s - mn);
+				l = l * corr + pw;
+				const __half2 *h0 = reinterpret_cast<const __half2 *>(&vr[u][0]), *h1 = reinterpret_cast<const __half2 *>(&vr[u][1]);
+#pragma unroll
+				for (int i = 0; i < 4; ++i) {
+					const float2 f = __half22float2(h0[i]), g = __half22float2(h1[i]);
+					acc[2 * i] = fmaf(pw, f.x, acc[2 * i] * corr);
+					acc[2 * i + 1] = fmaf(pw, f.y, acc[2 * i + 1] * corr);
+					acc[8 + 2 * i] = fmaf(pw, g.x, acc[8 + 2 * i] * corr);
+					acc[8 + 2 * i + 1] = fmaf(pw, g.y, acc[8 + 2 * i + 1] * corr);
+				}
+				m = mn;
+			}
+		}
+	}
+
+	// ---- merge the 16 groups of the CTA (fixed order) -------------------------------------------
+	const int g16 = warp * 4 + grp;
+	if (sub == 0) {
+		s_m[g16] = m;
+		s_l[g16] = l;
+	}
+#pragma unroll
+	for (int i = 0; i < 16; ++i) s_acc[g16][sub * 16 + i] = acc[i];
+	__syncthreads();
+	float M = -INFINITY;
+#pragma unroll
+	for (int g = 0; g < 16; ++g) M = fmaxf(M, s_m[g]);
+	float L = 0.f, o = 0.f;            // thread tid owns output dim tid
+#pragma unroll
+	for (int g = 0; g < 16; ++g) {
+		const float w = (s_m[g] == -INFINITY) ? 0.f : __expf(s_m[g] - M);
+		L = fmaf(s_l[g], w, L);
+		o = fmaf(s_acc[g][tid], w, o);
+	}
+
+	const int bh = b * p.heads + head;
+	if (p.splits == 1) {
+		p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(o / L);
+		return;
+	}
+	float *wp = p.ws_partial + ((size_t)bh * p.splits + split) * 130;
+	__stcg(wp + 2 + tid, o);
+	if (tid == 0) {
+		__stcg(wp, M);
+		__stcg(wp + 1, L);
+	}
+	__threadfence();
+	__syncthreads();
+	if (tid == 0) {
+		const int t = atomicAdd(p.ws_ticket + bh, 1);
+		const int last = (t == p.splits - 1);
+		if (last) p.ws_ticket[bh] = 0;
+		s_last = last;
+	}
+	__syncthreads();
+	if (!s_last) return;
+	__threadfence();
+	const float *wb = p.ws_partial + (size_t)bh * p.splits * 130;
+	float Mg = -INFINITY;
+	for (int s = 0; s < p.splits; ++s) Mg = fmaxf(Mg, __ldcg(wb + s * 130));
+	float Lg = 0.f, og = 0.f;
+	for (int s = 0; s < p.splits; ++s) {
+		const float ms = __ldcg(wb + s * 130);
+		const float w = (ms == -INFINITY) ? 0.f : __expf(ms - Mg);
+		Lg = fmaf(__ldcg(wb + s * 130 + 1), w, Lg);
+		og = fmaf(__ldcg(wb + s * 130 + 2 + tid), w, og);
+	}
+	p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(og / Lg);
+}
+
+// ---- RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, fp32 inside, one fp16 rounding ----------------
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const __half *__restrict__ x, long long ldx, const __half *__restrict__ w,
+													  __half *__restrict__ y, long long ldy, int K, float eps) {
+	const int row = blockIdx.x, tid = threadIdx.x;
+	const __half *xr = x + (size_t)row * ldx;
+	float ss = 0.f;
+	for (int k = tid * 8; k < K; k += 256 * 8) {
+		const uint4 v = *reinterpret_cast<const uint4 *>(xr + k);
+		const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+		for (int i = 0; i < 4; ++i) {
+			const float2 f = __half22float2(h[i]);
+			ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+		}
+	}
+	__shared__ float s_part[8];
+#pragma unroll
+	for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+	if ((tid & 31) == 0) s_part[tid >> 5] = ss;
+	__syncthreads();
+	float tot = 0.f;
+#pragma unroll
+	for (int i = 0; i < 8; ++i) tot += s_part[i];
+	const float inv = rsqrtf(tot / (float)K + eps);
+	for (int k = tid * 8; k < K; k += 256 * 8) {
+		const uint4 v = *reinterpret_cast<const uint4 *>(xr + k);
+		const uint4 g = *reinterpret_cast<const uint4 *>(w + k);
+		const __half2 *h = reinterpret_cast<const __half2 *>(&v), *gh = reinterpret_cast<const __half2 *>(&g);
+		uint4 o;
+		__half2 *oh = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+		for (int i = 0; i < 4; ++i) {
+			const float2 f = __half22float2(h[i]), gg = __half22float2(gh[i]);
+			oh[i] = __floats2half2_rn(f.x * inv * gg.x, f.y * inv * gg.y);
+		}
+		*reinterpret_cast<uint4 *>(y + (size_t)row * ldy + k) = o;
+	}
+}
+
+}   // namespace gptq

@@ -198,3 +198,33 @@ class QuantLlamaAttention(nn.Module):
 		attn_output = attn_output.transpose(1, 2).reshape(bsz, q_len, self.hidden_size)
 		attn_output = self.o_proj(attn_output)
 		return attn_output, attn_weights, past_key_value
+
+
+def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: torch.Tensor, len_hint: int) -> torch.Tensor:
+	"""Attention of one new token per sequence over a static cache.
+	q [b, heads, 1, 128] or [b, 1, heads, 128] memory as produced by qkv_rope (any view whose
+	(b, head) slices are 128 contiguous halfs with head stride 128); kcache/vcache [B, heads, S, 128]
+	contiguous; pos int32 [b] or [b, 1].  Returns [b, 1, heads*128] fp16."""
+	b = q.shape[0]
+	heads, S, D = kcache.shape[1], kcache.shape[2], kcache.shape[3]
+	_lib.require_cuda(q, kcache, vcache, pos)
+	out = torch.empty((b, 1, heads * D), device=q.device, dtype=torch.float16)
+	need = _lib.lib().gptq_attn_workspace_bytes(b, heads)
+	ws = _lib.workspace(q.device, 1, 128, 128, min_bytes=need)
+	rc = _lib.lib().gptq_attn_decode(_lib.ptr(q), heads * D, _lib.ptr(kcache), _lib.ptr(vcache), heads * S * D, S * D, _lib.ptr(pos),
+									 _lib.ptr(out), heads * D, b, heads, D, int(len_hint), 1.0 / math.sqrt(D), _lib.ptr(ws), ws.numel(),
+									 _lib.stream_ptr(q.device))
+	_lib.check(rc, 'gptq_attn_decode')
+	return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+	"""RMSNorm over the last dimension in one kernel (fp32 inside, one fp16 rounding)."""
+	_lib.require_cuda(x, weight)
+	assert x.is_contiguous() and x.dtype == torch.float16
+	K = x.shape[-1]
+	x2 = x.view(-1, K)
+	y = torch.empty_like(x2)
+	rc = _lib.lib().gptq_rmsnorm(_lib.ptr(x2), K, _lib.ptr(weight), _lib.ptr(y), K, x2.shape[0], K, float(eps), _lib.stream_ptr(x.device))
+	_lib.check(rc, 'gptq_rmsnorm')
+	return y.view(x.shape)

@@ -19,7 +19,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .fused_attention import QuantLlamaAttention
+from .fused_attention import QuantLlamaAttention, attn_decode
+from .fused_attention import rmsnorm as rmsnorm_kernel
 from .fused_mlp import QuantLlamaMLP
 
 
@@ -189,6 +190,7 @@ class DecodeEngine:
 		self.tok = torch.zeros((batch, 1), dtype=torch.int64, device=dev)          # token being fed
 		self.mask = torch.full((batch, 1, 1, max_seq), float('-inf'), dtype=torch.float16, device=dev)
 		self.use_graph = use_graph
+		self.len_hint = max_seq
 		self.graph = None
 		self.launches_per_step = None
 
@@ -196,15 +198,21 @@ class DecodeEngine:
 	def _layer(self, i, h, pos, attn_mask, kv_len):
 		layer = self.model.model.layers[i]
 		attn: QuantLlamaAttention = layer.self_attn
-		x = rmsnorm(h, layer.input_layernorm.weight, layer.input_layernorm.variance_epsilon)
+		decode = h.shape[1] == 1
+		norm = rmsnorm_kernel if h.is_contiguous() else rmsnorm
+		x = norm(h, layer.input_layernorm.weight, layer.input_layernorm.variance_epsilon)
 		q, _, _ = attn.project_qkv(x, pos, kv_cache=(self.kcache[i], self.vcache[i]))
 		b = h.shape[0]
-		k = self.kcache[i][:b, :, :kv_len]
-		v = self.vcache[i][:b, :, :kv_len]
-		o = F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask)
-		o = o.transpose(1, 2).reshape(h.shape)
+		if decode:
+			# own single-query kernel over the static cache (length read from `pos` on the device)
+			o = attn_decode(q, self.kcache[i], self.vcache[i], pos, self.len_hint)
+		else:
+			k = self.kcache[i][:b, :, :kv_len]
+			v = self.vcache[i][:b, :, :kv_len]
+			o = F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask)
+			o = o.transpose(1, 2).reshape(h.shape)
 		h = attn.o_proj(o, residual=h)
-		x = rmsnorm(h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.variance_epsilon)
+		x = norm(h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.variance_epsilon)
 		mlp = layer.mlp
 		if isinstance(mlp, QuantLlamaMLP):
 			h = mlp(x, residual=h)
@@ -226,6 +234,7 @@ class DecodeEngine:
 		logits = self.model.lm_head(h)
 		self.tok.copy_(logits.argmax(-1))
 		self.pos.fill_(t)
+		self.len_hint = t + 1
 		self.mask.fill_(float('-inf'))
 		self.mask[..., :t + 1] = 0
 		return self.tok.clone()
@@ -234,7 +243,7 @@ class DecodeEngine:
 		h = self.model.model.embed_tokens(self.tok)
 		for i in range(len(self.model.model.layers)):
 			h = self._layer(i, h, self.pos, self.mask, self.max_seq)
-		h = rmsnorm(h, self.model.model.norm.weight, self.model.model.norm.variance_epsilon)
+		h = rmsnorm_kernel(h, self.model.model.norm.weight, self.model.model.norm.variance_epsilon)
 		logits = self.model.lm_head(h)
 		self.logits = logits
 		nxt = logits.argmax(-1)

@@ -134,6 +134,29 @@ int gptq_act_order_rows(const int32_t *qweight, const int32_t *perm, int32_t *ou
                         gptq_stream_t stream);
 
 /*
+ * Single-query attention over a static KV cache: out[b, h*128 + :] = softmax(q·K^T * scale) · V
+ * over cache positions 0..pos[b].  Replaces, for one new token, the attention core of
+ * QuantLlamaAttention.forward (src/gptq_triton/fused_attention.py:119-146: QK^T / sqrt(d), fp32
+ * softmax, ·V) reading the cache that gptq_qkv_rope wrote in place instead of the torch.cat copy
+ * (:105-115).  q [b, heads, 128] fp16 (row stride q_stride_b), caches [b, heads, max_seq, 128]
+ * fp16 with the given strides, pos int32 [b], out fp16 [b, heads*128].  len_hint (host value,
+ * about the current context length) only chooses the split count.  The workspace may be the
+ * one used for gptq_qmatmul; size from gptq_attn_workspace_bytes, zeroed once.
+ */
+size_t gptq_attn_workspace_bytes(int batch, int heads);
+int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, const void *vcache,
+                     int64_t kv_stride_b, int64_t kv_stride_h, const int32_t *pos,
+                     void *out, int64_t out_stride_b, int batch, int heads, int head_dim,
+                     int len_hint, float scale, void *workspace, size_t workspace_bytes,
+                     gptq_stream_t stream);
+
+/* y = x * rsqrt(mean(x^2) + eps) * weight, per row, fp32 inside.  The RMSNorm that the HF
+ * decoder layer applies in front of the attention and MLP blocks (third-party code the
+ * reference model is built from, src/gptq_triton/__init__.py:47). */
+int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_t ldy,
+                 int M, int K, float eps, gptq_stream_t stream);
+
+/*
  * Allocation-free form of gptq_qmatmul for the decode regime (M <= 16).  No counterpart in the
  * reference.  It exists for callers that cannot provide or obtain scratch memory: a host that has
  * given the whole device to its own memory pool, or a latency-critical serving loop in which

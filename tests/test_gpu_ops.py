@@ -396,3 +396,37 @@ def test_empty_batch(G):
 	x = torch.zeros((0, 256), dtype=torch.float16, device='cuda')
 	y = G.qmatmul(128, x, t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda())
 	assert y.shape == (0, 256)
+
+
+# ---------------------------------------------------------------- decode attention + RMSNorm kernels
+@pytest.mark.parametrize('b,heads,S,positions', [(1, 4, 300, [0]), (1, 32, 2100, [2047]), (3, 4, 513, [5, 512, 63]), (2, 2, 64, [63, 1])])
+def test_attn_decode_matches_fp32_reference(G, b, heads, S, positions):
+	"""softmax(q K^T / sqrt(d)) V over cache positions 0..pos, fp32 softmax as in
+	fused_attention.py:119-137 of the reference, against a float64 evaluation."""
+	from gptq_triton_b200.fused_attention import attn_decode
+	D = 128
+	g = torch.Generator().manual_seed(b * 1000 + S)
+	q = torch.randn((b, 1, heads, D), generator=g).half()
+	kc = torch.randn((b, heads, S, D), generator=g).half()
+	vc = torch.randn((b, heads, S, D), generator=g).half()
+	pos = torch.tensor(positions, dtype=torch.int32).view(b, 1)
+	out = attn_decode(q.cuda().transpose(1, 2), kc.cuda(), vc.cuda(), pos.cuda(), len_hint=max(positions) + 1).cpu()
+	ref = torch.empty((b, heads * D), dtype=torch.float64)
+	for i in range(b):
+		n = positions[i] + 1
+		s = torch.einsum('hd,hsd->hs', q[i, 0].double(), kc[i, :, :n].double()) / D ** 0.5
+		ref[i] = torch.einsum('hs,hsd->hd', torch.softmax(s, dim=-1), vc[i, :, :n].double()).reshape(-1)
+	assert out.shape == (b, 1, heads * D)
+	assert O.max_rel_err(out.view(b, -1), ref.float()) <= TOL
+
+
+@pytest.mark.parametrize('M,K', [(1, 4096), (5, 512), (16, 11008)])
+def test_rmsnorm_kernel(G, M, K):
+	from gptq_triton_b200.fused_attention import rmsnorm
+	g = torch.Generator().manual_seed(M + K)
+	x = (torch.randn((M, K), generator=g) * 3).half()
+	w = (torch.rand((K,), generator=g) + 0.5).half()
+	y = rmsnorm(x.cuda(), w.cuda(), 1e-6).cpu()
+	xd = x.double()
+	ref = xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + 1e-6) * w.double()
+	assert O.max_rel_err(y, ref.float()) <= 1e-3
