@@ -190,11 +190,13 @@ def gpu_arm(args):
 	if rank == 0:
 		sampler.start()
 	e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+	torch.cuda.profiler.start()           # lets a profiler restrict itself to the timed region
 	e0.record()
 	for _ in range(args.steps):
 		engine.step()
 	e1.record()
 	barrier()
+	torch.cuda.profiler.stop()
 	ms = e0.elapsed_time(e1)
 	clocks = sampler.stop() if rank == 0 else None
 	t = torch.tensor([ms], device=dev)
@@ -267,7 +269,7 @@ def gpu_arm(args):
 			   'sample': 'one 4096x4096 g128 projection at M=1 through the CPU oracle (1/%.0f of the quantised weights of a decode step), median of 5' % scale}
 
 	if rank == 0:
-		launches_per_step = 4 * cfg.num_hidden_layers
+		launches_per_step = 7 * cfg.num_hidden_layers + 1      # 4 quantised matmuls, attention, 2 RMSNorm per layer + final norm
 		line = {
 			'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
 			'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f16',

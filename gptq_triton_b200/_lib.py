@@ -6,6 +6,7 @@ raised.  The library is built in-tree by `python -m gptq_triton_b200.build`.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 from typing import Dict, Optional, Tuple
@@ -42,6 +43,7 @@ _OPTIONAL = {
 	'gptq_debug_force_splitk': (None, [c_int]),
 	'gptq_debug_force_kw': (None, [c_int]),
 	'gptq_debug_allow_cluster': (None, [c_int]),
+	'gptq_debug_set_pdl': (None, [c_int]),
 }
 
 
@@ -67,6 +69,8 @@ def lib() -> ctypes.CDLL:
 				fn = getattr(l, name)
 				fn.restype = res
 				fn.argtypes = args
+		if os.environ.get('GPTQ_B200_PDL', '0') == '1' and hasattr(l, 'gptq_debug_set_pdl'):
+			l.gptq_debug_set_pdl(1)      # opt in to programmatic dependent launch (A/B measurements)
 		_lib = l
 	return _lib
 

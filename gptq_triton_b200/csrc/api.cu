@@ -2,6 +2,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
+#include <utility>
 
 #include <cuda.h>
 
@@ -16,6 +17,7 @@ thread_local int g_last_cuda_error = 0;
 
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
 static int g_force_kw = 2;
+static int g_pdl = 0;             // programmatic dependent launch for the decode-step kernels (opt-in: measured no gain)
 static int g_allow_cluster = 0;   // cluster (DSMEM) split-K reduction: opt-in, see gptq_debug_allow_cluster
 #ifdef GPTQ_SK_TIMING
 static long long *g_dbg = nullptr;
@@ -31,6 +33,34 @@ static int sm_count() {
 		cached[dev] = n;
 	}
 	return cached[dev];
+}
+
+// Launch with optional programmatic stream serialisation (the kernel may start while its
+// predecessor drains; it calls pdl_wait() before touching dependent data) and optional cluster.
+template <typename... KArgs, typename... Args>
+static int launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_y, Args &&...args) {
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = grid;
+	cfg.blockDim = block;
+	cfg.dynamicSmemBytes = smem;
+	cfg.stream = stream;
+	cudaLaunchAttribute attr[2];
+	int n = 0;
+	if (g_pdl) {
+		attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+		attr[n].val.programmaticStreamSerializationAllowed = 1;
+		++n;
+	}
+	if (cluster_y > 1) {
+		attr[n].id = cudaLaunchAttributeClusterDimension;
+		attr[n].val.clusterDim.x = 1;
+		attr[n].val.clusterDim.y = (unsigned)cluster_y;
+		attr[n].val.clusterDim.z = 1;
+		++n;
+	}
+	cfg.attrs = attr;
+	cfg.numAttrs = n;
+	return cuda_status(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...));
 }
 
 // ---- small utility kernels ----------------------------------------------------------------
@@ -201,6 +231,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 	p.chunks_per_split = cps;
 	p.splitk = eff;
 	p.cluster = (g_allow_cluster && eff > 1 && eff <= 8) ? 1 : 0;
+	p.pdl = g_pdl;
 	p.nstage = best_stage;
 	kw = best_kw;
 	grid = dim3(tiles, p.splitk, 1);
@@ -225,23 +256,7 @@ static int launch_skinny_inst(const CUtensorMap &tm0, const CUtensorMap &tm1, co
 	auto k = skinny_kernel<KW, NSTREAM, M8, SPG_T, EPI>;
 	static bool ready[64] = {false};
 	if (int rc = ensure_smem_attr(k, ready)) return rc;
-	if (p.cluster) {
-		cudaLaunchConfig_t cfg = {};
-		cfg.gridDim = grid;
-		cfg.blockDim = dim3(KW * 128, 1, 1);
-		cfg.dynamicSmemBytes = smem;
-		cfg.stream = stream;
-		cudaLaunchAttribute attr[1];
-		attr[0].id = cudaLaunchAttributeClusterDimension;
-		attr[0].val.clusterDim.x = 1;
-		attr[0].val.clusterDim.y = (unsigned)p.splitk;
-		attr[0].val.clusterDim.z = 1;
-		cfg.attrs = attr;
-		cfg.numAttrs = 1;
-		return cuda_status(cudaLaunchKernelEx(&cfg, k, tm0, tm1, p));
-	}
-	k<<<grid, KW * 128, smem, stream>>>(tm0, tm1, p);
-	return cuda_status(cudaGetLastError());
+	return launch_ex(k, grid, dim3(KW * 128, 1, 1), smem, stream, p.cluster ? p.splitk : 1, tm0, tm1, p);
 }
 
 template <int NSTREAM, int EPI>
@@ -350,6 +365,7 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
 void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
 void gptq_debug_allow_cluster(int on) { g_allow_cluster = on ? 1 : 0; }
+void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 #ifdef GPTQ_SK_TIMING
 void gptq_debug_set_timing(long long *buf) { g_dbg = buf; }
 #endif
@@ -421,8 +437,7 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 	p.scale = scale; p.heads = heads; p.splits = splits;
 	p.ws_ticket = reinterpret_cast<int *>(workspace);
 	p.ws_partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + AT_TICKET_BYTES);
-	attn_decode_kernel<<<dim3(splits, heads, batch), AT_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
-	return cuda_status(cudaGetLastError());
+	return launch_ex(attn_decode_kernel, dim3(splits, heads, batch), dim3(AT_THREADS, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), 1, p);
 }
 
 int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_t ldy, int M, int K, float eps, gptq_stream_t stream) {
@@ -430,8 +445,8 @@ int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_
 	if (K % 8 != 0) return GPTQ_ERR_SHAPE;
 	if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || ldx % 8 || ldy % 8) return GPTQ_ERR_ALIGN;
 	if (M == 0) return GPTQ_OK;
-	rmsnorm_kernel<<<M, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((const __half *)x, ldx, (const __half *)weight, (__half *)y, ldy, K, eps);
-	return cuda_status(cudaGetLastError());
+	return launch_ex(rmsnorm_kernel, dim3(M, 1, 1), dim3(256, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), 1, (const __half *)x, (long long)ldx,
+					 (const __half *)weight, (__half *)y, (long long)ldy, K, eps);
 }
 
 size_t gptq_noalloc_scratch_bytes(int M, int K, int N, int groupsize) {

@@ -36,6 +36,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int grp = lane >> 3, sub = lane & 7;           // 4 key groups per warp, 8 lanes per key
+	pdl_trigger();
+	pdl_wait();                                          // q, the cache row of this step and pos come from earlier kernels
 	const int len = p.pos[b] + 1;
 	const int per = (len + p.splits - 1) / p.splits;
 	const int k_lo = split * per, k_hi = min(k_lo + per, len);
@@ -178,6 +180,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __half *__restrict__
 													  __half *__restrict__ y, long long ldy, int K, float eps) {
 	const int row = blockIdx.x, tid = threadIdx.x;
 	const __half *xr = x + (size_t)row * ldx;
+	pdl_trigger();
+	pdl_wait();
 	float ss = 0.f;
 	for (int k = tid * 8; k < K; k += 256 * 8) {
 		const uint4 v = *reinterpret_cast<const uint4 *>(xr + k);

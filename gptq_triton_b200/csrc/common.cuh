@@ -73,6 +73,13 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void *p) {
 	return r;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------
+// pdl_trigger(): lets the next kernel in the stream start its independent prologue early.
+// pdl_wait(): returns once every kernel this one depends on has completed and its writes are
+// visible; nothing produced by an earlier kernel may be touched before it.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + __expf(-x)); }
 
 // ---- host-side launch plumbing -------------------------------------------------

@@ -61,6 +61,7 @@ struct SkinnyParams {
 	int xs_stride;         // bytes between rows of the staged x slice
 	int xs_bytes;          // M * xs_stride rounded up to 128
 	int strip_groups;      // capacity (groups) of the zero / scale strips per stream
+	int pdl;               // 1: launched with programmatic stream serialisation (x is loaded after pdl_wait)
 	int cluster;           // 1: the split-K CTAs of a tile form a thread-block cluster and reduce over DSMEM
 	float *ws_partial;
 	int *ws_ticket;
@@ -274,10 +275,15 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	{
 		uint32_t z0[SB];
 		uint4 sv0[SB], v0[XB];
-		strip_load(tid, z0, sv0);
-		x_load(tid, v0);
+		pdl_trigger();
+		strip_load(tid, z0, sv0);                            // weights side: independent of earlier kernels
+		if (!p.pdl) x_load(tid, v0);                         // ahead of the prefetch burst in the memory queues
 		for (int s = 0; s < p.nstage; ++s) produce();        // weight prefetch: nstage chunks per warp
 		SK_STAMP(1);
+		if (p.pdl) {
+			pdl_wait();                                      // x, residual and the workspace come from earlier kernels
+			x_load(tid, v0);
+		}
 		strip_store(tid, z0, sv0);
 		x_store(tid, v0);
 		for (int base = tid + NT * SB; base < n_strip; base += NT * SB) {

@@ -247,10 +247,9 @@ class DecodeEngine:
 		logits = self.model.lm_head(h)
 		self.logits = logits
 		nxt = logits.argmax(-1)
-		# advance: next token, next position, unmask one more cache slot
+		# advance: next token, next position (the attention kernel reads the length from `pos`)
 		self.tok.copy_(nxt)
 		self.pos.add_(1)
-		self.mask.scatter_(3, self.pos.view(self.batch, 1, 1, 1).to(torch.int64), 0.0)
 
 	@torch.no_grad()
 	def step(self) -> torch.Tensor:
