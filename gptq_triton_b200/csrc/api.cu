@@ -17,6 +17,7 @@ thread_local int g_last_cuda_error = 0;
 
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
 static int g_force_kw = 2;
+static int g_use_tc = 1;          // tensor-core kernel for M > 16
 static int g_pdl = 0;             // programmatic dependent launch for the decode-step kernels (opt-in: measured no gain)
 static int g_allow_cluster = 0;   // cluster (DSMEM) split-K reduction: opt-in, see gptq_debug_allow_cluster
 #ifdef GPTQ_SK_TIMING
@@ -131,10 +132,6 @@ static size_t skinny_ws_bytes(int M, int N, int nstream) {
 	const size_t tiles = (size_t)(N + SK_BN - 1) / SK_BN;
 	return SK_TICKET_BYTES + tiles * SK_MAX_SPLITK * nstream * (size_t)std::min(M, 16) * SK_BN * sizeof(float);
 }
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-								  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-								  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn tensor_map_encoder() {
 	static EncodeTiledFn fn = nullptr;
@@ -366,6 +363,7 @@ void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
 void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
 void gptq_debug_allow_cluster(int on) { g_allow_cluster = on ? 1 : 0; }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+void gptq_debug_use_tc(int on) { g_use_tc = on ? 1 : 0; }
 #ifdef GPTQ_SK_TIMING
 void gptq_debug_set_timing(long long *buf) { g_dbg = buf; }
 #endif
@@ -396,7 +394,7 @@ int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, c
 		p.y = (__half *)y; p.ldy = ldy;
 		return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, workspace, workspace_bytes, st);
 	}
-	if (fast && tc_shape_ok(M, K, N, groupsize)) {
+	if (fast && !perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};
 		a.x = (const __half *)x; a.ldx = ldx; a.qw0 = qweight; a.qz0 = qzeros; a.sc0 = (const __half *)scales;
 		a.perm = perm; a.M = M; a.K = K; a.N = N; a.groupsize = groupsize;
@@ -513,7 +511,7 @@ int gptq_gateup_silu(const void *x, const int32_t *gate_qweight, const int32_t *
 		p.y = (__half *)y; p.ldy = ldy;
 		return launch_skinny<2, EPI_SILU>(p, gate_qweight, up_qweight, workspace, workspace_bytes, st);
 	}
-	if (fast && tc_shape_ok(M, K, N, groupsize)) {
+	if (fast && !perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};
 		a.x = (const __half *)x; a.ldx = ldx;
 		a.qw0 = gate_qweight; a.qz0 = gate_qzeros; a.sc0 = (const __half *)gate_scales;
@@ -561,7 +559,7 @@ int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, 
 		p.kv_sp = kv_stride_pos; p.tokens_per_batch = tokens_per_batch; p.hidden = hidden;
 		return launch_skinny<1, EPI_ROPE>(p, qweight, nullptr, workspace, workspace_bytes, st);
 	}
-	if (tc_shape_ok(M, K, N, groupsize)) {
+	if (!perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};
 		a.x = (const __half *)x; a.ldx = ldx; a.qw0 = qweight; a.qz0 = qzeros; a.sc0 = (const __half *)scales;
 		a.perm = perm; a.M = M; a.K = K; a.N = N; a.groupsize = groupsize;

@@ -1,9 +1,169 @@
+// Prefill-regime (M > 16) quantised matmul on the 5th-generation tensor cores of sm_100a.
+//
+// Y[M,N] = X[M,K] · deq(W)[K,N] with fp16 operands and fp32 accumulation in tensor memory.
+// One CTA computes a 128 (rows of X) x 128 (columns of W) tile; K advances in blocks of 64.
+//
+//   warp 0      TMA producer: X tile [128 x 64] fp16, K-major, 128-byte swizzle (one thread)
+//   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::f16, M=128 N=128 K=16, four per
+//               K-block (eight with the second weight stream), tcgen05.commit frees the stage;
+//               the warp also owns the TMEM allocation
+//   warps 2-5   dequantise: thread n owns weight column n of the tile; per K-block it reads 8
+//               packed words (coalesced over the warp), turns each into 8 fp16 weights
+//               (q - zero) * scale with ONE rounding — the fp16 weight of the
+//               dequantise-then-matmul path — and stores them as one 16-byte unit of the
+//               K-major, 128-byte-swizzled B tile; fence.proxy.async + mbarrier arrive.
+//               After the last K-block the same warps drain TMEM (tcgen05.ld 32x32b) and run
+//               the epilogue: bias/residual, SiLU(gate)*up, or rotary + scatter to Q/K/V.
+//
+// Every mbarrier wait is bounded; a wait that runs out sets a status word and the kernel
+// unwinds (TMEM is still released).
+#include <cuda.h>
+
 #include "qmm_tc.cuh"
 
 namespace gptq {
 
-bool tc_shape_ok(int, int, int, int) { return false; }
-size_t tc_ws_bytes(int, int) { return 0; }
-int tc_launch(const TcArgs &, int, void *, size_t, cudaStream_t) { return GPTQ_ERR_UNSUPPORTED; }
+namespace {
+
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 4;
+constexpr int TC_THREADS = 192;
+constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;            // 16 KB: one A or B stage
+constexpr uint32_t TC_SPIN = 1u << 24;
+
+// ---- tcgen05 / TMEM wrappers -------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+	asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+	asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+	asm volatile(
+		"{\n\t.reg .pred p;\n\t"
+		"setp.ne.b32 p, %4, 0;\n\t"
+		"tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+		:
+		: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+		: "memory");
+}
+// arrive on an mbarrier once all MMAs issued so far by this thread have completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i receives row (lane quarter base + i)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+	uint32_t *r = reinterpret_cast<uint32_t *>(v);
+	asm volatile(
+		"tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+		"%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+		: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+		  "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+		  "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+		  "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+		: "r"(taddr)
+		: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row
+// groups 1024 bytes apart (SBO), LBO unused (1), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+	uint64_t d = 0;
+	d |= (uint64_t)((addr & 0x3FFFFu) >> 4);            // start address, bits [0,14)
+	d |= (uint64_t)1 << 16;                             // leading byte offset (ignored for swizzled K-major)
+	d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset, bits [32,46)
+	d |= (uint64_t)1 << 46;                             // version
+	d |= (uint64_t)2 << 61;                             // layout type: SWIZZLE_128B
+	return d;
+}
+
+// Instruction descriptor: D fp32, A and B fp16, both K-major, N = 128, M = 128.
+constexpr uint32_t TC_IDESC = (1u << 4) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+
+struct TcParams {
+	TcArgs a;
+	int epi;
+	int *status;
+};
+
+}   // namespace
+
+// forward declaration of the kernel body (second half of this file)
+template <int NSTREAM, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const TcParams p);
+
+}   // namespace gptq
+
+#include "qmm_tc_kernel.inl"
+
+// ---- host side -------------------------------------------------------------------------------
+namespace gptq {
+
+EncodeTiledFn tensor_map_encoder();      // defined in api.cu
+
+bool tc_shape_ok(int M, int K, int N, int groupsize) {
+	return M > 16 && N % TC_BN == 0 && K % TC_BK == 0 && groupsize % TC_BK == 0 && K % groupsize == 0;
+}
+
+size_t tc_ws_bytes(int, int) { return 16384; }       // only the status word at its end is used
+
+static int x_tensor_map(const __half *x, int M, int K, long long ldx, CUtensorMap *out) {
+	EncodeTiledFn enc = tensor_map_encoder();
+	if (!enc) return GPTQ_ERR_CUDA;
+	cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+	cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+	cuuint32_t box[2] = {TC_BK, TC_BM};
+	cuuint32_t estr[2] = {1, 1};
+	CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+					 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	if (r != CUDA_SUCCESS) {
+		g_last_cuda_error = (int)r;
+		return GPTQ_ERR_CUDA;
+	}
+	return GPTQ_OK;
+}
+
+template <int NSTREAM, int EPI>
+static int tc_launch_inst(const CUtensorMap &tmx, const TcParams &p, dim3 grid, cudaStream_t stream) {
+	auto k = tc_kernel<NSTREAM, EPI>;
+	const size_t smem = (size_t)(1 + NSTREAM) * TC_STAGES * TC_TILE_BYTES + 256;
+	static bool ready[64] = {false};
+	int dev = 0;
+	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GPTQ_ERR_CUDA;
+	if (!ready[dev]) {
+		cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+		if (e != cudaSuccess) return cuda_status(e);
+		ready[dev] = true;
+	}
+	k<<<grid, TC_THREADS, smem, stream>>>(tmx, p);
+	return cuda_status(cudaGetLastError());
+}
+
+int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaStream_t stream) {
+	if (a.perm) return GPTQ_ERR_UNSUPPORTED;
+	if (!workspace || ws_bytes < 16384) return GPTQ_ERR_WORKSPACE;
+	if (a.ldx % 8 != 0) return GPTQ_ERR_ALIGN;
+	alignas(64) CUtensorMap tmx;
+	if (int rc = x_tensor_map(a.x, a.M, a.K, a.ldx, &tmx)) return rc;
+	TcParams p;
+	p.a = a;
+	p.epi = epi;
+	p.status = reinterpret_cast<int *>(workspace) + (16384 / 4 - 1);
+	dim3 grid(a.N / TC_BN, (a.M + TC_BM - 1) / TC_BM, 1);
+	switch (epi) {
+		case TC_EPI_PLAIN: return tc_launch_inst<1, TC_EPI_PLAIN>(tmx, p, grid, stream);
+		case TC_EPI_SILU: return tc_launch_inst<2, TC_EPI_SILU>(tmx, p, grid, stream);
+		case TC_EPI_ROPE: return tc_launch_inst<1, TC_EPI_ROPE>(tmx, p, grid, stream);
+	}
+	return GPTQ_ERR_INVALID;
+}
 
 }   // namespace gptq

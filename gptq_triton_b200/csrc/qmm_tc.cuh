@@ -1,6 +1,8 @@
 // Prefill-regime (M > 16) quantised matmul on the tcgen05 tensor cores.
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace gptq {
@@ -26,6 +28,10 @@ struct TcArgs {
 	long long q_stride_m, kv_sb, kv_st, kv_sh, kv_sp;
 	int tokens_per_batch, hidden;
 };
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+								  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+								  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 bool tc_shape_ok(int M, int K, int N, int groupsize);
 size_t tc_ws_bytes(int M, int N);

@@ -1,0 +1,247 @@
+// Body of the tcgen05 prefill kernel; included by qmm_tc.cu.
+namespace gptq {
+
+template <int NSTREAM, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const TcParams p) {
+	extern __shared__ __align__(1024) unsigned char smem[];
+	constexpr int S = TC_STAGES;
+	constexpr uint32_t TMEM_COLS = NSTREAM * TC_BN;          // 128 or 256 fp32 columns
+	const TcArgs &a = p.a;
+
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	const int n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM;
+	const int nkb = a.K / TC_BK;
+
+	unsigned char *sA = smem;                                              // [S][16 KB]
+	unsigned char *sB = smem + S * TC_TILE_BYTES;                          // [NSTREAM][S][16 KB]
+	uint64_t *bars = reinterpret_cast<uint64_t *>(sB + NSTREAM * S * TC_TILE_BYTES);
+	const uint32_t bar_full_a = smem_u32(bars), bar_full_b = smem_u32(bars + S), bar_empty = smem_u32(bars + 2 * S);
+	const uint32_t bar_acc = smem_u32(bars + 3 * S);
+	uint32_t *s_tmem = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+	volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem + 1);
+
+	if (tid == 0) {
+		for (int s = 0; s < S; ++s) {
+			mbar_init(bar_full_a + 8 * s, 1);
+			mbar_init(bar_full_b + 8 * s, 128);
+			mbar_init(bar_empty + 8 * s, 1);
+		}
+		mbar_init(bar_acc, 1);
+		*s_abort = 0;
+		fence_mbar_init();
+		tma_prefetch_desc(&tmx);
+	}
+	if (warp == 1) {                       // the MMA warp owns tensor memory
+		tmem_alloc(smem_u32(s_tmem), TMEM_COLS);
+		tmem_relinquish();
+	}
+	tc_fence_before();
+	__syncthreads();
+	tc_fence_after();
+	const uint32_t tmem_base = *s_tmem;
+
+	auto fail = [&]() {
+		*s_abort = 1;
+		atomicExch(p.status, 3);           // 3: a wait inside the tensor-core kernel ran out
+	};
+
+	if (warp == 0) {
+		// ---------------- TMA producer: X tiles ----------------
+		if (lane == 0) {
+			for (int kb = 0; kb < nkb && !*s_abort; ++kb) {
+				const int s = kb % S;
+				if (!mbar_wait_bounded(bar_empty + 8 * s, ((kb / S) & 1) ^ 1, TC_SPIN)) { fail(); break; }
+				mbar_arrive_expect_tx(bar_full_a + 8 * s, TC_TILE_BYTES);
+				tma_load_2d(smem_u32(sA + s * TC_TILE_BYTES), &tmx, kb * TC_BK, m0, bar_full_a + 8 * s);
+			}
+		}
+	} else if (warp == 1) {
+		// ---------------- MMA issuer ----------------
+		if (lane == 0) {
+			for (int kb = 0; kb < nkb && !*s_abort; ++kb) {
+				const int s = kb % S;
+				const uint32_t ph = (kb / S) & 1;
+				if (!mbar_wait_bounded(bar_full_a + 8 * s, ph, TC_SPIN) || !mbar_wait_bounded(bar_full_b + 8 * s, ph, TC_SPIN)) { fail(); break; }
+				tc_fence_after();
+				const uint32_t a_addr = smem_u32(sA + s * TC_TILE_BYTES);
+#pragma unroll
+				for (int st = 0; st < NSTREAM; ++st) {
+					const uint32_t b_addr = smem_u32(sB + (st * S + s) * TC_TILE_BYTES);
+#pragma unroll
+					for (int k = 0; k < TC_BK / 16; ++k)
+						umma_f16(tmem_base + st * TC_BN, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), TC_IDESC,
+								 (kb > 0 || k > 0) ? 1u : 0u);
+				}
+				umma_commit(bar_empty + 8 * s);          // stage free once these MMAs have read it
+			}
+			umma_commit(bar_acc);                        // accumulators complete
+		}
+	} else {
+		// ---------------- dequantise producers, then epilogue ----------------
+		const int wt = tid - 64;                          // weight column of the tile owned by this thread
+		const int n = n0 + wt;
+		const int nz = a.N >> 3, zsh = (n & 7) * 4;
+		const uint32_t b_row = (uint32_t)((wt >> 3) * 1024 + (wt & 7) * 128);
+		uint32_t cur[NSTREAM][8], nxt[NSTREAM][8];
+		auto load_block = [&](int kb, uint32_t(&dst)[NSTREAM][8]) {
+#pragma unroll
+			for (int st = 0; st < NSTREAM; ++st) {
+				const int32_t *qw = (NSTREAM == 2 && st) ? a.qw1 : a.qw0;
+#pragma unroll
+				for (int r = 0; r < 8; ++r) dst[st][r] = (uint32_t)__ldg(qw + (size_t)(kb * 8 + r) * a.N + n);
+			}
+		};
+		load_block(0, nxt);
+		int g_cur = -1;
+		uint32_t ZE[NSTREAM], ZO[NSTREAM], S2[NSTREAM];
+		bool ok = true;
+		for (int kb = 0; kb < nkb; ++kb) {
+#pragma unroll
+			for (int st = 0; st < NSTREAM; ++st)
+#pragma unroll
+				for (int r = 0; r < 8; ++r) cur[st][r] = nxt[st][r];
+			if (kb + 1 < nkb) load_block(kb + 1, nxt);
+			const int g = (kb * TC_BK) / a.groupsize;
+			if (g != g_cur) {
+				g_cur = g;
+#pragma unroll
+				for (int st = 0; st < NSTREAM; ++st) {
+					const int32_t *qz = (NSTREAM == 2 && st) ? a.qz1 : a.qz0;
+					const __half *sc = (NSTREAM == 2 && st) ? a.sc1 : a.sc0;
+					const uint32_t zz = ((((uint32_t)__ldg(qz + (size_t)g * nz + (n >> 3))) >> zsh) & 0xFu) + 1u;
+					ZE[st] = (0x6400u + zz) * 0x00010001u;            // half2(1024 + zero)
+					ZO[st] = (0xD400u + (zz << 4)) * 0x00010001u;     // half2(-(64 + zero))
+					S2[st] = (uint32_t)__half_as_ushort(__ldg(sc + (size_t)g * a.N + n)) * 0x00010001u;
+				}
+			}
+			const int s = kb % S;
+			if (*s_abort || !mbar_wait_bounded(bar_empty + 8 * s, ((kb / S) & 1) ^ 1, TC_SPIN)) { ok = false; break; }
+#pragma unroll
+			for (int st = 0; st < NSTREAM; ++st) {
+				unsigned char *bst = sB + (st * S + s) * TC_TILE_BYTES + b_row;
+#pragma unroll
+				for (int r = 0; r < 8; ++r) {
+					const uint32_t w = cur[st][r], w8 = w >> 8;
+					const uint32_t p04 = h2_mul(h2_sub(lop3_and_or(w, MASK_LO, MAGIC_1024), ZE[st]), S2[st]);
+					const uint32_t p15 = h2_mul(h2_fma(lop3_and_or(w, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[st]), S2[st]);
+					const uint32_t p26 = h2_mul(h2_sub(lop3_and_or(w8, MASK_LO, MAGIC_1024), ZE[st]), S2[st]);
+					const uint32_t p37 = h2_mul(h2_fma(lop3_and_or(w8, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[st]), S2[st]);
+					uint4 o;                                   // natural k order k0..k7
+					o.x = __byte_perm(p04, p15, 0x5410);
+					o.y = __byte_perm(p26, p37, 0x5410);
+					o.z = __byte_perm(p04, p15, 0x7632);
+					o.w = __byte_perm(p26, p37, 0x7632);
+					*reinterpret_cast<uint4 *>(bst + ((r ^ (wt & 7)) << 4)) = o;
+				}
+			}
+			fence_proxy_async();                               // generic-proxy stores -> visible to the tensor core
+			mbar_arrive(bar_full_b + 8 * s);
+		}
+		if (!ok) fail();
+
+		// ---------------- epilogue: TMEM -> registers -> global ----------------
+		if (ok && !*s_abort && mbar_wait_bounded(bar_acc, 0, TC_SPIN)) {
+			tc_fence_after();
+			const int q = warp & 3;                             // TMEM lane quarter this warp may read
+			const int row = m0 + q * 32 + lane;
+			const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+			const bool live = row < a.M;
+			if (EPI == TC_EPI_ROPE) {
+				const int section = n0 / a.hidden, head = (n0 - section * a.hidden) >> 7;
+				const int pos = live ? a.pos[row] : 0;
+				__half *dst = nullptr;
+				if (live) {
+					if (section == 0) {
+						dst = a.q_out + (size_t)row * a.q_stride_m + head * 128;
+					} else {
+						const int bi = row / a.tokens_per_batch, ti = row - bi * a.tokens_per_batch;
+						dst = (section == 1 ? a.k_out : a.v_out) + (size_t)bi * a.kv_sb + (size_t)ti * a.kv_st + (size_t)head * a.kv_sh +
+							  (size_t)pos * a.kv_sp;
+					}
+				}
+#pragma unroll 1
+				for (int hc = 0; hc < 2; ++hc) {
+					float lo[32], hi[32];
+					tmem_ld32(t_row + hc * 32, lo);
+					tmem_ld32(t_row + 64 + hc * 32, hi);
+					tmem_ld_wait();
+					if (live) {
+						const __half *ct = a.cos_t + (size_t)pos * 128, *stb = a.sin_t + (size_t)pos * 128;
+#pragma unroll
+						for (int j = 0; j < 32; j += 2) {
+							const int d = hc * 32 + j;
+							float o1[2], o2[2];
+#pragma unroll
+							for (int e = 0; e < 2; ++e) {
+								const float x1 = lo[j + e], x2 = hi[j + e];
+								if (section < 2) {
+									o1[e] = x1 * __half2float(ct[d + e]) - x2 * __half2float(stb[d + e]);
+									o2[e] = x2 * __half2float(ct[d + e + 64]) + x1 * __half2float(stb[d + e + 64]);
+								} else {
+									o1[e] = x1;
+									o2[e] = x2;
+								}
+							}
+							*reinterpret_cast<__half2 *>(dst + d) = __floats2half2_rn(o1[0], o1[1]);
+							*reinterpret_cast<__half2 *>(dst + d + 64) = __floats2half2_rn(o2[0], o2[1]);
+						}
+					}
+				}
+			} else {
+#pragma unroll 1
+				for (int c = 0; c < TC_BN / 32; ++c) {
+					float v[32], u[32];
+					tmem_ld32(t_row + c * 32, v);
+					if (EPI == TC_EPI_SILU) tmem_ld32(t_row + TC_BN + c * 32, u);
+					tmem_ld_wait();
+					if (live) {
+						const int nc = n0 + c * 32;
+#pragma unroll
+						for (int j = 0; j < 32; j += 8) {
+							float o[8];
+#pragma unroll
+							for (int e = 0; e < 8; ++e) o[e] = (EPI == TC_EPI_SILU) ? silu_f32(v[j + e]) * u[j + e] : v[j + e];
+							if (EPI == TC_EPI_PLAIN) {
+								if (a.bias) {
+									const uint4 bv = *reinterpret_cast<const uint4 *>(a.bias + nc + j);
+									const __half2 *bh = reinterpret_cast<const __half2 *>(&bv);
+#pragma unroll
+									for (int e = 0; e < 4; ++e) {
+										const float2 f = __half22float2(bh[e]);
+										o[2 * e] += f.x;
+										o[2 * e + 1] += f.y;
+									}
+								}
+								if (a.residual) {
+									const uint4 rv = *reinterpret_cast<const uint4 *>(a.residual + (size_t)row * a.ldr + nc + j);
+									const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+									for (int e = 0; e < 4; ++e) {
+										const float2 f = __half22float2(rh[e]);
+										o[2 * e] += f.x;
+										o[2 * e + 1] += f.y;
+									}
+								}
+							}
+							uint4 ov;
+							__half2 *oh = reinterpret_cast<__half2 *>(&ov);
+#pragma unroll
+							for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(o[2 * e], o[2 * e + 1]);
+							*reinterpret_cast<uint4 *>(a.y + (size_t)row * a.ldy + nc + j) = ov;
+						}
+					}
+				}
+			}
+		} else if (ok) {
+			fail();
+		}
+	}
+	tc_fence_before();
+	__syncthreads();
+	if (warp == 1) {
+		__syncwarp();
+		tmem_dealloc(tmem_base, TMEM_COLS);
+	}
+}
+
+}   // namespace gptq

@@ -58,6 +58,9 @@ def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin,
 		S = k.shape[2]
 		sb, st, sh, sp = n_heads * S * head_dim, 0, S * head_dim, head_dim
 	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available
+	if M > DECODE_MAX_M and perm is not None and prefill_kernel_available(M, K, 3 * hidden, groupsize):
+		a = a.view(M, K)[:, perm.long()].contiguous().view(b, t, K)
+		perm = None
 	if M > DECODE_MAX_M and not prefill_kernel_available(M, K, 3 * hidden, groupsize):
 		y = dequant_matmul(a.view(M, K), groupsize, qweight, scales, qzeros, None, perm).float().view(b, t, 3, n_heads, head_dim)
 		c = cos[pos.long()].float().view(b, t, 1, head_dim)

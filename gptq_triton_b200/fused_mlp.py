@@ -55,7 +55,10 @@ def gateup_silu(groupsize: int, a: torch.Tensor, gate_qweight, gate_scales, gate
 	if M == 0:
 		return c.view(a.shape[:-1] + (N,))
 	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available
-	if M > DECODE_MAX_M and not prefill_kernel_available(M, K, N, groupsize):
+	if M > DECODE_MAX_M and perm is not None and g_idx is None and prefill_kernel_available(M, K, N, groupsize):
+		x = x[:, perm.long()].contiguous()
+		perm = None
+	if M > DECODE_MAX_M and (g_idx is not None or not prefill_kernel_available(M, K, N, groupsize)):
 		g = dequant_matmul(x, groupsize, gate_qweight, gate_scales, gate_qzeros, g_idx, perm).float()
 		u = dequant_matmul(x, groupsize, up_qweight, up_scales, up_qzeros, g_idx, perm).float()
 		c = (torch.nn.functional.silu(g) * u).half()

@@ -8,6 +8,7 @@ unchanged; an optional `g_idx` buffer (int32 [K], group of each input row) adds 
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -63,9 +64,14 @@ def act_order_rows(qweight: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
 DECODE_MAX_M = 16
 
 
+USE_TENSOR_CORE_KERNEL = os.environ.get('GPTQ_B200_TC', '1') != '0'
+
+
 def prefill_kernel_available(M: int, K: int, N: int, groupsize: int) -> bool:
-	"""True when the tensor-core (tcgen05) kernel of the library covers this shape."""
-	return False
+	"""True when the tensor-core (tcgen05) kernel of the library covers this shape
+	(the rule of tc_shape_ok in csrc/qmm_tc.cu)."""
+	gs = K if groupsize == -1 else groupsize
+	return USE_TENSOR_CORE_KERNEL and M > DECODE_MAX_M and N % 128 == 0 and K % 64 == 0 and gs % 64 == 0 and K % gs == 0
 
 
 def dequant_matmul(x2d: torch.Tensor, groupsize: int, qweight, scales, qzeros, g_idx=None, perm=None) -> torch.Tensor:
@@ -104,7 +110,10 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 	if residual is not None:
 		assert residual.is_contiguous() and residual.numel() == M * N
 		res = residual.view(M, N)
-	if M > DECODE_MAX_M and not prefill_kernel_available(M, K, N, groupsize):
+	if M > DECODE_MAX_M and perm is not None and g_idx is None and prefill_kernel_available(M, K, N, groupsize):
+		x = x[:, perm.long()].contiguous()      # the tensor-core kernel reads x through TMA: gather once up front
+		perm = None
+	if M > DECODE_MAX_M and (g_idx is not None or not prefill_kernel_available(M, K, N, groupsize)):
 		c = dequant_matmul(x, groupsize, qweight, scales, qzeros, g_idx, perm)
 		if bias is not None:
 			c = c + bias

@@ -430,3 +430,55 @@ def test_rmsnorm_kernel(G, M, K):
 	xd = x.double()
 	ref = xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + 1e-6) * w.double()
 	assert O.max_rel_err(y, ref.float()) <= 1e-3
+
+
+# ---------------------------------------------------------------- prefill (M > 16): tcgen05 kernel
+TC_SHAPES = [(256, 256, 128), (512, 384, 128), (4096, 512, -1), (1408, 256, 64), (2048, 1024, 128)]
+
+
+@pytest.mark.parametrize('K,N,gs', TC_SHAPES)
+@pytest.mark.parametrize('M', [17, 128, 200, 512])
+def test_qmatmul_prefill_tensor_core(G, M, K, N, gs):
+	from gptq_triton_b200 import _lib
+	from gptq_triton_b200.quant_linear import prefill_kernel_available
+	assert prefill_kernel_available(M, K, N, gs)
+	t = synth(K, N, gs, seed=K + N + M, bias=True)
+	x = acts((M, K), seed=M)
+	res = acts((M, N), seed=M + 1)
+	y = G.qmatmul(gs, x.cuda(), t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda(), bias=t['bias'].cuda(), residual=res.cuda())
+	r32 = O.qmatmul_r32(x, t['qweight'], t['qzeros'], t['scales'], gs, bias=t['bias'], residual=res)
+	assert O.max_rel_err(y, r32) <= TOL
+	torch.cuda.synchronize()
+	assert _lib.kernel_status() == 0
+
+
+@pytest.mark.parametrize('M', [64, 300])
+def test_prefill_act_order_and_gateup_and_rope(G, M):
+	from gptq_triton_b200.quant_linear import _act_order_perm, act_order_rows
+	K, N, gs = 512, 256, 128
+	t = synth(K, N, gs, seed=5, act_order=True)
+	x = acts((M, K), seed=6)
+	d = {k: dev(v) for k, v in t.items() if isinstance(v, torch.Tensor)}
+	perm = _act_order_perm(d['g_idx'], gs)
+	y = G.qmatmul(gs, x.cuda(), act_order_rows(d['qweight'], perm), d['scales'], d['qzeros'], perm=perm)
+	assert O.max_rel_err(y, O.qmatmul_r32(x, t['qweight'], t['qzeros'], t['scales'], gs, g_idx=t['g_idx'])) <= TOL
+	# fused gate/up
+	g, u = synth(K, N, gs, 41), synth(K, N, gs, 42)
+	h = G.gateup_silu(gs, x.cuda(), g['qweight'].cuda(), g['scales'].cuda(), g['qzeros'].cuda(), u['qweight'].cuda(), u['scales'].cuda(), u['qzeros'].cuda())
+	rh = O.gateup_silu_r32(x, (g['qweight'], g['qzeros'], g['scales']), (u['qweight'], u['qzeros'], u['scales']), gs)
+	assert O.max_rel_err(h, rh) <= TOL
+	# fused QKV + rotary, prefill layout [1, M, K]
+	H, D = 2, 128
+	w = synth(K, 3 * H * D, gs, seed=61)
+	pos = torch.arange(M).unsqueeze(0)
+	cos, sin = O.rope_tables(D, 512)
+	q, k, v = G.qkv_rope(gs, x.view(1, M, K).cuda(), w['qweight'].cuda(), w['scales'].cuda(), w['qzeros'].cuda(), cos.cuda(), sin.cuda(), pos.cuda(), H, D)
+	rq, rk, rv = O.qkv_rope_r32(x.view(1, M, K), w['qweight'], w['qzeros'], w['scales'], gs, cos, sin, pos, H, D)
+	assert O.max_rel_err(q.transpose(1, 2), rq) <= TOL and O.max_rel_err(k.transpose(1, 2), rk) <= TOL and O.max_rel_err(v.transpose(1, 2), rv) <= TOL
+	# ... and straight into a KV cache
+	S = 512
+	kc = torch.zeros((1, H, S, D), dtype=torch.float16, device='cuda')
+	vc = torch.zeros_like(kc)
+	G.qkv_rope(gs, x.view(1, M, K).cuda(), w['qweight'].cuda(), w['scales'].cuda(), w['qzeros'].cuda(), cos.cuda(), sin.cuda(), pos.cuda(), H, D, kv_cache=(kc, vc))
+	assert O.max_rel_err(kc[0, :, :M].transpose(0, 1), rk[0]) <= TOL and O.max_rel_err(vc[0, :, :M].transpose(0, 1), rv[0]) <= TOL
+	assert bool((kc[0, :, M:] == 0).all())
