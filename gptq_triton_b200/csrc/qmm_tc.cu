@@ -7,8 +7,9 @@
 //   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::f16, M=128 N=128 K=16, four per
 //               K-block (eight with the second weight stream), tcgen05.commit frees the stage;
 //               the warp also owns the TMEM allocation
-//   warps 2-5   dequantise: thread n owns weight column n of the tile; per K-block it reads 8
-//               packed words (coalesced over the warp), turns each into 8 fp16 weights
+//   warps 2-17  dequantise, four groups of four warps, group j serving K-blocks j, j+4, ...: a
+//               thread owns a weight column of the tile, reads the K-block's 8 packed words of that
+//               column from a TMA-fed ring, turns each into 8 fp16 weights
 //               (q - zero) * scale with ONE rounding — the fp16 weight of the
 //               dequantise-then-matmul path — and stores them as one 16-byte unit of the
 //               K-major, 128-byte-swizzled B tile; fence.proxy.async + mbarrier arrive.
@@ -26,7 +27,8 @@ namespace gptq {
 namespace {
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 4;
-constexpr int TC_THREADS = 192;
+constexpr int TC_WORKERS = 512;                             // dequantise / epilogue threads: 4 groups x 4 warps
+constexpr int TC_THREADS = 64 + TC_WORKERS;
 constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;            // 16 KB: one A or B stage
 constexpr uint32_t TC_SPIN = 1u << 24;
 
@@ -92,13 +94,17 @@ struct TcParams {
 	TcArgs a;
 	int epi;
 	int *status;
+#ifdef GPTQ_TC_TIMING
+	long long *dbg;
+#endif
 };
 
 }   // namespace
 
 // forward declaration of the kernel body (second half of this file)
 template <int NSTREAM, int EPI>
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const TcParams p);
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw0,
+														   const __grid_constant__ CUtensorMap tmw1, const TcParams p);
 
 }   // namespace gptq
 
@@ -108,6 +114,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 namespace gptq {
 
 EncodeTiledFn tensor_map_encoder();      // defined in api.cu
+#ifdef GPTQ_TC_TIMING
+long long *g_tc_dbg = nullptr;
+extern "C" void gptq_debug_set_tc_timing(long long *b) { g_tc_dbg = b; }
+#endif
 
 bool tc_shape_ok(int M, int K, int N, int groupsize) {
 	return M > 16 && N % TC_BN == 0 && K % TC_BK == 0 && groupsize % TC_BK == 0 && K % groupsize == 0;
@@ -131,10 +141,34 @@ static int x_tensor_map(const __half *x, int M, int K, long long ldx, CUtensorMa
 	return GPTQ_OK;
 }
 
+// Tensor map over packed weights int32 [K/8, N]: box 128 columns x 8 packed rows (one K-block), no swizzle.
+static int w_tensor_map(const int32_t *qw, int K, int N, CUtensorMap *out) {
+	EncodeTiledFn enc = tensor_map_encoder();
+	if (!enc) return GPTQ_ERR_CUDA;
+	cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 8)};
+	cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+	cuuint32_t box[2] = {TC_BN, 8};
+	cuuint32_t estr[2] = {1, 1};
+	CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t *>(qw), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+					 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	if (r != CUDA_SUCCESS) {
+		g_last_cuda_error = (int)r;
+		return GPTQ_ERR_CUDA;
+	}
+	return GPTQ_OK;
+}
+
 template <int NSTREAM, int EPI>
 static int tc_launch_inst(const CUtensorMap &tmx, const TcParams &p, dim3 grid, cudaStream_t stream) {
 	auto k = tc_kernel<NSTREAM, EPI>;
-	const size_t smem = (size_t)(1 + NSTREAM) * TC_STAGES * TC_TILE_BYTES + 256;
+	const size_t smem = (size_t)(1 + NSTREAM) * TC_STAGES * TC_TILE_BYTES + (size_t)(NSTREAM == 2 ? 4 : 8) * NSTREAM * 8 * TC_BN * 4 + 512;
+	alignas(64) CUtensorMap tmw0, tmw1;
+	if (int rc = w_tensor_map(p.a.qw0, p.a.K, p.a.N, &tmw0)) return rc;
+	if (NSTREAM == 2) {
+		if (int rc = w_tensor_map(p.a.qw1, p.a.K, p.a.N, &tmw1)) return rc;
+	} else {
+		tmw1 = tmw0;
+	}
 	static bool ready[64] = {false};
 	int dev = 0;
 	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GPTQ_ERR_CUDA;
@@ -143,7 +177,7 @@ static int tc_launch_inst(const CUtensorMap &tmx, const TcParams &p, dim3 grid, 
 		if (e != cudaSuccess) return cuda_status(e);
 		ready[dev] = true;
 	}
-	k<<<grid, TC_THREADS, smem, stream>>>(tmx, p);
+	k<<<grid, TC_THREADS, smem, stream>>>(tmx, tmw0, tmw1, p);
 	return cuda_status(cudaGetLastError());
 }
 
@@ -157,6 +191,9 @@ int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaSt
 	p.a = a;
 	p.epi = epi;
 	p.status = reinterpret_cast<int *>(workspace) + (16384 / 4 - 1);
+#ifdef GPTQ_TC_TIMING
+	p.dbg = g_tc_dbg;
+#endif
 	dim3 grid(a.N / TC_BN, (a.M + TC_BM - 1) / TC_BM, 1);
 	switch (epi) {
 		case TC_EPI_PLAIN: return tc_launch_inst<1, TC_EPI_PLAIN>(tmx, p, grid, stream);

@@ -2,10 +2,13 @@
 namespace gptq {
 
 template <int NSTREAM, int EPI>
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const TcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw0,
+																 const __grid_constant__ CUtensorMap tmw1, const TcParams p) {
 	extern __shared__ __align__(1024) unsigned char smem[];
 	constexpr int S = TC_STAGES;
 	constexpr uint32_t TMEM_COLS = NSTREAM * TC_BN;          // 128 or 256 fp32 columns
+	constexpr int PS = (NSTREAM == 2) ? 4 : 8;               // stages of the packed-weight ring
+	constexpr int PW_BYTES = 8 * TC_BN * 4;                  // packed tile of one K-block: 8 words x 128 columns
 	const TcArgs &a = p.a;
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -14,19 +17,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 
 	unsigned char *sA = smem;                                              // [S][16 KB]
 	unsigned char *sB = smem + S * TC_TILE_BYTES;                          // [NSTREAM][S][16 KB]
-	uint64_t *bars = reinterpret_cast<uint64_t *>(sB + NSTREAM * S * TC_TILE_BYTES);
+	unsigned char *sW = sB + NSTREAM * S * TC_TILE_BYTES;                  // [PS][NSTREAM][4 KB] packed words
+	uint64_t *bars = reinterpret_cast<uint64_t *>(sW + PS * NSTREAM * PW_BYTES);
 	const uint32_t bar_full_a = smem_u32(bars), bar_full_b = smem_u32(bars + S), bar_empty = smem_u32(bars + 2 * S);
 	const uint32_t bar_acc = smem_u32(bars + 3 * S);
-	uint32_t *s_tmem = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+	const uint32_t bar_full_w = smem_u32(bars + 3 * S + 1), bar_empty_w = smem_u32(bars + 3 * S + 1 + PS);
+	uint32_t *s_tmem = reinterpret_cast<uint32_t *>(bars + 3 * S + 1 + 2 * PS);
 	volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem + 1);
 
 	if (tid == 0) {
 		for (int s = 0; s < S; ++s) {
 			mbar_init(bar_full_a + 8 * s, 1);
-			mbar_init(bar_full_b + 8 * s, 128);
+			mbar_init(bar_full_b + 8 * s, 128);               // the 128 threads of the group that owns the stage
 			mbar_init(bar_empty + 8 * s, 1);
 		}
 		mbar_init(bar_acc, 1);
+		for (int s = 0; s < PS; ++s) {
+			mbar_init(bar_full_w + 8 * s, 1);
+			mbar_init(bar_empty_w + 8 * s, 4);                // one arrival per warp of the consuming group
+		}
 		*s_abort = 0;
 		fence_mbar_init();
 		tma_prefetch_desc(&tmx);
@@ -46,9 +55,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 	};
 
 	if (warp == 0) {
-		// ---------------- TMA producer: X tiles ----------------
+		// ---------------- TMA producer: packed weight tiles (deep ring) and X tiles ----------------
 		if (lane == 0) {
+			int kw = 0;                           // next K-block of packed weights to request
+			auto feed_w = [&](int upto) -> bool {
+				for (; kw < upto && kw < nkb; ++kw) {
+					const int s = kw % PS;
+					if (!mbar_wait_bounded(bar_empty_w + 8 * s, ((kw / PS) & 1) ^ 1, TC_SPIN)) return false;
+					mbar_arrive_expect_tx(bar_full_w + 8 * s, NSTREAM * PW_BYTES);
+					tma_load_2d(smem_u32(sW + (s * NSTREAM) * PW_BYTES), &tmw0, n0, kw * 8, bar_full_w + 8 * s);
+					if (NSTREAM == 2) tma_load_2d(smem_u32(sW + (s * NSTREAM + 1) * PW_BYTES), &tmw1, n0, kw * 8, bar_full_w + 8 * s);
+				}
+				return true;
+			};
 			for (int kb = 0; kb < nkb && !*s_abort; ++kb) {
+				if (!feed_w(kb + PS)) { fail(); break; }
 				const int s = kb % S;
 				if (!mbar_wait_bounded(bar_empty + 8 * s, ((kb / S) & 1) ^ 1, TC_SPIN)) { fail(); break; }
 				mbar_arrive_expect_tx(bar_full_a + 8 * s, TC_TILE_BYTES);
@@ -61,7 +82,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 			for (int kb = 0; kb < nkb && !*s_abort; ++kb) {
 				const int s = kb % S;
 				const uint32_t ph = (kb / S) & 1;
-				if (!mbar_wait_bounded(bar_full_a + 8 * s, ph, TC_SPIN) || !mbar_wait_bounded(bar_full_b + 8 * s, ph, TC_SPIN)) { fail(); break; }
+#ifdef GPTQ_TC_TIMING
+				const long long t0 = clock64();
+#endif
+				if (!mbar_wait_bounded(bar_full_a + 8 * s, ph, TC_SPIN)) { fail(); break; }
+#ifdef GPTQ_TC_TIMING
+				const long long t1 = clock64();
+#endif
+				if (!mbar_wait_bounded(bar_full_b + 8 * s, ph, TC_SPIN)) { fail(); break; }
+#ifdef GPTQ_TC_TIMING
+				if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) { atomicAdd((unsigned long long *)p.dbg + 0, (unsigned long long)(t1 - t0)); atomicAdd((unsigned long long *)p.dbg + 1, (unsigned long long)(clock64() - t1)); }
+#endif
 				tc_fence_after();
 				const uint32_t a_addr = smem_u32(sA + s * TC_TILE_BYTES);
 #pragma unroll
@@ -78,49 +109,78 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 		}
 	} else {
 		// ---------------- dequantise producers, then epilogue ----------------
-		const int wt = tid - 64;                          // weight column of the tile owned by this thread
+		// Four groups of 128 threads; group j dequantises K-blocks j, j+4, ... into B stage j, so the
+		// groups' barrier round trips and proxy fences overlap.  Thread -> weight column wt of the tile.
+		constexpr int RPT = 8, r0 = 0;
+		const int wt = (tid - 64) & (TC_BN - 1), grp = (tid - 64) / TC_BN;
 		const int n = n0 + wt;
 		const int nz = a.N >> 3, zsh = (n & 7) * 4;
 		const uint32_t b_row = (uint32_t)((wt >> 3) * 1024 + (wt & 7) * 128);
-		uint32_t cur[NSTREAM][8], nxt[NSTREAM][8];
-		auto load_block = [&](int kb, uint32_t(&dst)[NSTREAM][8]) {
+		uint32_t cur[NSTREAM][RPT];
+		// scale / zero of the current and of the next group (fetched one group ahead)
+		uint32_t ZE[NSTREAM], ZO[NSTREAM], S2[NSTREAM], zraw[NSTREAM];
+		unsigned short sraw[NSTREAM];
+		const int ngroups = a.K / a.groupsize;
+		auto fetch_group = [&](int g) {
 #pragma unroll
 			for (int st = 0; st < NSTREAM; ++st) {
-				const int32_t *qw = (NSTREAM == 2 && st) ? a.qw1 : a.qw0;
-#pragma unroll
-				for (int r = 0; r < 8; ++r) dst[st][r] = (uint32_t)__ldg(qw + (size_t)(kb * 8 + r) * a.N + n);
+				const int32_t *qz = (NSTREAM == 2 && st) ? a.qz1 : a.qz0;
+				const __half *sc = (NSTREAM == 2 && st) ? a.sc1 : a.sc0;
+				zraw[st] = (uint32_t)__ldg(qz + (size_t)g * nz + (n >> 3));
+				sraw[st] = __half_as_ushort(__ldg(sc + (size_t)g * a.N + n));
 			}
 		};
-		load_block(0, nxt);
+		fetch_group(min((grp * TC_BK) / a.groupsize, ngroups - 1));
 		int g_cur = -1;
-		uint32_t ZE[NSTREAM], ZO[NSTREAM], S2[NSTREAM];
 		bool ok = true;
-		for (int kb = 0; kb < nkb; ++kb) {
-#pragma unroll
-			for (int st = 0; st < NSTREAM; ++st)
-#pragma unroll
-				for (int r = 0; r < 8; ++r) cur[st][r] = nxt[st][r];
-			if (kb + 1 < nkb) load_block(kb + 1, nxt);
+		for (int kb = grp; kb < nkb; kb += S) {
 			const int g = (kb * TC_BK) / a.groupsize;
 			if (g != g_cur) {
 				g_cur = g;
 #pragma unroll
 				for (int st = 0; st < NSTREAM; ++st) {
-					const int32_t *qz = (NSTREAM == 2 && st) ? a.qz1 : a.qz0;
-					const __half *sc = (NSTREAM == 2 && st) ? a.sc1 : a.sc0;
-					const uint32_t zz = ((((uint32_t)__ldg(qz + (size_t)g * nz + (n >> 3))) >> zsh) & 0xFu) + 1u;
+					const uint32_t zz = ((zraw[st] >> zsh) & 0xFu) + 1u;
 					ZE[st] = (0x6400u + zz) * 0x00010001u;            // half2(1024 + zero)
 					ZO[st] = (0xD400u + (zz << 4)) * 0x00010001u;     // half2(-(64 + zero))
-					S2[st] = (uint32_t)__half_as_ushort(__ldg(sc + (size_t)g * a.N + n)) * 0x00010001u;
+					S2[st] = (uint32_t)sraw[st] * 0x00010001u;
 				}
 			}
+			{
+				const int g_next = ((kb + S) * TC_BK) / a.groupsize;      // group of this thread's next K-block
+				if (g_next < ngroups) fetch_group(g_next);                 // always: the registers then hold that group's data
+			}
+			{
+				const int ws = kb % PS;
+#ifdef GPTQ_TC_TIMING
+				const long long t0 = clock64();
+#endif
+				if (*s_abort || !mbar_wait_bounded(bar_full_w + 8 * ws, (kb / PS) & 1, TC_SPIN)) { ok = false; break; }
+#ifdef GPTQ_TC_TIMING
+				if (p.dbg && tid == 64 && blockIdx.x == 0 && blockIdx.y == 0) p.dbg[2] += clock64() - t0;
+#endif
+#pragma unroll
+				for (int st = 0; st < NSTREAM; ++st) {
+					const uint32_t *wp = reinterpret_cast<const uint32_t *>(sW + (ws * NSTREAM + st) * PW_BYTES) + wt;
+#pragma unroll
+					for (int r = 0; r < RPT; ++r) cur[st][r] = wp[(r0 + r) * TC_BN];
+				}
+				__syncwarp();
+				if (lane == 0) mbar_arrive(bar_empty_w + 8 * ws);
+			}
 			const int s = kb % S;
+#ifdef GPTQ_TC_TIMING
+			const long long t2 = clock64();
+#endif
 			if (*s_abort || !mbar_wait_bounded(bar_empty + 8 * s, ((kb / S) & 1) ^ 1, TC_SPIN)) { ok = false; break; }
+#ifdef GPTQ_TC_TIMING
+			const long long t3 = clock64();
+			if (p.dbg && tid == 64 && blockIdx.x == 0 && blockIdx.y == 0) p.dbg[3] += t3 - t2;
+#endif
 #pragma unroll
 			for (int st = 0; st < NSTREAM; ++st) {
 				unsigned char *bst = sB + (st * S + s) * TC_TILE_BYTES + b_row;
 #pragma unroll
-				for (int r = 0; r < 8; ++r) {
+				for (int r = 0; r < RPT; ++r) {
 					const uint32_t w = cur[st][r], w8 = w >> 8;
 					const uint32_t p04 = h2_mul(h2_sub(lop3_and_or(w, MASK_LO, MAGIC_1024), ZE[st]), S2[st]);
 					const uint32_t p15 = h2_mul(h2_fma(lop3_and_or(w, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[st]), S2[st]);
@@ -131,11 +191,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 					o.y = __byte_perm(p26, p37, 0x5410);
 					o.z = __byte_perm(p04, p15, 0x7632);
 					o.w = __byte_perm(p26, p37, 0x7632);
-					*reinterpret_cast<uint4 *>(bst + ((r ^ (wt & 7)) << 4)) = o;
+					*reinterpret_cast<uint4 *>(bst + (((r0 + r) ^ (wt & 7)) << 4)) = o;
 				}
 			}
+#ifdef GPTQ_TC_TIMING
+			const long long t4 = clock64();
+#endif
 			fence_proxy_async();                               // generic-proxy stores -> visible to the tensor core
 			mbar_arrive(bar_full_b + 8 * s);
+#ifdef GPTQ_TC_TIMING
+			if (p.dbg && tid == 64 && blockIdx.x == 0 && blockIdx.y == 0) { p.dbg[4] += t4 - t3; p.dbg[5] += clock64() - t4; }
+#endif
 		}
 		if (!ok) fail();
 
@@ -143,6 +209,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 		if (ok && !*s_abort && mbar_wait_bounded(bar_acc, 0, TC_SPIN)) {
 			tc_fence_after();
 			const int q = warp & 3;                             // TMEM lane quarter this warp may read
+			const int cq = (warp - 2) >> 2;                     // which 32-column chunk of the tile this warp drains
 			const int row = m0 + q * 32 + lane;
 			const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
 			const bool live = row < a.M;
@@ -160,7 +227,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 					}
 				}
 #pragma unroll 1
-				for (int hc = 0; hc < 2; ++hc) {
+				for (int hc = cq; hc < (cq < 2 ? cq + 1 : cq); ++hc) {
 					float lo[32], hi[32];
 					tmem_ld32(t_row + hc * 32, lo);
 					tmem_ld32(t_row + 64 + hc * 32, hi);
@@ -189,7 +256,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				}
 			} else {
 #pragma unroll 1
-				for (int c = 0; c < TC_BN / 32; ++c) {
+				for (int c = cq; c < cq + 1; ++c) {
 					float v[32], u[32];
 					tmem_ld32(t_row + c * 32, v);
 					if (EPI == TC_EPI_SILU) tmem_ld32(t_row + TC_BN + c * 32, u);
