@@ -165,14 +165,25 @@ def gpu_arm(args):
 	from gptq_triton_b200 import _lib
 	from gptq_triton_b200.llama import LlamaConfig
 
-	cfg = LlamaConfig.llama_7b()
+	from gptq_triton_b200 import tp
+	big = args.workload == 'llama65b-b16'
+	cfg = LlamaConfig.llama_65b() if big else LlamaConfig.llama_7b()
+	batch = 16 if big else 1
 	if args.layers:
 		cfg.num_hidden_layers = args.layers            # debugging aid only; the default is the full model
-	model = G.synthetic_quantized_llama(cfg, groupsize=GROUPSIZE, seed=1234 + rank, device=dev)
+	# N > 1: ONE model, tensor-parallel over the N GPUs (same seed on every rank, each keeps its shards)
+	if world > 1:
+		model = G.synthetic_quantized_llama(cfg, groupsize=GROUPSIZE, seed=1234, device=dev, fuse=False)
+		tp.shard_llama(model, rank, world)
+		G.make_quant_attn(model)
+		G.make_fused_mlp(model)
+		torch.cuda.empty_cache()
+	else:
+		model = G.synthetic_quantized_llama(cfg, groupsize=GROUPSIZE, seed=1234, device=dev)
 	max_seq = PROMPT + args.warmup + 2 * args.steps + 16
-	engine = G.DecodeEngine(model, batch=1, max_seq=max_seq, use_graph=True)
-	gen = torch.Generator().manual_seed(99 + rank)
-	prompt = torch.randint(0, cfg.vocab_size, (1, PROMPT), generator=gen).to(dev)
+	engine = G.DecodeEngine(model, batch=batch, max_seq=max_seq, use_graph=not args.no_graph)
+	gen = torch.Generator().manual_seed(99)
+	prompt = torch.randint(0, cfg.vocab_size, (batch, PROMPT), generator=gen).to(dev)
 	engine.prefill(prompt)
 	torch.cuda.synchronize()
 
@@ -203,11 +214,11 @@ def gpu_arm(args):
 	if world > 1:
 		dist.all_reduce(t, op=dist.ReduceOp.MAX)
 	ms = float(t.item())
-	tok_s = world * args.steps / (ms / 1e3)
+	tok_s = batch * args.steps / (ms / 1e3)            # every rank works on the same tokens (tensor parallel)
 
 	# ---- end to end through DecodeEngine.step(): token in from pinned host memory, token out ----
-	host_tok = torch.zeros((1, 1), dtype=torch.int64).pin_memory()
-	host_out = torch.zeros((1, 1), dtype=torch.int64).pin_memory()
+	host_tok = torch.zeros((batch, 1), dtype=torch.int64).pin_memory()
+	host_out = torch.zeros((batch, 1), dtype=torch.int64).pin_memory()
 	host_tok.copy_(engine.tok.cpu())
 	barrier()
 	t0 = time.perf_counter()
@@ -221,14 +232,14 @@ def gpu_arm(args):
 	t = torch.tensor([e2e_s], device=dev)
 	if world > 1:
 		dist.all_reduce(t, op=dist.ReduceOp.MAX)
-	e2e_tok_s = world * args.steps / float(t.item())
+	e2e_tok_s = batch * args.steps / float(t.item())
 
 	# ---- roofline of the dominant kernel: fused gate/up decode kernel, live, rotating weights ----
 	roof = None
 	status = None
 	if rank == 0:
 		layers = model.model.layers
-		x = torch.randn((1, 1, cfg.hidden_size), device=dev, dtype=torch.float16)
+		x = torch.randn((batch, 1, cfg.hidden_size), device=dev, dtype=torch.float16)
 		for l in layers[:4]:
 			l.mlp.intermediate(x)
 		torch.cuda.synchronize()
@@ -252,12 +263,12 @@ def gpu_arm(args):
 			k1.record(s)
 			s.synchronize()
 		us = k0.elapsed_time(k1) * 1e3 / (reps * len(layers))
-		K, N = cfg.hidden_size, cfg.intermediate_size
-		alg = 2 * quantised_bytes(K, N) + 2 * K + 2 * N           # two weight streams + x + y at M=1
+		K, N = cfg.hidden_size, int(layers[0].mlp.gate_proj_qweight.shape[1])      # N is this rank's share under tensor parallelism
+		alg = 2 * quantised_bytes(K, N) + batch * (2 * K + 2 * N)           # two weight streams + x + y
 		peak, which = measured_peaks()
 		ach = alg / us / 1e3
-		roof = {'bound': 'hbm', 'kernel': 'skinny_kernel<gate/up, SiLU epilogue> M=1 K=4096 N=11008', 'achieved': ach, 'peak': peak, 'unit': 'GB/s',
-				'frac': ach / peak, 'peak_source': which, 'us_per_launch': us, 'algorithmic_bytes': alg, 'traffic': 46.9e6}
+		roof = {'bound': 'hbm', 'kernel': 'skinny_kernel<gate/up, SiLU epilogue> M=%d K=%d N=%d' % (batch, K, N), 'achieved': ach, 'peak': peak, 'unit': 'GB/s',
+				'frac': ach / peak, 'peak_source': which, 'us_per_launch': us, 'algorithmic_bytes': alg, 'traffic': 46.96e6 if (world == 1 and not big) else None}
 		status = _lib.kernel_status(dev)
 
 	# ---- CPU baseline (rank 0, N=1 only) -----------------------------------------------------------
@@ -269,15 +280,15 @@ def gpu_arm(args):
 			   'sample': 'one 4096x4096 g128 projection at M=1 through the CPU oracle (1/%.0f of the quantised weights of a decode step), median of 5' % scale}
 
 	if rank == 0:
-		launches_per_step = 7 * cfg.num_hidden_layers + 1      # 4 quantised matmuls, attention, 2 RMSNorm per layer + final norm
+		launches_per_step = 7 * cfg.num_hidden_layers + 1      # per rank      # 4 quantised matmuls, attention, 2 RMSNorm per layer + final norm
 		line = {
 			'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
-			'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f16',
+			'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'strong' if world > 1 else 'weak', 'vs_baseline': None, 'dtype': 'f16',
 			'data': 'synthetic',
-			'config': {'workload': WORKLOAD, 'layers': cfg.num_hidden_layers, 'hidden': cfg.hidden_size, 'groupsize': GROUPSIZE,
-					   'parallelism': 'replicas x%d' % world if world > 1 else 'single GPU',
+			'config': {'workload': WORKLOAD if not big else 'llama65b-arch 4-bit g128 greedy decode, batch 16, 2048-token prompts', 'layers': cfg.num_hidden_layers, 'hidden': cfg.hidden_size, 'groupsize': GROUPSIZE,
+					   'parallelism': ('tp%d: QKV and gate/up by columns, o_proj and down by rows, one NCCL all-reduce after each' % world) if world > 1 else 'single GPU',
 					   'l2': 'inputs larger than L2: 3.6 GB of weights + KV cache are streamed every step'},
-			'e2e': {'value': e2e_tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 8, 'd2h_bytes_per_step': 8},
+			'e2e': {'value': e2e_tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 8 * batch, 'd2h_bytes_per_step': 8 * batch},
 			'gpu_launches': launches_per_step * args.steps,
 			'roofline': roof, 'cpu_baseline': cpu, 'clocks': clocks, 'kernel_status': status,
 		}
@@ -320,6 +331,8 @@ def main():
 	ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
 	ap.add_argument('--layers', type=int, default=0, help='debug: fewer decoder layers')
 	ap.add_argument('--no-cpu-baseline', action='store_true')
+	ap.add_argument('--workload', default='llama7b', choices=['llama7b', 'llama65b-b16'], help='llama65b-b16: 65B architecture, batch 16 (tensor-parallel runs)')
+	ap.add_argument('--no-graph', action='store_true', help='do not capture the decode step in a CUDA graph')
 	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down'], help='profiling aid: run 8 launches of one decode kernel and exit')
 	ap.add_argument('--m', type=int, default=1, help='batch rows for --kernel-case')
 	args = ap.parse_args()

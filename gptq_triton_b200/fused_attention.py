@@ -131,13 +131,14 @@ class QuantLlamaAttention(nn.Module):
 		super().__init__()
 		self.config = config
 		self.hidden_size = config.hidden_size
-		self.num_heads = config.num_attention_heads
-		self.head_dim = self.hidden_size // self.num_heads
+		self.head_dim = getattr(config, 'head_dim', None) or self.hidden_size // config.num_attention_heads
 		self.max_position_embeddings = config.max_position_embeddings
-		if (self.head_dim * self.num_heads) != self.hidden_size:
+		if (self.head_dim * config.num_attention_heads) != self.hidden_size:
 			raise ValueError(
 				f"hidden_size must be divisible by num_heads (got `hidden_size`: {self.hidden_size}"
-				f" and `num_heads`: {self.num_heads}).")
+				f" and `num_heads`: {config.num_attention_heads}).")
+		# heads held by THIS module: all of them, or this rank's share under tensor parallelism
+		self.num_heads = qkv_proj.outfeatures // (3 * self.head_dim)
 		self.qkv_proj = qkv_proj
 		self.o_proj = o_proj
 		self.rotary_emb = rotary_emb
@@ -198,7 +199,7 @@ class QuantLlamaAttention(nn.Module):
 				raise ValueError(f"Attention mask should be of size {(bsz, 1, q_len, kv_seq_len)}, but is {attention_mask.size()}")
 			attn_output = nn.functional.scaled_dot_product_attention(query_states, key_states, value_states, attn_mask=attention_mask)
 
-		attn_output = attn_output.transpose(1, 2).reshape(bsz, q_len, self.hidden_size)
+		attn_output = attn_output.transpose(1, 2).reshape(bsz, q_len, self.num_heads * self.head_dim)
 		attn_output = self.o_proj(attn_output)
 		return attn_output, attn_weights, past_key_value
 

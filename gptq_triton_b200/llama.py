@@ -22,6 +22,7 @@ import torch.nn.functional as F
 from .fused_attention import QuantLlamaAttention, attn_decode
 from .fused_attention import rmsnorm as rmsnorm_kernel
 from .fused_mlp import QuantLlamaMLP
+from .tp import all_reduce_
 
 
 @dataclass
@@ -174,16 +175,21 @@ class DecodeEngine:
 	QKV+rotary writing K/V into the cache, attention over the cache, o_proj + residual, RMSNorm,
 	fused gate/up, down_proj + residual), final norm, fp16 lm_head, argmax."""
 
-	def __init__(self, model: LlamaForCausalLM, batch: int, max_seq: int, use_graph: bool = True):
+	def __init__(self, model: LlamaForCausalLM, batch: int, max_seq: int, use_graph: bool = True, tp_group=None):
 		self.model = model
+		# tensor parallelism: the model holds this rank's shards (tp.shard_llama); partial sums of the
+		# row-parallel projections are all-reduced, the residual is added on rank 0 only
+		self.tp_group = tp_group
+		self.tp_rank = getattr(model, 'tp_rank', 0)
+		self.tp_world = getattr(model, 'tp_world', 1)
 		cfg = model.config
 		self.cfg = cfg
 		dev = model.lm_head.weight.device
 		self.device = dev
 		self.batch, self.max_seq = batch, max_seq
-		H, D = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads
 		for layer in model.model.layers:
 			assert isinstance(layer.self_attn, QuantLlamaAttention), 'run make_quant_attn first'
+		H, D = model.model.layers[0].self_attn.num_heads, cfg.hidden_size // cfg.num_attention_heads      # local heads
 		self.kcache = [torch.zeros((batch, H, max_seq, D), dtype=torch.float16, device=dev) for _ in model.model.layers]
 		self.vcache = [torch.zeros((batch, H, max_seq, D), dtype=torch.float16, device=dev) for _ in model.model.layers]
 		self.pos = torch.zeros((batch, 1), dtype=torch.int32, device=dev)          # position of the token being fed
@@ -210,14 +216,20 @@ class DecodeEngine:
 			k = self.kcache[i][:b, :, :kv_len]
 			v = self.vcache[i][:b, :, :kv_len]
 			o = F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask)
-			o = o.transpose(1, 2).reshape(h.shape)
-		h = attn.o_proj(o, residual=h)
+			o = o.transpose(1, 2).reshape(b, h.shape[1], -1)      # local heads x head_dim
+		res = h if self.tp_rank == 0 else None
+		h = attn.o_proj(o, residual=res)
+		if self.tp_world > 1:
+			all_reduce_(h, self.tp_group)
 		x = norm(h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.variance_epsilon)
 		mlp = layer.mlp
+		res = h if self.tp_rank == 0 else None
 		if isinstance(mlp, QuantLlamaMLP):
-			h = mlp(x, residual=h)
+			h = mlp(x, residual=res)
 		else:
-			h = h + mlp(x)
+			h = mlp(x) if res is None else res + mlp(x)
+		if self.tp_world > 1:
+			all_reduce_(h, self.tp_group)
 		return h
 
 	@torch.no_grad()
