@@ -292,9 +292,14 @@ def gpu_arm(args):
 			'gpu_launches': launches_per_step * args.steps,
 			'roofline': roof, 'cpu_baseline': cpu, 'clocks': clocks, 'kernel_status': status,
 		}
-		print(json.dumps(line))
+		print(json.dumps(line), flush=True)
 	if world > 1:
-		dist.destroy_process_group()
+		# Leave without tearing the communicator down: destroying a process group while CUDA graphs
+		# that captured its collectives are alive was seen to block until the NCCL watchdog fired.
+		torch.cuda.synchronize()
+		dist.barrier()
+		sys.stdout.flush()
+		os._exit(0)
 
 
 def kernel_case(args):

@@ -26,7 +26,7 @@ _SIGNATURES = {
 	'gptq_workspace_bytes': (c_size_t, [c_int, c_int, c_int]),
 	'gptq_qmatmul': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P, c_size_t, _P]),
 	'gptq_gateup_silu': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P, c_size_t, _P]),
-	'gptq_qkv_rope': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int64, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64,
+	'gptq_qkv_rope': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int64, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64,
 							  c_int, c_int, c_int, c_int, c_int, c_int64, _P, c_size_t, _P]),
 	'gptq_unpack_qweight': (c_int, [_P, _P, c_int, c_int, _P]),
 	'gptq_unpack_qzeros': (c_int, [_P, _P, c_int, c_int, _P]),
@@ -131,3 +131,9 @@ def kernel_status(device=None) -> int:
 		if device is None or dev == (device.index if isinstance(device, torch.device) else device):
 			st |= int(ws[16384 - 4:16384].view(torch.int32).item())
 	return st
+
+
+def clear_kernel_status():
+	"""Resets the status words (after the cause of a non-zero status has been dealt with)."""
+	for ws in _workspaces.values():
+		ws[16384 - 4:16384].zero_()

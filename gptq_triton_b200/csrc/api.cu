@@ -364,6 +364,21 @@ void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
 void gptq_debug_allow_cluster(int on) { g_allow_cluster = on ? 1 : 0; }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 void gptq_debug_use_tc(int on) { g_use_tc = on ? 1 : 0; }
+// Host-only: the launch plan of the decode kernel for a shape.  out[0..7] = split-K, K-warps, ring stages,
+// dynamic shared memory bytes, x-slice bytes, strip groups, chunks per split, cluster flag.
+int gptq_debug_plan(int M, int K, int N, int groupsize, int nstream, int *out) {
+	if (groupsize == -1) groupsize = K;
+	if (M <= 0 || M > 16 || !skinny_shape_ok(K, N, groupsize, nullptr)) return GPTQ_ERR_UNSUPPORTED;
+	SkinnyParams p = {};
+	p.M = M; p.K = K; p.N = N; p.groupsize = groupsize;
+	dim3 grid;
+	size_t smem;
+	int kw;
+	plan_skinny(p, nstream, kw, grid, smem);
+	out[0] = p.splitk; out[1] = kw; out[2] = p.nstage; out[3] = (int)smem; out[4] = p.xs_bytes; out[5] = p.strip_groups;
+	out[6] = p.chunks_per_split; out[7] = p.cluster;
+	return GPTQ_OK;
+}
 #ifdef GPTQ_SK_TIMING
 void gptq_debug_set_timing(long long *buf) { g_dbg = buf; }
 #endif
@@ -528,13 +543,13 @@ int gptq_gateup_silu(const void *x, const int32_t *gate_qweight, const int32_t *
 }
 
 int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
-				  const int32_t *perm, const void *cos, const void *sin, const int32_t *position_ids, void *q_out,
+				  const int32_t *perm, const void *cos, const void *sin, const int32_t *position_ids, int max_pos, void *q_out,
 				  int64_t q_stride_m, void *k_out, void *v_out, int tokens_per_batch, int64_t kv_stride_b,
 				  int64_t kv_stride_t, int64_t kv_stride_h, int64_t kv_stride_pos, int M, int K, int n_heads, int head_dim,
 				  int groupsize, int64_t ldx, void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
 	if (!x || !qweight || !qzeros || !scales || !cos || !sin || !position_ids || !q_out || !k_out || !v_out)
 		return GPTQ_ERR_INVALID;
-	if (M < 0 || K <= 0 || n_heads <= 0 || tokens_per_batch <= 0) return GPTQ_ERR_INVALID;
+	if (M < 0 || K <= 0 || n_heads <= 0 || tokens_per_batch <= 0 || max_pos <= 0) return GPTQ_ERR_INVALID;
 	if (head_dim != 128) return GPTQ_ERR_UNSUPPORTED;
 	if (groupsize == -1) groupsize = K;
 	if (groupsize <= 0) return GPTQ_ERR_INVALID;
@@ -556,7 +571,7 @@ int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, 
 		p.cos_t = (const __half *)cos; p.sin_t = (const __half *)sin; p.pos = position_ids;
 		p.q_out = (__half *)q_out; p.k_out = (__half *)k_out; p.v_out = (__half *)v_out;
 		p.q_stride_m = q_stride_m; p.kv_sb = kv_stride_b; p.kv_st = kv_stride_t; p.kv_sh = kv_stride_h;
-		p.kv_sp = kv_stride_pos; p.tokens_per_batch = tokens_per_batch; p.hidden = hidden;
+		p.kv_sp = kv_stride_pos; p.tokens_per_batch = tokens_per_batch; p.hidden = hidden; p.max_pos = max_pos;
 		return launch_skinny<1, EPI_ROPE>(p, qweight, nullptr, workspace, workspace_bytes, st);
 	}
 	if (!perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
@@ -566,7 +581,7 @@ int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, 
 		a.cos_t = (const __half *)cos; a.sin_t = (const __half *)sin; a.pos = position_ids;
 		a.q_out = (__half *)q_out; a.k_out = (__half *)k_out; a.v_out = (__half *)v_out;
 		a.q_stride_m = q_stride_m; a.kv_sb = kv_stride_b; a.kv_st = kv_stride_t; a.kv_sh = kv_stride_h;
-		a.kv_sp = kv_stride_pos; a.tokens_per_batch = tokens_per_batch; a.hidden = hidden;
+		a.kv_sp = kv_stride_pos; a.tokens_per_batch = tokens_per_batch; a.hidden = hidden; a.max_pos = max_pos;
 		return tc_launch(a, TC_EPI_ROPE, workspace, workspace_bytes, st);
 	}
 	return GPTQ_ERR_UNSUPPORTED;

@@ -38,7 +38,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	const int grp = lane >> 3, sub = lane & 7;           // 4 key groups per warp, 8 lanes per key
 	pdl_trigger();
 	pdl_wait();                                          // q, the cache row of this step and pos come from earlier kernels
-	const int len = p.pos[b] + 1;
+	// positions beyond the cache are never read: the length is clamped to the rows a head owns
+	const int len = max(1, min(p.pos[b] + 1, (int)(p.kv_stride_h / AT_D)));
 	const int per = (len + p.splits - 1) / p.splits;
 	const int k_lo = split * per, k_hi = min(k_lo + per, len);
 

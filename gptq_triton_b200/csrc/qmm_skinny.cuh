@@ -76,7 +76,7 @@ struct SkinnyParams {
 	const int32_t *pos;
 	__half *q_out, *k_out, *v_out;
 	long long q_stride_m, kv_sb, kv_st, kv_sh, kv_sp;
-	int tokens_per_batch, hidden;
+	int tokens_per_batch, hidden, max_pos;
 #ifdef GPTQ_SK_TIMING
 	long long *dbg;        // [cta][8] phase timestamps (debug builds only)
 	const int32_t *raw0, *raw1;
@@ -644,7 +644,11 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		for (int e = e_lo + tid; e < e_hi; e += NT) {
 			const int row = e >> 6, d = e & 63;
 			const float a = fin[(size_t)row * SK_BN + d], b = fin[(size_t)row * SK_BN + d + 64];
-			const int pos = p.pos[row];
+			int pos = p.pos[row];
+			if (pos < 0 || pos >= p.max_pos) {          // never index the tables / the cache out of range
+				atomicExch(p.ws_ticket + SK_STATUS_SLOT, 4);
+				pos = 0;
+			}
 			float o1 = a, o2 = b;
 			if (section < 2) {
 				const __half *ct = p.cos_t + (size_t)pos * 128, *st = p.sin_t + (size_t)pos * 128;

@@ -26,7 +26,7 @@ struct TcArgs {
 	const int32_t *pos;
 	__half *q_out, *k_out, *v_out;
 	long long q_stride_m, kv_sb, kv_st, kv_sh, kv_sp;
-	int tokens_per_batch, hidden;
+	int tokens_per_batch, hidden, max_pos;
 };
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,

@@ -215,7 +215,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 			const bool live = row < a.M;
 			if (EPI == TC_EPI_ROPE) {
 				const int section = n0 / a.hidden, head = (n0 - section * a.hidden) >> 7;
-				const int pos = live ? a.pos[row] : 0;
+				int pos = live ? a.pos[row] : 0;
+				if (pos < 0 || pos >= a.max_pos) {      // never index the tables / the cache out of range
+					atomicExch(p.status, 4);
+					pos = 0;
+				}
 				__half *dst = nullptr;
 				if (live) {
 					if (section == 0) {

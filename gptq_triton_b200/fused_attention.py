@@ -81,7 +81,7 @@ def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin,
 	ws = _lib.workspace(a.device, M, K, 3 * hidden)
 	rc = _lib.lib().gptq_qkv_rope(
 		_lib.ptr(a), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), None, _lib.ptr(perm),
-		_lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), _lib.ptr(q), hidden, _lib.ptr(k), _lib.ptr(v), t, sb, st, sh, sp,
+		_lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), min(cos.shape[0], (kv_cache[0].shape[2] if kv_cache is not None else cos.shape[0])), _lib.ptr(q), hidden, _lib.ptr(k), _lib.ptr(v), t, sb, st, sh, sp,
 		M, K, n_heads, head_dim, groupsize, K, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device))
 	_lib.check(rc, 'gptq_qkv_rope')
 	return q.transpose(1, 2), k, v
@@ -162,7 +162,8 @@ class QuantLlamaAttention(nn.Module):
 		bsz, q_len, _ = hidden_states.shape
 		if position_ids is None:
 			position_ids = torch.arange(q_len, device=hidden_states.device).unsqueeze(0).expand(bsz, q_len)
-		cos, sin = self.tables(hidden_states.device, 0)
+		need = 0 if kv_cache is None else kv_cache[0].shape[2]      # a static cache fixes the position range
+		cos, sin = self.tables(hidden_states.device, need)
 		return qkv_rope(self.qkv_proj.groupsize, hidden_states, qw, self.qkv_proj.scales, self.qkv_proj.qzeros, cos, sin,
 						position_ids, self.num_heads, self.head_dim, perm=perm, kv_cache=kv_cache)
 

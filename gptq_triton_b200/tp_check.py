@@ -51,10 +51,13 @@ def main():
 		del whole, part, e1, e2
 	flag = torch.tensor([1 if ok else 0], device=dev)
 	dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-	dist.destroy_process_group()
+	res = int(flag.item())
 	if rank == 0:
-		print('TP_CHECK', 'OK' if flag.item() else 'FAIL', flush=True)
-	sys.exit(0 if flag.item() else 1)
+		print('TP_CHECK', 'OK' if res else 'FAIL', flush=True)
+	torch.cuda.synchronize()
+	dist.barrier()
+	sys.stdout.flush()
+	os._exit(0 if res else 1)        # no communicator teardown while captured graphs are alive
 
 
 if __name__ == '__main__':

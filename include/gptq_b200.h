@@ -95,7 +95,9 @@ int gptq_gateup_silu(const void *x,
  * followed by the split into heads and apply_rotary_pos_emb on Q and K (:92-102),
  * done in the epilogue from the fp32 accumulators.
  *   cos, sin      fp16 [max_pos, head_dim] rotate-half tables
- *   position_ids  int32 [M]  (row m = b*tokens_per_batch + t)
+ *   position_ids  int32 [M]  (row m = b*tokens_per_batch + t); every value must be in [0, max_pos).
+ *                 A value outside is not dereferenced: the row is computed at position 0 and the
+ *                 status word at the end of the workspace's counter area is set to 4.
  *   q_out         fp16, element (m, h, d) at  m*q_stride_m + h*head_dim + d
  *   k_out, v_out  fp16, element (m, h, d) at
  *                   (m / tokens_per_batch)*kv_stride_b + (m % tokens_per_batch)*kv_stride_t
@@ -108,7 +110,7 @@ int gptq_gateup_silu(const void *x,
  */
 int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales,
                   const int32_t *g_idx, const int32_t *perm,
-                  const void *cos, const void *sin, const int32_t *position_ids,
+                  const void *cos, const void *sin, const int32_t *position_ids, int max_pos,
                   void *q_out, int64_t q_stride_m,
                   void *k_out, void *v_out, int tokens_per_batch,
                   int64_t kv_stride_b, int64_t kv_stride_t, int64_t kv_stride_h, int64_t kv_stride_pos,

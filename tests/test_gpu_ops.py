@@ -482,3 +482,22 @@ def test_prefill_act_order_and_gateup_and_rope(G, M):
 	G.qkv_rope(gs, x.view(1, M, K).cuda(), w['qweight'].cuda(), w['scales'].cuda(), w['qzeros'].cuda(), cos.cuda(), sin.cuda(), pos.cuda(), H, D, kv_cache=(kc, vc))
 	assert O.max_rel_err(kc[0, :, :M].transpose(0, 1), rk[0]) <= TOL and O.max_rel_err(vc[0, :, :M].transpose(0, 1), rv[0]) <= TOL
 	assert bool((kc[0, :, M:] == 0).all())
+
+
+def test_qkv_rope_position_outside_tables_is_reported_not_dereferenced(G):
+	"""A position beyond the cos/sin tables must not be used as an index: the kernel computes that
+	row at position 0 and raises status 4 in the workspace."""
+	from gptq_triton_b200 import _lib
+	H, D, K, gs = 2, 128, 256, 128
+	w = synth(K, 3 * H * D, gs, seed=5)
+	x = acts((1, 2, K), seed=6)
+	cos, sin = O.rope_tables(D, 16)
+	pos = torch.tensor([[3, 99]])                 # 99 >= 16 rows
+	assert _lib.kernel_status() == 0
+	q, k, v = G.qkv_rope(gs, x.cuda(), w['qweight'].cuda(), w['scales'].cuda(), w['qzeros'].cuda(), cos.cuda(), sin.cuda(), pos.cuda(), H, D)
+	torch.cuda.synchronize()
+	assert _lib.kernel_status() == 4
+	rq, _, _ = O.qkv_rope_r32(x, w['qweight'], w['qzeros'], w['scales'], gs, cos, sin, torch.tensor([[3, 0]]), H, D)
+	assert O.max_rel_err(q.transpose(1, 2), rq) <= TOL
+	_lib.clear_kernel_status()
+	assert _lib.kernel_status() == 0
