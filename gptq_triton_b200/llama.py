@@ -244,6 +244,7 @@ class DecodeEngine:
 			h = self._layer(i, h, pos, mask, t)
 		h = rmsnorm(h[:, -1:, :], self.model.model.norm.weight, self.model.model.norm.variance_epsilon)
 		logits = self.model.lm_head(h)
+		self.logits = logits
 		self.tok.copy_(logits.argmax(-1))
 		self.pos.fill_(t)
 		self.len_hint = t + 1
