@@ -87,8 +87,6 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 	return d;
 }
 
-// Instruction descriptor: D fp32, A and B fp16, both K-major, N = 128, M = 128.
-constexpr uint32_t TC_IDESC = (1u << 4) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
 
 struct TcParams {
 	TcArgs a;
@@ -102,7 +100,7 @@ struct TcParams {
 }   // namespace
 
 // forward declaration of the kernel body (second half of this file)
-template <int NSTREAM, int EPI>
+template <int NSTREAM, int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw0,
 														   const __grid_constant__ CUtensorMap tmw1, const TcParams p);
 
@@ -114,6 +112,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 namespace gptq {
 
 EncodeTiledFn tensor_map_encoder();      // defined in api.cu
+int g_tc_wide = 1;
+extern "C" void gptq_debug_tc_wide(int on) { g_tc_wide = on ? 1 : 0; }
 #ifdef GPTQ_TC_TIMING
 long long *g_tc_dbg = nullptr;
 extern "C" void gptq_debug_set_tc_timing(long long *b) { g_tc_dbg = b; }
@@ -141,13 +141,13 @@ static int x_tensor_map(const __half *x, int M, int K, long long ldx, CUtensorMa
 	return GPTQ_OK;
 }
 
-// Tensor map over packed weights int32 [K/8, N]: box 128 columns x 8 packed rows (one K-block), no swizzle.
-static int w_tensor_map(const int32_t *qw, int K, int N, CUtensorMap *out) {
+// Tensor map over packed weights int32 [K/8, N]: box bn columns x 8 packed rows (one K-block), no swizzle.
+static int w_tensor_map(const int32_t *qw, int K, int N, int bn, CUtensorMap *out) {
 	EncodeTiledFn enc = tensor_map_encoder();
 	if (!enc) return GPTQ_ERR_CUDA;
 	cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 8)};
 	cuuint64_t strides[1] = {(cuuint64_t)N * 4};
-	cuuint32_t box[2] = {TC_BN, 8};
+	cuuint32_t box[2] = {(cuuint32_t)bn, 8};
 	cuuint32_t estr[2] = {1, 1};
 	CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t *>(qw), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
 					 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -158,14 +158,15 @@ static int w_tensor_map(const int32_t *qw, int K, int N, CUtensorMap *out) {
 	return GPTQ_OK;
 }
 
-template <int NSTREAM, int EPI>
-static int tc_launch_inst(const CUtensorMap &tmx, const TcParams &p, dim3 grid, cudaStream_t stream) {
-	auto k = tc_kernel<NSTREAM, EPI>;
-	const size_t smem = (size_t)(1 + NSTREAM) * TC_STAGES * TC_TILE_BYTES + (size_t)(NSTREAM == 2 ? 4 : 8) * NSTREAM * 8 * TC_BN * 4 + 512;
+template <int NSTREAM, int EPI, int BN>
+static int tc_launch_inst(const CUtensorMap &tmx, const TcParams &p, cudaStream_t stream) {
+	auto k = tc_kernel<NSTREAM, EPI, BN>;
+	constexpr int PS = (NSTREAM * BN == 256) ? 4 : 8;
+	const size_t smem = (size_t)TC_STAGES * (TC_TILE_BYTES + NSTREAM * BN * TC_BK * 2) + (size_t)PS * NSTREAM * 8 * BN * 4 + 512;
 	alignas(64) CUtensorMap tmw0, tmw1;
-	if (int rc = w_tensor_map(p.a.qw0, p.a.K, p.a.N, &tmw0)) return rc;
+	if (int rc = w_tensor_map(p.a.qw0, p.a.K, p.a.N, BN, &tmw0)) return rc;
 	if (NSTREAM == 2) {
-		if (int rc = w_tensor_map(p.a.qw1, p.a.K, p.a.N, &tmw1)) return rc;
+		if (int rc = w_tensor_map(p.a.qw1, p.a.K, p.a.N, BN, &tmw1)) return rc;
 	} else {
 		tmw1 = tmw0;
 	}
@@ -177,6 +178,7 @@ static int tc_launch_inst(const CUtensorMap &tmx, const TcParams &p, dim3 grid, 
 		if (e != cudaSuccess) return cuda_status(e);
 		ready[dev] = true;
 	}
+	dim3 grid(p.a.N / BN, (p.a.M + TC_BM - 1) / TC_BM, 1);
 	k<<<grid, TC_THREADS, smem, stream>>>(tmx, tmw0, tmw1, p);
 	return cuda_status(cudaGetLastError());
 }
@@ -194,11 +196,14 @@ int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaSt
 #ifdef GPTQ_TC_TIMING
 	p.dbg = g_tc_dbg;
 #endif
-	dim3 grid(a.N / TC_BN, (a.M + TC_BM - 1) / TC_BM, 1);
+	// 256-column tiles (one N = 256 MMA per K step reads the X tile once for twice the work) when N allows
+	int dev = 0, sms = 148;
+	if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+	const bool wide = g_tc_wide && (a.N % 256 == 0) && (a.N / 256) * ((a.M + TC_BM - 1) / TC_BM) >= sms;      // else more, narrower CTAs
 	switch (epi) {
-		case TC_EPI_PLAIN: return tc_launch_inst<1, TC_EPI_PLAIN>(tmx, p, grid, stream);
-		case TC_EPI_SILU: return tc_launch_inst<2, TC_EPI_SILU>(tmx, p, grid, stream);
-		case TC_EPI_ROPE: return tc_launch_inst<1, TC_EPI_ROPE>(tmx, p, grid, stream);
+		case TC_EPI_PLAIN: return wide ? tc_launch_inst<1, TC_EPI_PLAIN, 256>(tmx, p, stream) : tc_launch_inst<1, TC_EPI_PLAIN, 128>(tmx, p, stream);
+		case TC_EPI_SILU: return tc_launch_inst<2, TC_EPI_SILU, 128>(tmx, p, stream);
+		case TC_EPI_ROPE: return wide ? tc_launch_inst<1, TC_EPI_ROPE, 256>(tmx, p, stream) : tc_launch_inst<1, TC_EPI_ROPE, 128>(tmx, p, stream);
 	}
 	return GPTQ_ERR_INVALID;
 }

@@ -1,23 +1,27 @@
 // Body of the tcgen05 prefill kernel; included by qmm_tc.cu.
 namespace gptq {
 
-template <int NSTREAM, int EPI>
+template <int NSTREAM, int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw0,
 																 const __grid_constant__ CUtensorMap tmw1, const TcParams p) {
 	extern __shared__ __align__(1024) unsigned char smem[];
 	constexpr int S = TC_STAGES;
-	constexpr uint32_t TMEM_COLS = NSTREAM * TC_BN;          // 128 or 256 fp32 columns
-	constexpr int PS = (NSTREAM == 2) ? 4 : 8;               // stages of the packed-weight ring
-	constexpr int PW_BYTES = 8 * TC_BN * 4;                  // packed tile of one K-block: 8 words x 128 columns
+	static_assert(NSTREAM * BN <= 256, "one accumulator set of at most 256 TMEM columns");
+	constexpr uint32_t TMEM_COLS = NSTREAM * BN;             // 128 or 256 fp32 columns
+	constexpr int PS = (NSTREAM * BN == 256) ? 4 : 8;        // stages of the packed-weight ring
+	constexpr int PW_BYTES = 8 * BN * 4;                     // packed tile of one K-block: 8 words x BN columns
+	constexpr int B_TILE = BN * TC_BK * 2;                   // dequantised B stage: BN rows x 128 bytes
+	constexpr int CPT = BN / 128;                            // weight columns per dequantise thread
+	constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);   // D fp32, A/B fp16 K-major, N = BN, M = 128
 	const TcArgs &a = p.a;
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-	const int n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM;
+	const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TC_BM;
 	const int nkb = a.K / TC_BK;
 
 	unsigned char *sA = smem;                                              // [S][16 KB]
 	unsigned char *sB = smem + S * TC_TILE_BYTES;                          // [NSTREAM][S][16 KB]
-	unsigned char *sW = sB + NSTREAM * S * TC_TILE_BYTES;                  // [PS][NSTREAM][4 KB] packed words
+	unsigned char *sW = sB + NSTREAM * S * B_TILE;                         // [PS][NSTREAM][PW_BYTES] packed words
 	uint64_t *bars = reinterpret_cast<uint64_t *>(sW + PS * NSTREAM * PW_BYTES);
 	const uint32_t bar_full_a = smem_u32(bars), bar_full_b = smem_u32(bars + S), bar_empty = smem_u32(bars + 2 * S);
 	const uint32_t bar_acc = smem_u32(bars + 3 * S);
@@ -97,13 +101,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				const uint32_t a_addr = smem_u32(sA + s * TC_TILE_BYTES);
 #pragma unroll
 				for (int st = 0; st < NSTREAM; ++st) {
-					const uint32_t b_addr = smem_u32(sB + (st * S + s) * TC_TILE_BYTES);
+					const uint32_t b_addr = smem_u32(sB + (st * S + s) * B_TILE);
 #pragma unroll
 					for (int k = 0; k < TC_BK / 16; ++k)
-						umma_f16(tmem_base + st * TC_BN, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), TC_IDESC,
+						umma_f16(tmem_base + st * BN, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), IDESC,
 								 (kb > 0 || k > 0) ? 1u : 0u);
 				}
+#ifdef GPTQ_TC_TIMING
+				const long long t5 = clock64();
+#endif
 				umma_commit(bar_empty + 8 * s);          // stage free once these MMAs have read it
+#ifdef GPTQ_TC_TIMING
+				if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) { p.dbg[6] += t5 - t1; p.dbg[7] += clock64() - t5; }
+#endif
 			}
 			umma_commit(bar_acc);                        // accumulators complete
 		}
@@ -112,22 +122,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 		// Four groups of 128 threads; group j dequantises K-blocks j, j+4, ... into B stage j, so the
 		// groups' barrier round trips and proxy fences overlap.  Thread -> weight column wt of the tile.
 		constexpr int RPT = 8, r0 = 0;
-		const int wt = (tid - 64) & (TC_BN - 1), grp = (tid - 64) / TC_BN;
-		const int n = n0 + wt;
-		const int nz = a.N >> 3, zsh = (n & 7) * 4;
+		const int wt = (tid - 64) & 127, grp = (tid - 64) >> 7;         // columns wt (+128 when BN = 256)
+		const int nz = a.N >> 3, zsh = (wt & 7) * 4;
 		const uint32_t b_row = (uint32_t)((wt >> 3) * 1024 + (wt & 7) * 128);
-		uint32_t cur[NSTREAM][RPT];
+		// a "unit" is one weight column of one stream: NU = NSTREAM * CPT units per thread
+		constexpr int NU = NSTREAM * CPT;
+		uint32_t cur[NU][RPT];
 		// scale / zero of the current and of the next group (fetched one group ahead)
-		uint32_t ZE[NSTREAM], ZO[NSTREAM], S2[NSTREAM], zraw[NSTREAM];
-		unsigned short sraw[NSTREAM];
+		uint32_t ZE[NU], ZO[NU], S2[NU], zraw[NU];
+		unsigned short sraw[NU];
 		const int ngroups = a.K / a.groupsize;
 		auto fetch_group = [&](int g) {
 #pragma unroll
-			for (int st = 0; st < NSTREAM; ++st) {
+			for (int u = 0; u < NU; ++u) {
+				const int st = u / CPT, n = n0 + wt + 128 * (u % CPT);
 				const int32_t *qz = (NSTREAM == 2 && st) ? a.qz1 : a.qz0;
 				const __half *sc = (NSTREAM == 2 && st) ? a.sc1 : a.sc0;
-				zraw[st] = (uint32_t)__ldg(qz + (size_t)g * nz + (n >> 3));
-				sraw[st] = __half_as_ushort(__ldg(sc + (size_t)g * a.N + n));
+				zraw[u] = (uint32_t)__ldg(qz + (size_t)g * nz + (n >> 3));
+				sraw[u] = __half_as_ushort(__ldg(sc + (size_t)g * a.N + n));
 			}
 		};
 		fetch_group(min((grp * TC_BK) / a.groupsize, ngroups - 1));
@@ -138,11 +150,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 			if (g != g_cur) {
 				g_cur = g;
 #pragma unroll
-				for (int st = 0; st < NSTREAM; ++st) {
-					const uint32_t zz = ((zraw[st] >> zsh) & 0xFu) + 1u;
-					ZE[st] = (0x6400u + zz) * 0x00010001u;            // half2(1024 + zero)
-					ZO[st] = (0xD400u + (zz << 4)) * 0x00010001u;     // half2(-(64 + zero))
-					S2[st] = (uint32_t)sraw[st] * 0x00010001u;
+				for (int u = 0; u < NU; ++u) {
+					const uint32_t zz = ((zraw[u] >> zsh) & 0xFu) + 1u;
+					ZE[u] = (0x6400u + zz) * 0x00010001u;            // half2(1024 + zero)
+					ZO[u] = (0xD400u + (zz << 4)) * 0x00010001u;     // half2(-(64 + zero))
+					S2[u] = (uint32_t)sraw[u] * 0x00010001u;
 				}
 			}
 			{
@@ -159,10 +171,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				if (p.dbg && tid == 64 && blockIdx.x == 0 && blockIdx.y == 0) p.dbg[2] += clock64() - t0;
 #endif
 #pragma unroll
-				for (int st = 0; st < NSTREAM; ++st) {
-					const uint32_t *wp = reinterpret_cast<const uint32_t *>(sW + (ws * NSTREAM + st) * PW_BYTES) + wt;
+				for (int u = 0; u < NU; ++u) {
+					const uint32_t *wp = reinterpret_cast<const uint32_t *>(sW + (ws * NSTREAM + u / CPT) * PW_BYTES) + wt + 128 * (u % CPT);
 #pragma unroll
-					for (int r = 0; r < RPT; ++r) cur[st][r] = wp[(r0 + r) * TC_BN];
+					for (int r = 0; r < RPT; ++r) cur[u][r] = wp[(r0 + r) * BN];
 				}
 				__syncwarp();
 				if (lane == 0) mbar_arrive(bar_empty_w + 8 * ws);
@@ -177,15 +189,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 			if (p.dbg && tid == 64 && blockIdx.x == 0 && blockIdx.y == 0) p.dbg[3] += t3 - t2;
 #endif
 #pragma unroll
-			for (int st = 0; st < NSTREAM; ++st) {
-				unsigned char *bst = sB + (st * S + s) * TC_TILE_BYTES + b_row;
+			for (int u = 0; u < NU; ++u) {
+				// row (wt + 128j) of the B tile: 8-row groups of 1024 bytes, 16 groups per 128 rows
+				unsigned char *bst = sB + ((u / CPT) * S + s) * B_TILE + b_row + (u % CPT) * 16384;
 #pragma unroll
 				for (int r = 0; r < RPT; ++r) {
-					const uint32_t w = cur[st][r], w8 = w >> 8;
-					const uint32_t p04 = h2_mul(h2_sub(lop3_and_or(w, MASK_LO, MAGIC_1024), ZE[st]), S2[st]);
-					const uint32_t p15 = h2_mul(h2_fma(lop3_and_or(w, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[st]), S2[st]);
-					const uint32_t p26 = h2_mul(h2_sub(lop3_and_or(w8, MASK_LO, MAGIC_1024), ZE[st]), S2[st]);
-					const uint32_t p37 = h2_mul(h2_fma(lop3_and_or(w8, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[st]), S2[st]);
+					const uint32_t w = cur[u][r], w8 = w >> 8;
+					const uint32_t p04 = h2_mul(h2_sub(lop3_and_or(w, MASK_LO, MAGIC_1024), ZE[u]), S2[u]);
+					const uint32_t p15 = h2_mul(h2_fma(lop3_and_or(w, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[u]), S2[u]);
+					const uint32_t p26 = h2_mul(h2_sub(lop3_and_or(w8, MASK_LO, MAGIC_1024), ZE[u]), S2[u]);
+					const uint32_t p37 = h2_mul(h2_fma(lop3_and_or(w8, MASK_HI, MAGIC_1024), 0x2C002C00u, ZO[u]), S2[u]);
 					uint4 o;                                   // natural k order k0..k7
 					o.x = __byte_perm(p04, p15, 0x5410);
 					o.y = __byte_perm(p26, p37, 0x5410);
@@ -214,7 +227,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 			const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
 			const bool live = row < a.M;
 			if (EPI == TC_EPI_ROPE) {
-				const int section = n0 / a.hidden, head = (n0 - section * a.hidden) >> 7;
+				// the tile holds BN/128 heads; warp group cq takes head cq>>1, rotary half cq&1
+				const int head_local = cq >> 1;
+				const int ncol = n0 + head_local * 128;
+				const int section = ncol / a.hidden, head = (ncol - section * a.hidden) >> 7;
 				int pos = live ? a.pos[row] : 0;
 				if (pos < 0 || pos >= a.max_pos) {      // never index the tables / the cache out of range
 					atomicExch(p.status, 4);
@@ -230,11 +246,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 							  (size_t)pos * a.kv_sp;
 					}
 				}
+				const uint32_t t_head = t_row + head_local * 128;
 #pragma unroll 1
-				for (int hc = cq; hc < (cq < 2 ? cq + 1 : cq); ++hc) {
+				for (int hc = (cq & 1); hc < ((cq < 2 * (BN / 128)) ? (cq & 1) + 1 : (cq & 1)); ++hc) {
 					float lo[32], hi[32];
-					tmem_ld32(t_row + hc * 32, lo);
-					tmem_ld32(t_row + 64 + hc * 32, hi);
+					tmem_ld32(t_head + hc * 32, lo);
+					tmem_ld32(t_head + 64 + hc * 32, hi);
 					tmem_ld_wait();
 					if (live) {
 						const __half *ct = a.cos_t + (size_t)pos * 128, *stb = a.sin_t + (size_t)pos * 128;
@@ -260,10 +277,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				}
 			} else {
 #pragma unroll 1
-				for (int c = cq; c < cq + 1; ++c) {
+				for (int c = cq * (BN / 128); c < (cq + 1) * (BN / 128); ++c) {
 					float v[32], u[32];
 					tmem_ld32(t_row + c * 32, v);
-					if (EPI == TC_EPI_SILU) tmem_ld32(t_row + TC_BN + c * 32, u);
+					if (EPI == TC_EPI_SILU) tmem_ld32(t_row + BN + c * 32, u);
 					tmem_ld_wait();
 					if (live) {
 						const int nc = n0 + c * 32;
