@@ -17,6 +17,7 @@ thread_local int g_last_cuda_error = 0;
 
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
 static int g_force_kw = 2;
+static int g_attn_splits = 0;     // tuning hook: 0 = heuristic
 static int g_use_tc = 1;          // tensor-core kernel for M > 16
 static int g_pdl = 0;             // programmatic dependent launch for the decode-step kernels (opt-in: measured no gain)
 static int g_allow_cluster = 0;   // cluster (DSMEM) split-K reduction: opt-in, see gptq_debug_allow_cluster
@@ -364,6 +365,7 @@ void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
 void gptq_debug_allow_cluster(int on) { g_allow_cluster = on ? 1 : 0; }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 void gptq_debug_use_tc(int on) { g_use_tc = on ? 1 : 0; }
+void gptq_debug_attn_splits(int n) { g_attn_splits = n; }
 // Host-only: the launch plan of the decode kernel for a shape.  out[0..7] = split-K, K-warps, ring stages,
 // dynamic shared memory bytes, x-slice bytes, strip groups, chunks per split, cluster flag.
 int gptq_debug_plan(int M, int K, int N, int groupsize, int nstream, int *out) {
@@ -439,7 +441,9 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 		return GPTQ_ERR_ALIGN;
 	if (batch == 0) return GPTQ_OK;
 	if ((size_t)batch * heads * 4 > (size_t)AT_TICKET_BYTES - 8) return GPTQ_ERR_UNSUPPORTED;
-	int splits = (4 * sm_count() + batch * heads - 1) / (batch * heads);
+	// about 2.6 CTAs of 128 threads per SM measured best (12 splits for 32 heads at 2k context)
+	int splits = (13 * sm_count() / 5 + batch * heads - 1) / (batch * heads);
+	if (g_attn_splits > 0) splits = g_attn_splits;
 	splits = std::max(1, std::min(splits, std::min(AT_MAX_SPLITS, (len_hint + 63) / 64)));
 	if (splits > 1 && (!workspace || workspace_bytes < gptq_attn_workspace_bytes(batch, heads))) return GPTQ_ERR_WORKSPACE;
 	AttnParams p = {};

@@ -533,28 +533,71 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	// first exchanged through the workspace.
 	const int nelem = NSTREAM * p.M * SK_BN;        // only rows < M matter
 	float *wsp = p.ws_partial + (size_t)(tile * p.splitk + split) * nelem;   // [stream][row < M][128]
+	if (M8) {
+		// few rows: one element per thread and pass
 	for (int e = tid; e < nelem; e += NT) {
-		const int s = e / (p.M * SK_BN), rc = e - s * (p.M * SK_BN);
-		const int row = rc >> 7, col = rc & 127;
-		float v = 0.f;
+			const int s = e / (p.M * SK_BN), rc = e - s * (p.M * SK_BN);
+			const int row = rc >> 7, col = rc & 127;
+			float v = 0.f;
 #pragma unroll
-		for (int k = 0; k < KW; ++k) v += red[((size_t)(k * NSTREAM + s) * ROWS + row) * SK_BN + col];
-		{
-			// remove the 1024-offsets and the zero points of this CTA's K-slice
-			const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
-			const __half *zz = s_zz + (size_t)s * p.strip_groups * SK_BN + col;
-			const __half *sc = s_sc + (size_t)s * p.strip_groups * SK_BN + col;
-			float corr = 0.f;
-			for (int gi = 0; gi < ng; ++gi) {
-				const float2 cs = s_cs[gi * 16 + row];
-				corr = fmaf(__half2float(sc[(size_t)gi * SK_BN]), fmaf(__half2float(zz[(size_t)gi * SK_BN]), cs.y, cs.x), corr);
+			for (int k = 0; k < KW; ++k) v += red[((size_t)(k * NSTREAM + s) * ROWS + row) * SK_BN + col];
+			{
+				// remove the 1024-offsets and the zero points of this CTA's K-slice
+				const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
+				const __half *zz = s_zz + (size_t)s * p.strip_groups * SK_BN + col;
+				const __half *sc = s_sc + (size_t)s * p.strip_groups * SK_BN + col;
+				float corr = 0.f;
+				for (int gi = 0; gi < ng; ++gi) {
+					const float2 cs = s_cs[gi * 16 + row];
+					corr = fmaf(__half2float(sc[(size_t)gi * SK_BN]), fmaf(__half2float(zz[(size_t)gi * SK_BN]), cs.y, cs.x), corr);
+				}
+				v -= corr;
 			}
-			v -= corr;
+			if (p.splitk == 1 || p.cluster)
+				red[((size_t)s * ROWS + row) * SK_BN + col] = v;
+			else
+				__stcg(wsp + e, v);
 		}
-		if (p.splitk == 1 || p.cluster)
-			red[((size_t)s * ROWS + row) * SK_BN + col] = v;
-		else
-			__stcg(wsp + e, v);
+	} else
+	{
+		// A thread owns one (stream, column) pair and every tpp-th batch row.  It first builds the
+		// correction sum_g s*(C + z*S) of its rows (scale and zero are read once per group), then
+		// adds the KW warp-row partials and subtracts it.
+		constexpr int PAIRS = NSTREAM * SK_BN, TPP = NT / PAIRS, RPT = 16 / TPP;
+		const int pair = tid % PAIRS, sub = tid / PAIRS;
+		const int s = pair >> 7, col = pair & 127;
+		const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
+		const __half *zz = s_zz + (size_t)s * p.strip_groups * SK_BN + col;
+		const __half *sc = s_sc + (size_t)s * p.strip_groups * SK_BN + col;
+		float corr[RPT];
+#pragma unroll
+		for (int i = 0; i < RPT; ++i) corr[i] = 0.f;
+		for (int gi = 0; gi < ng; ++gi) {
+			const float sv = __half2float(sc[(size_t)gi * SK_BN]);
+			const float sz = sv * __half2float(zz[(size_t)gi * SK_BN]);
+#pragma unroll
+			for (int i = 0; i < RPT; ++i) {
+				const int row = sub + i * TPP;
+				if (row < p.M) {
+					const float2 cs = s_cs[gi * 16 + row];
+					corr[i] = fmaf(sv, cs.x, fmaf(sz, cs.y, corr[i]));
+				}
+			}
+		}
+#pragma unroll
+		for (int i = 0; i < RPT; ++i) {
+			const int row = sub + i * TPP;
+			if (row < p.M) {
+				float v = 0.f;
+#pragma unroll
+				for (int k = 0; k < KW; ++k) v += red[((size_t)(k * NSTREAM + s) * ROWS + row) * SK_BN + col];
+				v -= corr[i];
+				if (p.splitk == 1 || p.cluster)
+					red[((size_t)s * ROWS + row) * SK_BN + col] = v;
+				else
+					__stcg(wsp + (size_t)s * p.M * SK_BN + row * SK_BN + col, v);
+			}
+		}
 	}
 	if (p.splitk > 1 && !p.cluster) {
 		__threadfence();
@@ -570,16 +613,37 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		if (!s_last) return;
 		__threadfence();
 		const float *wt = p.ws_partial + (size_t)tile * p.splitk * nelem;
+		if (M8) {
 		for (int e = tid; e < nelem; e += NT) {
-			const int s = e / (p.M * SK_BN), rc = e - s * (p.M * SK_BN);
-			const int row = rc >> 7, col = rc & 127;
-			float part[16];       // split-K <= 16; loads first, then a fixed-order sum
+				const int s = e / (p.M * SK_BN), rc = e - s * (p.M * SK_BN);
+				const int row = rc >> 7, col = rc & 127;
+				float part[16];       // split-K <= 16; loads first, then a fixed-order sum
 #pragma unroll
-			for (int k = 0; k < 16; ++k) part[k] = (k < p.splitk) ? __ldcg(wt + (size_t)k * nelem + e) : 0.f;
-			float v = 0.f;
+				for (int k = 0; k < 16; ++k) part[k] = (k < p.splitk) ? __ldcg(wt + (size_t)k * nelem + e) : 0.f;
+				float v = 0.f;
 #pragma unroll
-			for (int k = 0; k < 16; ++k) v += part[k];
-			red[((size_t)s * ROWS + row) * SK_BN + col] = v;
+				for (int k = 0; k < 16; ++k) v += part[k];
+				red[((size_t)s * ROWS + row) * SK_BN + col] = v;
+			}
+		} else {
+		for (int e0 = tid; e0 < nelem; e0 += NT * 4) {        // four elements in flight per thread; fixed split order
+				float v[4] = {0.f, 0.f, 0.f, 0.f};
+				for (int k = 0; k < p.splitk; ++k) {
+					float t[4];
+#pragma unroll
+					for (int j = 0; j < 4; ++j) t[j] = (e0 + j * NT < nelem) ? __ldcg(wt + (size_t)k * nelem + e0 + j * NT) : 0.f;
+#pragma unroll
+					for (int j = 0; j < 4; ++j) v[j] += t[j];
+				}
+#pragma unroll
+				for (int j = 0; j < 4; ++j) {
+					const int e = e0 + j * NT;
+					if (e < nelem) {
+						const int s = e / (p.M * SK_BN), rc = e - s * (p.M * SK_BN);
+						red[((size_t)s * ROWS + (rc >> 7)) * SK_BN + (rc & 127)] = v[j];
+					}
+				}
+			}
 		}
 	}
 	__syncthreads();

@@ -29,7 +29,8 @@ def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, device=None
 
 
 def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin, position_ids, n_heads: int, head_dim: int,
-			 perm: Optional[torch.Tensor] = None, kv_cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+			 perm: Optional[torch.Tensor] = None, kv_cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+			 rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6):
 	"""One kernel: a x deq(Wqkv), rotary on Q and K, scatter to heads.
 
 	a: [b, t, K] fp16 contiguous; position_ids: [b, t] integer.
@@ -58,6 +59,8 @@ def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin,
 		S = k.shape[2]
 		sb, st, sh, sp = n_heads * S * head_dim, 0, S * head_dim, head_dim
 	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available
+	if rms_weight is not None:
+		a = rmsnorm(a, rms_weight, rms_eps)          # the norm runs as its own kernel
 	if M > DECODE_MAX_M and perm is not None and prefill_kernel_available(M, K, 3 * hidden, groupsize):
 		a = a.view(M, K)[:, perm.long()].contiguous().view(b, t, K)
 		perm = None
@@ -155,7 +158,7 @@ class QuantLlamaAttention(nn.Module):
 			self._tables = rope_tables(self.head_dim, n, self.rope_theta, device=device)
 		return self._tables
 
-	def project_qkv(self, hidden_states, position_ids, kv_cache=None):
+	def project_qkv(self, hidden_states, position_ids, kv_cache=None, rms_weight=None, rms_eps=1e-6):
 		qw, g_idx, perm = self.qkv_proj.kernel_operands()
 		if g_idx is not None:
 			raise NotImplementedError('fused QKV needs act-order groups of equal size')
@@ -165,7 +168,7 @@ class QuantLlamaAttention(nn.Module):
 		need = 0 if kv_cache is None else kv_cache[0].shape[2]      # a static cache fixes the position range
 		cos, sin = self.tables(hidden_states.device, need)
 		return qkv_rope(self.qkv_proj.groupsize, hidden_states, qw, self.qkv_proj.scales, self.qkv_proj.qzeros, cos, sin,
-						position_ids, self.num_heads, self.head_dim, perm=perm, kv_cache=kv_cache)
+						position_ids, self.num_heads, self.head_dim, perm=perm, kv_cache=kv_cache, rms_weight=rms_weight, rms_eps=rms_eps)
 
 	def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
 				position_ids: Optional[torch.LongTensor] = None, past_key_value: Optional[Tuple[torch.Tensor]] = None,

@@ -40,8 +40,11 @@ def autotune_warmup(model):
 
 
 def gateup_silu(groupsize: int, a: torch.Tensor, gate_qweight, gate_scales, gate_qzeros, up_qweight, up_scales, up_qzeros,
-				g_idx: Optional[torch.Tensor] = None, perm: Optional[torch.Tensor] = None) -> torch.Tensor:
-	"""silu(a x deq(gate)) * (a x deq(up)); fp32 until the one fp16 store."""
+				g_idx: Optional[torch.Tensor] = None, perm: Optional[torch.Tensor] = None,
+				rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6) -> torch.Tensor:
+	"""silu(a x deq(gate)) * (a x deq(up)); fp32 until the one fp16 store.  With rms_weight the input is
+	RMS-normalised first by the library's RMSNorm kernel (folding the norm into the decode kernel was
+	tried and measured slower than the separate 2 us kernel)."""
 	assert gate_qweight.shape == up_qweight.shape and gate_scales.shape == up_scales.shape and gate_qzeros.shape == up_qzeros.shape, "All weights must have the same shape"
 	assert a.shape[-1] == (gate_qweight.shape[0] * 8), "A must be a multiple of 8 in the last dimension"
 	assert a.is_contiguous(), "A must be contiguous"
@@ -55,6 +58,10 @@ def gateup_silu(groupsize: int, a: torch.Tensor, gate_qweight, gate_scales, gate
 	if M == 0:
 		return c.view(a.shape[:-1] + (N,))
 	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available
+	if rms_weight is not None:
+		from .fused_attention import rmsnorm
+		x = rmsnorm(x.contiguous(), rms_weight, rms_eps)
+		rms_weight = None
 	if M > DECODE_MAX_M and perm is not None and g_idx is None and prefill_kernel_available(M, K, N, groupsize):
 		x = x[:, perm.long()].contiguous()
 		perm = None
@@ -125,14 +132,15 @@ class QuantLlamaMLP(nn.Module):
 					self._gidx = self.g_idx
 		self._ao_ready = True
 
-	def intermediate(self, x):
+	def intermediate(self, x, rms_weight=None, rms_eps=1e-6):
 		if not self._ao_ready:
 			self._prepare()
 		return gateup_silu(self.groupsize, x, self._gate_qw, self.gate_proj_scales, self.gate_proj_qzeros,
-						   self._up_qw, self.up_proj_scales, self.up_proj_qzeros, g_idx=self._gidx, perm=self._perm)
+						   self._up_qw, self.up_proj_scales, self.up_proj_qzeros, g_idx=self._gidx, perm=self._perm,
+						   rms_weight=rms_weight, rms_eps=rms_eps)
 
-	def forward(self, x, residual: Optional[torch.Tensor] = None):
-		h = self.intermediate(x)
+	def forward(self, x, residual: Optional[torch.Tensor] = None, rms_weight=None, rms_eps=1e-6):
+		h = self.intermediate(x, rms_weight, rms_eps)
 		if residual is None:
 			return self.down_proj(h)
 		return self.down_proj(h, residual=residual)

@@ -196,6 +196,7 @@ class DecodeEngine:
 		self.tok = torch.zeros((batch, 1), dtype=torch.int64, device=dev)          # token being fed
 		self.mask = torch.full((batch, 1, 1, max_seq), float('-inf'), dtype=torch.float16, device=dev)
 		self.use_graph = use_graph
+		self.fuse_norm = False       # True: pass the norm weights to the QKV / gate-up ops (same kernels underneath)
 		self.len_hint = max_seq
 		self.graph = None
 		self.launches_per_step = None
@@ -205,9 +206,12 @@ class DecodeEngine:
 		layer = self.model.model.layers[i]
 		attn: QuantLlamaAttention = layer.self_attn
 		decode = h.shape[1] == 1
-		norm = rmsnorm_kernel if h.is_contiguous() else rmsnorm
-		x = norm(h, layer.input_layernorm.weight, layer.input_layernorm.variance_epsilon)
-		q, _, _ = attn.project_qkv(x, pos, kv_cache=(self.kcache[i], self.vcache[i]))
+		ln1, ln2 = layer.input_layernorm, layer.post_attention_layernorm
+		if self.fuse_norm and decode:
+			q, _, _ = attn.project_qkv(h.contiguous(), pos, kv_cache=(self.kcache[i], self.vcache[i]), rms_weight=ln1.weight, rms_eps=ln1.variance_epsilon)
+		else:
+			x = rmsnorm_kernel(h.contiguous(), ln1.weight, ln1.variance_epsilon)
+			q, _, _ = attn.project_qkv(x, pos, kv_cache=(self.kcache[i], self.vcache[i]))
 		b = h.shape[0]
 		if decode:
 			# own single-query kernel over the static cache (length read from `pos` on the device)
@@ -221,12 +225,14 @@ class DecodeEngine:
 		h = attn.o_proj(o, residual=res)
 		if self.tp_world > 1:
 			all_reduce_(h, self.tp_group)
-		x = norm(h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.variance_epsilon)
 		mlp = layer.mlp
 		res = h if self.tp_rank == 0 else None
-		if isinstance(mlp, QuantLlamaMLP):
-			h = mlp(x, residual=res)
+		if isinstance(mlp, QuantLlamaMLP) and self.fuse_norm and decode:
+			h = mlp(h, residual=res, rms_weight=ln2.weight, rms_eps=ln2.variance_epsilon)
+		elif isinstance(mlp, QuantLlamaMLP):
+			h = mlp(rmsnorm_kernel(h, ln2.weight, ln2.variance_epsilon), residual=res)
 		else:
+			x = rmsnorm_kernel(h, ln2.weight, ln2.variance_epsilon)
 			h = mlp(x) if res is None else res + mlp(x)
 		if self.tp_world > 1:
 			all_reduce_(h, self.tp_group)

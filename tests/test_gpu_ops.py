@@ -501,3 +501,37 @@ def test_qkv_rope_position_outside_tables_is_reported_not_dereferenced(G):
 	assert O.max_rel_err(q.transpose(1, 2), rq) <= TOL
 	_lib.clear_kernel_status()
 	assert _lib.kernel_status() == 0
+
+
+# ---------------------------------------------------------------- RMSNorm folded into the decode kernels
+@pytest.mark.parametrize('M', [1, 5, 16])
+@pytest.mark.parametrize('ao', [False, True])
+def test_fused_rmsnorm_in_gateup_and_qkv(G, M, ao):
+	from gptq_triton_b200.quant_linear import _act_order_perm, act_order_rows
+	K, N, gs, H, D = 1024, 384, 128, 2, 128
+	rng = torch.Generator().manual_seed(M)
+	x = (torch.randn((1, M, K), generator=rng) * 2.5).half()
+	gamma = (torch.rand((K,), generator=rng) + 0.5).half()
+	xd = x.double()
+	xn = (xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.double()).half()       # one rounding, as in the kernel
+	g, u = synth(K, N, gs, 71, act_order=ao), synth(K, N, gs, 72)
+	w = synth(K, 3 * H * D, gs, 73, act_order=ao)
+	perm = None
+	gq, uq, wq = g['qweight'].cuda(), u['qweight'].cuda(), w['qweight'].cuda()
+	if ao:
+		perm = _act_order_perm(g['g_idx'].cuda(), gs)
+		gq, uq = act_order_rows(gq, perm), act_order_rows(uq, perm)
+	y = G.gateup_silu(gs, x.cuda(), gq, g['scales'].cuda(), g['qzeros'].cuda(), uq, u['scales'].cuda(), u['qzeros'].cuda(), perm=perm,
+					  rms_weight=gamma.cuda(), rms_eps=1e-6)
+	ref = O.gateup_silu_r32(xn, (g['qweight'], g['qzeros'], g['scales']), (u['qweight'], u['qzeros'], u['scales']), gs, g_idx=g['g_idx'])
+	assert O.max_rel_err(y, ref) <= TOL
+	permw = None
+	if ao:
+		permw = _act_order_perm(w['g_idx'].cuda(), gs)
+		wq = act_order_rows(wq, permw)
+	pos = torch.arange(M).unsqueeze(0)
+	cos, sin = O.rope_tables(D, 64)
+	q, k, v = G.qkv_rope(gs, x.cuda(), wq, w['scales'].cuda(), w['qzeros'].cuda(), cos.cuda(), sin.cuda(), pos.cuda(), H, D, perm=permw,
+						 rms_weight=gamma.cuda(), rms_eps=1e-6)
+	rq, rk, rv = O.qkv_rope_r32(xn, w['qweight'], w['qzeros'], w['scales'], gs, cos, sin, pos, H, D, g_idx=w['g_idx'])
+	assert O.max_rel_err(q.transpose(1, 2), rq) <= TOL and O.max_rel_err(k.transpose(1, 2), rk) <= TOL and O.max_rel_err(v.transpose(1, 2), rv) <= TOL
