@@ -310,6 +310,29 @@ def kernel_case(args):
 	from gptq_triton_b200 import synth
 	dev = torch.device('cuda', 0)
 	M = args.m
+	if args.kernel_case == 'prefill':
+		# tensor-core kernel: M x 4096 x 4096 quantised matmul, three launches
+		K, N = 4096, 4096
+		t = synth.quant_tensors(K, N, GROUPSIZE, seed=2)
+		w = tuple(v.to(dev) for v in (t['qweight'], t['scales'], t['qzeros']))
+		x = synth.activations((max(M, 2048), K), seed=1).to(dev)
+		for i in range(3):
+			G.qmatmul(GROUPSIZE, x, *w)
+		torch.cuda.synchronize()
+		print(json.dumps({'kernel_case': 'prefill', 'M': int(x.shape[0]), 'launches': 3}))
+		return
+	if args.kernel_case == 'attn':
+		# single-query attention over 8 rotating caches (8 x 36 MB > L2) at 2100 tokens of context
+		from gptq_triton_b200.fused_attention import attn_decode
+		H, S, D = 32, 2200, 128
+		caches = [(torch.randn((1, H, S, D), device=dev).half(), torch.randn((1, H, S, D), device=dev).half()) for _ in range(8)]
+		q = torch.randn((1, 1, H, D), device=dev).half().transpose(1, 2)
+		pos = torch.full((1, 1), 2100, dtype=torch.int32, device=dev)
+		for i in range(8):
+			attn_decode(q, caches[i][0], caches[i][1], pos, 2101)
+		torch.cuda.synchronize()
+		print(json.dumps({'kernel_case': 'attn', 'launches': 8}))
+		return
 	if args.kernel_case == 'gateup':
 		K, N = 4096, 11008
 		g, u = synth.quant_tensors(K, N, GROUPSIZE, seed=2), synth.quant_tensors(K, N, GROUPSIZE, seed=3)
@@ -338,7 +361,7 @@ def main():
 	ap.add_argument('--no-cpu-baseline', action='store_true')
 	ap.add_argument('--workload', default='llama7b', choices=['llama7b', 'llama65b-b16'], help='llama65b-b16: 65B architecture, batch 16 (tensor-parallel runs)')
 	ap.add_argument('--no-graph', action='store_true', help='do not capture the decode step in a CUDA graph')
-	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down'], help='profiling aid: run 8 launches of one decode kernel and exit')
+	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down', 'prefill', 'attn'], help='profiling aid: run a few launches of one kernel and exit')
 	ap.add_argument('--m', type=int, default=1, help='batch rows for --kernel-case')
 	args = ap.parse_args()
 	if args.kernel_case:
