@@ -42,7 +42,6 @@ _SIGNATURES = {
 _OPTIONAL = {
 	'gptq_debug_force_splitk': (None, [c_int]),
 	'gptq_debug_force_kw': (None, [c_int]),
-	'gptq_debug_allow_cluster': (None, [c_int]),
 	'gptq_debug_set_pdl': (None, [c_int]),
 }
 

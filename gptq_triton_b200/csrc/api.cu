@@ -20,7 +20,6 @@ static int g_force_kw = 2;
 static int g_attn_splits = 0;     // tuning hook: 0 = heuristic
 static int g_use_tc = 1;          // tensor-core kernel for M > 16
 static int g_pdl = 0;             // programmatic dependent launch for the decode-step kernels (opt-in: measured no gain)
-static int g_allow_cluster = 0;   // cluster (DSMEM) split-K reduction: opt-in, see gptq_debug_allow_cluster
 #ifdef GPTQ_SK_TIMING
 static long long *g_dbg = nullptr;
 #endif
@@ -38,9 +37,9 @@ static int sm_count() {
 }
 
 // Launch with optional programmatic stream serialisation (the kernel may start while its
-// predecessor drains; it calls pdl_wait() before touching dependent data) and optional cluster.
+// predecessor drains; it calls pdl_wait() before touching dependent data).
 template <typename... KArgs, typename... Args>
-static int launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_y, Args &&...args) {
+static int launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
 	cudaLaunchConfig_t cfg = {};
 	cfg.gridDim = grid;
 	cfg.blockDim = block;
@@ -51,13 +50,6 @@ static int launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
 	if (g_pdl) {
 		attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
 		attr[n].val.programmaticStreamSerializationAllowed = 1;
-		++n;
-	}
-	if (cluster_y > 1) {
-		attr[n].id = cudaLaunchAttributeClusterDimension;
-		attr[n].val.clusterDim.x = 1;
-		attr[n].val.clusterDim.y = (unsigned)cluster_y;
-		attr[n].val.clusterDim.z = 1;
 		++n;
 	}
 	cfg.attrs = attr;
@@ -191,7 +183,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 		const int per_sm = 4 / kwarps;
 		const size_t cap = kwarps == 2 ? (size_t)113 * 1024 : (size_t)SK_SMEM_LIMIT - 2048;
 		const int slots = sms * per_sm;
-		for (int sk = 1; sk <= std::min(p.total_chunks, g_allow_cluster ? 8 : SK_MAX_SPLITK); ++sk) {
+		for (int sk = 1; sk <= std::min(p.total_chunks, SK_MAX_SPLITK); ++sk) {
 			int cps, eff, a, b, c;
 			int nstage = 4;
 			while (nstage > 2 && layout(sk, kwarps, nstage, cps, eff, a, b, c) > cap) --nstage;
@@ -228,8 +220,6 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 	smem = layout(best_sk, best_kw, best_stage, cps, eff, p.xs_stride, p.xs_bytes, p.strip_groups);
 	p.chunks_per_split = cps;
 	p.splitk = eff;
-	p.cluster = (g_allow_cluster && eff > 1 && eff <= 8) ? 1 : 0;
-	p.pdl = g_pdl;
 	p.nstage = best_stage;
 	kw = best_kw;
 	grid = dim3(tiles, p.splitk, 1);
@@ -254,7 +244,7 @@ static int launch_skinny_inst(const CUtensorMap &tm0, const CUtensorMap &tm1, co
 	auto k = skinny_kernel<KW, NSTREAM, M8, SPG_T, EPI>;
 	static bool ready[64] = {false};
 	if (int rc = ensure_smem_attr(k, ready)) return rc;
-	return launch_ex(k, grid, dim3(KW * 128, 1, 1), smem, stream, p.cluster ? p.splitk : 1, tm0, tm1, p);
+	return launch_ex(k, grid, dim3(KW * 128, 1, 1), smem, stream, tm0, tm1, p);
 }
 
 template <int NSTREAM, int EPI>
@@ -362,12 +352,11 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 // Tuning / test hook: force the split-K factor of the decode kernel (0 restores the heuristic).
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
 void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
-void gptq_debug_allow_cluster(int on) { g_allow_cluster = on ? 1 : 0; }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 void gptq_debug_use_tc(int on) { g_use_tc = on ? 1 : 0; }
 void gptq_debug_attn_splits(int n) { g_attn_splits = n; }
 // Host-only: the launch plan of the decode kernel for a shape.  out[0..7] = split-K, K-warps, ring stages,
-// dynamic shared memory bytes, x-slice bytes, strip groups, chunks per split, cluster flag.
+// dynamic shared memory bytes, x-slice bytes, strip groups, chunks per split, 0.
 int gptq_debug_plan(int M, int K, int N, int groupsize, int nstream, int *out) {
 	if (groupsize == -1) groupsize = K;
 	if (M <= 0 || M > 16 || !skinny_shape_ok(K, N, groupsize, nullptr)) return GPTQ_ERR_UNSUPPORTED;
@@ -378,7 +367,7 @@ int gptq_debug_plan(int M, int K, int N, int groupsize, int nstream, int *out) {
 	int kw;
 	plan_skinny(p, nstream, kw, grid, smem);
 	out[0] = p.splitk; out[1] = kw; out[2] = p.nstage; out[3] = (int)smem; out[4] = p.xs_bytes; out[5] = p.strip_groups;
-	out[6] = p.chunks_per_split; out[7] = p.cluster;
+	out[6] = p.chunks_per_split; out[7] = 0;
 	return GPTQ_OK;
 }
 #ifdef GPTQ_SK_TIMING
@@ -454,7 +443,7 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 	p.scale = scale; p.heads = heads; p.splits = splits;
 	p.ws_ticket = reinterpret_cast<int *>(workspace);
 	p.ws_partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + AT_TICKET_BYTES);
-	return launch_ex(attn_decode_kernel, dim3(splits, heads, batch), dim3(AT_THREADS, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), 1, p);
+	return launch_ex(attn_decode_kernel, dim3(splits, heads, batch), dim3(AT_THREADS, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), p);
 }
 
 int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_t ldy, int M, int K, float eps, gptq_stream_t stream) {
@@ -462,7 +451,7 @@ int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_
 	if (K % 8 != 0) return GPTQ_ERR_SHAPE;
 	if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || ldx % 8 || ldy % 8) return GPTQ_ERR_ALIGN;
 	if (M == 0) return GPTQ_OK;
-	return launch_ex(rmsnorm_kernel, dim3(M, 1, 1), dim3(256, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), 1, (const __half *)x, (long long)ldx,
+	return launch_ex(rmsnorm_kernel, dim3(M, 1, 1), dim3(256, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), (const __half *)x, (long long)ldx,
 					 (const __half *)weight, (__half *)y, (long long)ldy, K, eps);
 }
 

@@ -122,6 +122,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 
 // Bounded wait: returns false when the phase did not complete within `limit` polls.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+#pragma unroll 1
 	for (uint32_t i = 0; i < limit; ++i)
 		if (mbar_try_wait(bar, parity)) return true;
 	return false;

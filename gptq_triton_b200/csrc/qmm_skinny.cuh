@@ -31,7 +31,6 @@
 // with a scatter into Q / K / V (or the KV cache).
 #pragma once
 
-#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
@@ -61,8 +60,6 @@ struct SkinnyParams {
 	int xs_stride;         // bytes between rows of the staged x slice
 	int xs_bytes;          // M * xs_stride rounded up to 128
 	int strip_groups;      // capacity (groups) of the zero / scale strips per stream
-	int pdl;               // 1: launched with programmatic stream serialisation (x is loaded after pdl_wait)
-	int cluster;           // 1: the split-K CTAs of a tile form a thread-block cluster and reduce over DSMEM
 	float *ws_partial;
 	int *ws_ticket;
 	// EPI_PLAIN / EPI_SILU
@@ -182,19 +179,19 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
 	const int n_strip = NSTREAM * ng * 16;              // items of 8 columns
 	const int units = (c_hi - c_lo) * 16;               // 16-byte units per x row
-	const int n_x = p.M * units;
 	constexpr int SB = 2, XB = 4;
+	// strips: item -> (stream, group, 8-column unit) without a division (NSTREAM <= 2)
 	auto strip_load = [&](int base, uint32_t(&z)[SB], uint4(&sv)[SB]) {
 		const int nz = p.N >> 3;
 #pragma unroll
 		for (int j = 0; j < SB; ++j) {
 			const int idx = base + j * NT;
 			if (idx < n_strip) {
-				const int s = idx / (ng * 16), r = idx - s * (ng * 16);
-				const int gi = r >> 4, c = r & 15;
+				const int r = idx >> 4, c = idx & 15;
+				const int s = (NSTREAM == 2 && r >= ng) ? 1 : 0, gi = r - s * ng;
 				if (n0 + c * 8 < p.N) {
-					const int32_t *qz = (NSTREAM == 2 && s) ? p.qz1 : p.qz0;
-					const __half *sc = (NSTREAM == 2 && s) ? p.sc1 : p.sc0;
+					const int32_t *qz = s ? p.qz1 : p.qz0;
+					const __half *sc = s ? p.sc1 : p.sc0;
 					z[j] = (uint32_t)__ldg(qz + (size_t)(g_lo + gi) * nz + (n0 >> 3) + c);
 					sv[j] = __ldg(reinterpret_cast<const uint4 *>(sc + (size_t)(g_lo + gi) * p.N + n0 + c * 8));
 				}
@@ -206,8 +203,8 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		for (int j = 0; j < SB; ++j) {
 			const int idx = base + j * NT;
 			if (idx < n_strip) {
-				const int s = idx / (ng * 16), r = idx - s * (ng * 16);
-				const int gi = r >> 4, c = r & 15;
+				const int r = idx >> 4, c = idx & 15;
+				const int s = (NSTREAM == 2 && r >= ng) ? 1 : 0, gi = r - s * ng;
 				if (n0 + c * 8 < p.N) {
 					// zero point (stored + 1) as fp16, two per word: (0x6401 + nibble) - 1024
 					const uint32_t zv = z[j];
@@ -223,76 +220,72 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			}
 		}
 	};
-	auto x_load = [&](int base, uint4(&v)[XB]) {
+	// x slice: a pass covers XB batch rows of one 16-byte unit per thread (same k for every row,
+	// so the act-order permutation is read once per pass)
+	auto x_load = [&](int row0, int unit, uint4(&v)[XB]) {
+		if (unit >= units) return;
+		const int k = (c_lo * 16 + unit) * 8;
 		if (p.perm == nullptr) {
 #pragma unroll
-			for (int j = 0; j < XB; ++j) {
-				const int idx = base + j * NT;
-				if (idx < n_x) {
-					const int row = idx / units, unit = idx - row * units;
-					v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)row * p.ldx + (c_lo * 16 + unit) * 8));
-				}
-			}
+			for (int j = 0; j < XB; ++j)
+				if (row0 + j < p.M) v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)(row0 + j) * p.ldx + k));
 		} else {
-			int4 pa[XB], pb[XB];
+			const int4 pa = __ldg(reinterpret_cast<const int4 *>(p.perm + k));
+			const int4 pb = __ldg(reinterpret_cast<const int4 *>(p.perm + k + 4));
 #pragma unroll
 			for (int j = 0; j < XB; ++j) {
-				const int idx = base + j * NT;
-				if (idx < n_x) {
-					const int k = (c_lo * 16 + idx % units) * 8;
-					pa[j] = __ldg(reinterpret_cast<const int4 *>(p.perm + k));
-					pb[j] = __ldg(reinterpret_cast<const int4 *>(p.perm + k + 4));
-				}
-			}
-#pragma unroll
-			for (int j = 0; j < XB; ++j) {
-				const int idx = base + j * NT;
-				if (idx < n_x) {
-					const unsigned short *xr = reinterpret_cast<const unsigned short *>(p.x) + (size_t)(idx / units) * p.ldx;
-					const uint32_t h0 = __ldg(xr + pa[j].x), h1 = __ldg(xr + pa[j].y), h2 = __ldg(xr + pa[j].z), h3 = __ldg(xr + pa[j].w);
-					const uint32_t h4 = __ldg(xr + pb[j].x), h5 = __ldg(xr + pb[j].y), h6 = __ldg(xr + pb[j].z), h7 = __ldg(xr + pb[j].w);
+				if (row0 + j < p.M) {
+					const unsigned short *xr = reinterpret_cast<const unsigned short *>(p.x) + (size_t)(row0 + j) * p.ldx;
+					const uint32_t h0 = __ldg(xr + pa.x), h1 = __ldg(xr + pa.y), h2 = __ldg(xr + pa.z), h3 = __ldg(xr + pa.w);
+					const uint32_t h4 = __ldg(xr + pb.x), h5 = __ldg(xr + pb.y), h6 = __ldg(xr + pb.z), h7 = __ldg(xr + pb.w);
 					v[j] = make_uint4(h0 | (h1 << 16), h2 | (h3 << 16), h4 | (h5 << 16), h6 | (h7 << 16));
 				}
 			}
 		}
 	};
-	auto x_store = [&](int base, const uint4(&v)[XB]) {
+	auto x_store = [&](int row0, int unit, const uint4(&v)[XB]) {
 		// [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7, the (1,5) and (3,7) pairs divided by 16
+		if (unit >= units) return;
 #pragma unroll
 		for (int j = 0; j < XB; ++j) {
-			const int idx = base + j * NT;
-			if (idx < n_x) {
-				const int row = idx / units, unit = idx - row * units;
+			if (row0 + j < p.M) {
 				uint4 o;
 				o.x = __byte_perm(v[j].x, v[j].z, 0x5410);                          // (x0, x4)
 				o.y = h2_mul(__byte_perm(v[j].x, v[j].z, 0x7632), 0x2C002C00u);    // (x1, x5) / 16
 				o.z = __byte_perm(v[j].y, v[j].w, 0x5410);                          // (x2, x6)
 				o.w = h2_mul(__byte_perm(v[j].y, v[j].w, 0x7632), 0x2C002C00u);    // (x3, x7) / 16
-				*reinterpret_cast<uint4 *>(xs + (size_t)row * p.xs_stride + unit * 16) = o;
+				*reinterpret_cast<uint4 *>(xs + (size_t)(row0 + j) * p.xs_stride + unit * 16) = o;
 			}
 		}
 	};
 	{
-		uint32_t z0[SB];
-		uint4 sv0[SB], v0[XB];
+		// One copy of the staging code (real loops; the first pass issues its loads before the
+		// weight prefetch).  Straight-line code that runs once costs instruction fetch, and this
+		// prologue used to be more than half of the kernel's code.
 		pdl_trigger();
-		strip_load(tid, z0, sv0);                            // weights side: independent of earlier kernels
-		if (!p.pdl) x_load(tid, v0);                         // ahead of the prefetch burst in the memory queues
-		for (int s = 0; s < p.nstage; ++s) produce();        // weight prefetch: nstage chunks per warp
-		SK_STAMP(1);
-		if (p.pdl) {
-			pdl_wait();                                      // x, residual and the workspace come from earlier kernels
-			x_load(tid, v0);
-		}
-		strip_store(tid, z0, sv0);
-		x_store(tid, v0);
-		for (int base = tid + NT * SB; base < n_strip; base += NT * SB) {
-			strip_load(base, z0, sv0);
-			strip_store(base, z0, sv0);
-		}
-		for (int base = tid + NT * XB; base < n_x; base += NT * XB) {
-			x_load(base, v0);
-			x_store(base, v0);
+		pdl_wait();                                          // x, residual and the workspace come from earlier kernels
+		const int x_passes = ((p.M + XB - 1) / XB) * ((units + NT - 1) / NT);      // (row block, unit block) pairs
+		const int u_blocks = (units + NT - 1) / NT;
+		const int n_it = max(max(1, x_passes), (n_strip + NT * SB - 1) / (NT * SB));
+		int xr0 = 0, xu = tid;                               // row block / unit of the current x pass
+#pragma unroll 1
+		for (int it = 0; it < n_it; ++it) {
+			uint32_t z0[SB];
+			uint4 sv0[SB], v0[XB];
+			strip_load(tid + it * NT * SB, z0, sv0);
+			if (it < x_passes) x_load(xr0, xu, v0);          // ahead of the prefetch burst in the memory queues
+			if (it == 0) {
+#pragma unroll 1
+				for (int s = 0; s < p.nstage; ++s) produce();    // weight prefetch: nstage chunks per warp
+				SK_STAMP(1);
+			}
+			strip_store(tid + it * NT * SB, z0, sv0);
+			if (it < x_passes) x_store(xr0, xu, v0);
+			xu += NT;
+			if (xu - tid >= u_blocks * NT) {
+				xu = tid;
+				xr0 += XB;
+			}
 		}
 	}
 	__syncthreads();
@@ -361,9 +354,16 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		int stage = 0;
 		uint32_t parity = 0;
 		bool first = true;
-#pragma unroll
+		// The streams share ONE copy of the loop code (a real loop over s, accumulating into accw):
+		// instruction fetch is the largest stall of a kernel this short, so code size is kept down.
+#pragma unroll 1
 		for (int s = 0; s < NSTREAM; ++s) {
 			const __half *sc_s = s_sc + (size_t)s * p.strip_groups * SK_BN + strip_col;
+			float accw[MB][4][2];
+#pragma unroll
+			for (int b = 0; b < MB; ++b)
+#pragma unroll
+				for (int c = 0; c < 4; ++c) accw[b][c][0] = accw[b][c][1] = 0.f;
 			// Two accumulator sets: while the MMAs of one group are still in the tensor pipe, the
 			// finished set of the previous group is scaled and added, so nothing waits for a drain.
 			float gA[MB][4][2], gB[MB][4][2];
@@ -382,8 +382,8 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 				for (int b = 0; b < MB; ++b)
 #pragma unroll
 					for (int c = 0; c < 4; ++c) {
-						acc[s][b][c][0] = fmaf(sf[c], g[b][c][0], acc[s][b][c][0]);
-						acc[s][b][c][1] = fmaf(sf[c], g[b][c][1], acc[s][b][c][1]);
+						accw[b][c][0] = fmaf(sf[c], g[b][c][0], accw[b][c][0]);
+						accw[b][c][1] = fmaf(sf[c], g[b][c][1], accw[b][c][1]);
 					}
 				clear(g);
 			};
@@ -446,52 +446,61 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			clear(gA);
 			clear(gB);
 
-			if (SPG_T == 0 && p.spg == 4) {
-				// one group per chunk: chunks alternate between the two accumulator sets
+			if (SPG_T == 0) {
+				// Groups of 128 rows or more (a multiple of the 4 steps of a chunk).  The two
+				// accumulator sets alternate by GROUP: while one group's MMAs are in flight the
+				// finished set of the previous group is flushed, one chunk later.
 				int chunk = w_lo;
-				for (; chunk + 1 < w_hi; chunk += 2) {
-					if (!begin()) { failed = true; break; }
-#pragma unroll
-					for (int l = 0; l < 4; ++l) step(gA, ring_of(l), xrow0 + xoff_of(chunk, l), xrow1 + xoff_of(chunk, l));
-					if (chunk > w_lo) flush(gB, chunk - 1 - g_lo);
-					end();
-					if (!begin()) { failed = true; break; }
-#pragma unroll
-					for (int l = 0; l < 4; ++l) step(gB, ring_of(l), xrow0 + xoff_of(chunk + 1, l), xrow1 + xoff_of(chunk + 1, l));
-					flush(gA, chunk - g_lo);
-					end();
-				}
-				if (!failed && chunk < w_hi) {          // odd chunk count: one more on set A
-					if (begin()) {
-#pragma unroll
-						for (int l = 0; l < 4; ++l) step(gA, ring_of(l), xrow0 + xoff_of(chunk, l), xrow1 + xoff_of(chunk, l));
-						if (chunk > w_lo) flush(gB, chunk - 1 - g_lo);
-						end();
-						flush(gA, chunk - g_lo);
-					} else {
-						failed = true;
-					}
-				} else if (!failed && w_hi > w_lo) {
-					flush(gB, w_hi - 1 - g_lo);
-				}
-			} else if (SPG_T == 0) {
-				// groups span several chunks: flushes are rare, a single accumulator set is enough
 				int gi = (w_lo * 4) / p.spg - g_lo;
 				int left = p.spg - (w_lo * 4) % p.spg;          // steps left in the current group
-				for (int chunk = w_lo; chunk < w_hi; ++chunk) {
-					if (!begin()) { failed = true; break; }
+				bool pendA = false, pendB = false;
+				int giA = 0, giB = 0;
+				while (chunk < w_hi) {
+					bool done;
+					do {
+						if (!begin()) { failed = true; break; }
 #pragma unroll
-					for (int l = 0; l < 4; ++l) step(gA, ring_of(l), xrow0 + xoff_of(chunk, l), xrow1 + xoff_of(chunk, l));
-					left -= 4;
-					if (left == 0 || chunk + 1 == w_hi) {
-						flush(gA, gi);
-						if (left == 0) {
-							++gi;
-							left = p.spg;
+						for (int l = 0; l < 4; ++l) step(gA, ring_of(l), xrow0 + xoff_of(chunk, l), xrow1 + xoff_of(chunk, l));
+						if (pendB) {
+							flush(gB, giB);
+							pendB = false;
 						}
+						left -= 4;
+						++chunk;
+						done = (left == 0) || (chunk == w_hi);
+						end();
+					} while (!done);
+					if (failed) break;
+					pendA = true;
+					giA = gi;
+					if (left == 0) {
+						++gi;
+						left = p.spg;
 					}
-					end();
+					if (chunk >= w_hi) break;
+					do {
+						if (!begin()) { failed = true; break; }
+#pragma unroll
+						for (int l = 0; l < 4; ++l) step(gB, ring_of(l), xrow0 + xoff_of(chunk, l), xrow1 + xoff_of(chunk, l));
+						if (pendA) {
+							flush(gA, giA);
+							pendA = false;
+						}
+						left -= 4;
+						++chunk;
+						done = (left == 0) || (chunk == w_hi);
+						end();
+					} while (!done);
+					if (failed) break;
+					pendB = true;
+					giB = gi;
+					if (left == 0) {
+						++gi;
+						left = p.spg;
+					}
 				}
+				if (pendA) flush(gA, giA);
+				if (pendB) flush(gB, giB);
 			} else {
 				// 32- or 64-row groups: SPG_T steps per group, flushes at compile-time positions
 				constexpr int SP = SPG_T ? SPG_T : 1;
@@ -504,6 +513,23 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 					}
 					end();
 				}
+			}
+			if (NSTREAM == 1 || s == 0) {
+#pragma unroll
+				for (int b = 0; b < MB; ++b)
+#pragma unroll
+					for (int c = 0; c < 4; ++c) {
+						acc[0][b][c][0] = accw[b][c][0];
+						acc[0][b][c][1] = accw[b][c][1];
+					}
+			} else {
+#pragma unroll
+				for (int b = 0; b < MB; ++b)
+#pragma unroll
+					for (int c = 0; c < 4; ++c) {
+						acc[NSTREAM - 1][b][c][0] = accw[b][c][0];
+						acc[NSTREAM - 1][b][c][1] = accw[b][c][1];
+					}
 			}
 			if (failed) break;
 		}
@@ -536,7 +562,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	if (M8) {
 		// few rows: one element per thread and pass
 	for (int e = tid; e < nelem; e += NT) {
-			const int s = e / (p.M * SK_BN), rc = e - s * (p.M * SK_BN);
+			const int s = (NSTREAM == 2 && e >= p.M * SK_BN) ? 1 : 0, rc = e - s * (p.M * SK_BN);
 			const int row = rc >> 7, col = rc & 127;
 			float v = 0.f;
 #pragma unroll
@@ -553,7 +579,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 				}
 				v -= corr;
 			}
-			if (p.splitk == 1 || p.cluster)
+			if (p.splitk == 1)
 				red[((size_t)s * ROWS + row) * SK_BN + col] = v;
 			else
 				__stcg(wsp + e, v);
@@ -592,14 +618,14 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 #pragma unroll
 				for (int k = 0; k < KW; ++k) v += red[((size_t)(k * NSTREAM + s) * ROWS + row) * SK_BN + col];
 				v -= corr[i];
-				if (p.splitk == 1 || p.cluster)
+				if (p.splitk == 1)
 					red[((size_t)s * ROWS + row) * SK_BN + col] = v;
 				else
 					__stcg(wsp + (size_t)s * p.M * SK_BN + row * SK_BN + col, v);
 			}
 		}
 	}
-	if (p.splitk > 1 && !p.cluster) {
+	if (p.splitk > 1) {
 		__threadfence();
 		__syncthreads();
 		if (tid == 0) {
@@ -615,7 +641,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		const float *wt = p.ws_partial + (size_t)tile * p.splitk * nelem;
 		if (M8) {
 		for (int e = tid; e < nelem; e += NT) {
-				const int s = e / (p.M * SK_BN), rc = e - s * (p.M * SK_BN);
+				const int s = (NSTREAM == 2 && e >= p.M * SK_BN) ? 1 : 0, rc = e - s * (p.M * SK_BN);
 				const int row = rc >> 7, col = rc & 127;
 				float part[16];       // split-K <= 16; loads first, then a fixed-order sum
 #pragma unroll
@@ -639,7 +665,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 				for (int j = 0; j < 4; ++j) {
 					const int e = e0 + j * NT;
 					if (e < nelem) {
-						const int s = e / (p.M * SK_BN), rc = e - s * (p.M * SK_BN);
+						const int s = (NSTREAM == 2 && e >= p.M * SK_BN) ? 1 : 0, rc = e - s * (p.M * SK_BN);
 						red[((size_t)s * ROWS + (rc >> 7)) * SK_BN + (rc & 127)] = v[j];
 					}
 				}
@@ -648,45 +674,9 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	}
 	__syncthreads();
 
-	// ---- cluster mode: every CTA of the cluster finishes a share of the tile.  It sums the
-	// partials of all ranks over distributed shared memory, in rank order (deterministic).
 	const int epi_n = (EPI == EPI_ROPE) ? p.M * 64 : p.M * SK_BN;
-	int e_lo = 0, e_hi = epi_n;
+	const int e_lo = 0, e_hi = epi_n;
 	const float *fin = red;
-	if (p.cluster) {
-		namespace cg = cooperative_groups;
-		cg::cluster_group cluster = cg::this_cluster();
-		cluster.sync();
-		SK_STAMP(4);
-		const int per = (((epi_n + p.splitk - 1) / p.splitk) + 31) & ~31;
-		e_lo = min(split * per, epi_n);
-		e_hi = min(e_lo + per, epi_n);
-		float *finw = red + (size_t)NSTREAM * ROWS * SK_BN;       // slot of warp-row 1: free by now
-		for (int e = e_lo + tid; e < e_hi; e += NT) {
-			int idx[2];
-			int cnt;
-			if (EPI == EPI_ROPE) {
-				idx[0] = (e >> 6) * SK_BN + (e & 63);
-				idx[1] = idx[0] + 64;
-				cnt = 2;
-			} else {
-				idx[0] = (e >> 7) * SK_BN + (e & 127);
-				idx[1] = idx[0] + ROWS * SK_BN;                       // the second stream (SiLU epilogue)
-				cnt = NSTREAM;
-			}
-			for (int j = 0; j < cnt; ++j) {
-				float part[8];
-#pragma unroll
-				for (int r = 0; r < 8; ++r) part[r] = (r < p.splitk) ? *(cluster.map_shared_rank(red, r) + idx[j]) : 0.f;
-				float v = 0.f;
-#pragma unroll
-				for (int r = 0; r < 8; ++r) v += part[r];
-				finw[idx[j]] = v;
-			}
-		}
-		fin = finw;
-	}
-
 	SK_STAMP(5);
 	// ---- epilogue from shared memory ---------------------------------------------------------
 	if (EPI == EPI_PLAIN || EPI == EPI_SILU) {
@@ -731,7 +721,6 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			dst[d + 64] = __float2half_rn(o2);
 		}
 	}
-	if (p.cluster) cooperative_groups::this_cluster().sync();     // peers may still be reading this CTA's partials
 	SK_STAMP(6);
 }
 

@@ -160,28 +160,6 @@ def test_split_k_variants_agree_and_are_deterministic(G):
 		_lib.lib().gptq_debug_force_splitk(0)
 
 
-@pytest.mark.parametrize('M', [1, 16])
-def test_cluster_reduction_matches_workspace_reduction(G, M):
-	"""Split-K partials can be reduced through the workspace (default) or, as a thread-block
-	cluster, over distributed shared memory; both sum in the same fixed order."""
-	from gptq_triton_b200 import _lib
-	K, N, gs = 4096, 1024, 128
-	t = synth(K, N, gs, seed=3)
-	x = acts((M, K), seed=3).cuda()
-	d = {k: dev(v) for k, v in t.items() if isinstance(v, torch.Tensor)}
-	r32 = O.qmatmul_r32(x.cpu(), t['qweight'], t['qzeros'], t['scales'], gs)
-	try:
-		_lib.lib().gptq_debug_force_splitk(4)
-		a = G.qmatmul(gs, x, d['qweight'], d['scales'], d['qzeros'])
-		_lib.lib().gptq_debug_allow_cluster(1)
-		b = G.qmatmul(gs, x, d['qweight'], d['scales'], d['qzeros'])
-	finally:
-		_lib.lib().gptq_debug_allow_cluster(0)
-		_lib.lib().gptq_debug_force_splitk(0)
-	assert O.max_rel_err(a, r32) <= 6e-4
-	assert torch.equal(a, b)
-
-
 @pytest.mark.parametrize('name', ['a', 'b', 'c', 'd'])
 def test_against_reference_kernel_golden(G, golden_dir, name):
 	d = dict(np.load(golden_dir / f'matmul4_{name}.npz'))
