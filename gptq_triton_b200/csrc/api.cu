@@ -238,10 +238,10 @@ static int ensure_smem_attr(Kern k, bool (&ready)[64]) {
 	return GPTQ_OK;
 }
 
-template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI>
+template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI, int PERM_T>
 static int launch_skinny_inst(const CUtensorMap &tm0, const CUtensorMap &tm1, const SkinnyParams &p, dim3 grid, size_t smem,
 							  cudaStream_t stream) {
-	auto k = skinny_kernel<KW, NSTREAM, M8, SPG_T, EPI>;
+	auto k = skinny_kernel<KW, NSTREAM, M8, SPG_T, EPI, PERM_T>;
 	static bool ready[64] = {false};
 	if (int rc = ensure_smem_attr(k, ready)) return rc;
 	return launch_ex(k, grid, dim3(KW * 128, 1, 1), smem, stream, tm0, tm1, p);
@@ -273,19 +273,23 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	}
 	const bool m8 = p.M <= 8;
 	if (p.spg == 1) {
-		return m8 ? launch_skinny_inst<2, NSTREAM, true, 1, EPI>(tm0, tm1, p, grid, smem, stream)
-				  : launch_skinny_inst<2, NSTREAM, false, 1, EPI>(tm0, tm1, p, grid, smem, stream);
+		return m8 ? launch_skinny_inst<2, NSTREAM, true, 1, EPI, 2>(tm0, tm1, p, grid, smem, stream)
+				  : launch_skinny_inst<2, NSTREAM, false, 1, EPI, 2>(tm0, tm1, p, grid, smem, stream);
 	}
 	if (p.spg == 2) {
-		return m8 ? launch_skinny_inst<2, NSTREAM, true, 2, EPI>(tm0, tm1, p, grid, smem, stream)
-				  : launch_skinny_inst<2, NSTREAM, false, 2, EPI>(tm0, tm1, p, grid, smem, stream);
+		return m8 ? launch_skinny_inst<2, NSTREAM, true, 2, EPI, 2>(tm0, tm1, p, grid, smem, stream)
+				  : launch_skinny_inst<2, NSTREAM, false, 2, EPI, 2>(tm0, tm1, p, grid, smem, stream);
 	}
 	if (kw == 2) {
-		return m8 ? launch_skinny_inst<2, NSTREAM, true, 0, EPI>(tm0, tm1, p, grid, smem, stream)
-				  : launch_skinny_inst<2, NSTREAM, false, 0, EPI>(tm0, tm1, p, grid, smem, stream);
+		// the common kernels are compiled once per x addressing mode (less code per kernel)
+		if (p.perm == nullptr)
+			return m8 ? launch_skinny_inst<2, NSTREAM, true, 0, EPI, 0>(tm0, tm1, p, grid, smem, stream)
+					  : launch_skinny_inst<2, NSTREAM, false, 0, EPI, 0>(tm0, tm1, p, grid, smem, stream);
+		return m8 ? launch_skinny_inst<2, NSTREAM, true, 0, EPI, 1>(tm0, tm1, p, grid, smem, stream)
+				  : launch_skinny_inst<2, NSTREAM, false, 0, EPI, 1>(tm0, tm1, p, grid, smem, stream);
 	}
-	return m8 ? launch_skinny_inst<4, NSTREAM, true, 0, EPI>(tm0, tm1, p, grid, smem, stream)
-			  : launch_skinny_inst<4, NSTREAM, false, 0, EPI>(tm0, tm1, p, grid, smem, stream);
+	return m8 ? launch_skinny_inst<4, NSTREAM, true, 0, EPI, 2>(tm0, tm1, p, grid, smem, stream)
+			  : launch_skinny_inst<4, NSTREAM, false, 0, EPI, 2>(tm0, tm1, p, grid, smem, stream);
 }
 
 static int check_common(const void *x, const void *qw, const void *qz, const void *sc, const void *y, int M, int K, int N,
@@ -451,7 +455,7 @@ int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_
 	if (K % 8 != 0) return GPTQ_ERR_SHAPE;
 	if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || ldx % 8 || ldy % 8) return GPTQ_ERR_ALIGN;
 	if (M == 0) return GPTQ_OK;
-	return launch_ex(rmsnorm_kernel, dim3(M, 1, 1), dim3(256, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), (const __half *)x, (long long)ldx,
+	return launch_ex(rmsnorm_kernel, dim3(M, 1, 1), dim3(RN_THREADS, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), (const __half *)x, (long long)ldx,
 					 (const __half *)weight, (__half *)y, (long long)ldy, K, eps);
 }
 

@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	for (int i = 0; i < 16; ++i) acc[i] = 0.f;
 
 	constexpr int UNROLL = 4;          // keys in flight per 8-lane group
+#pragma unroll 1
 	for (int base = k_lo + warp * 4; base < k_hi; base += 16 * UNROLL) {      // trip count uniform within the warp
 		const int k0 = base + grp;
 		uint4 kr[UNROLL][2], vr[UNROLL][2];
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 #pragma unroll
 	for (int g = 0; g < 16; ++g) M = fmaxf(M, s_m[g]);
 	float L = 0.f, o = 0.f;            // thread tid owns output dim tid
-#pragma unroll
+#pragma unroll 4
 	for (int g = 0; g < 16; ++g) {
 		const float w = (s_m[g] == -INFINITY) ? 0.f : __expf(s_m[g] - M);
 		L = fmaf(s_l[g], w, L);
@@ -165,8 +166,10 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	__threadfence();
 	const float *wb = p.ws_partial + (size_t)bh * p.splits * 130;
 	float Mg = -INFINITY;
+#pragma unroll 4
 	for (int s = 0; s < p.splits; ++s) Mg = fmaxf(Mg, __ldcg(wb + s * 130));
 	float Lg = 0.f, og = 0.f;
+#pragma unroll 2
 	for (int s = 0; s < p.splits; ++s) {
 		const float ms = __ldcg(wb + s * 130);
 		const float w = (ms == -INFINITY) ? 0.f : __expf(ms - Mg);
@@ -177,44 +180,61 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 }
 
 // ---- RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, fp32 inside, one fp16 rounding ----------------
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const __half *__restrict__ x, long long ldx, const __half *__restrict__ w,
-													  __half *__restrict__ y, long long ldy, int K, float eps) {
-	const int row = blockIdx.x, tid = threadIdx.x;
-	const __half *xr = x + (size_t)row * ldx;
-	pdl_trigger();
-	pdl_wait();
+// One CTA of 512 threads per row.  A thread keeps its first 16-byte unit of x (and of w) in
+// registers across the reduction, so rows of up to 4096 elements are read once with a single
+// round trip to memory; longer rows loop over the remaining units.
+constexpr int RN_THREADS = 512;
+
+__device__ __forceinline__ float rn_sumsq(const uint4 &v) {
+	const __half2 *h = reinterpret_cast<const __half2 *>(&v);
 	float ss = 0.f;
-	for (int k = tid * 8; k < K; k += 256 * 8) {
-		const uint4 v = *reinterpret_cast<const uint4 *>(xr + k);
-		const __half2 *h = reinterpret_cast<const __half2 *>(&v);
 #pragma unroll
-		for (int i = 0; i < 4; ++i) {
-			const float2 f = __half22float2(h[i]);
-			ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
-		}
+	for (int i = 0; i < 4; ++i) {
+		const float2 f = __half22float2(h[i]);
+		ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
 	}
-	__shared__ float s_part[8];
+	return ss;
+}
+
+__device__ __forceinline__ uint4 rn_scale(const uint4 &v, const uint4 &g, float inv) {
+	const __half2 *h = reinterpret_cast<const __half2 *>(&v), *gh = reinterpret_cast<const __half2 *>(&g);
+	uint4 o;
+	__half2 *oh = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+	for (int i = 0; i < 4; ++i) {
+		const float2 f = __half22float2(h[i]), gg = __half22float2(gh[i]);
+		oh[i] = __floats2half2_rn(f.x * inv * gg.x, f.y * inv * gg.y);
+	}
+	return o;
+}
+
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const __half *__restrict__ x, long long ldx, const __half *__restrict__ w,
+															 __half *__restrict__ y, long long ldy, int K, float eps) {
+	const int row = blockIdx.x, tid = threadIdx.x;
+	const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * ldx);
+	const uint4 *wr = reinterpret_cast<const uint4 *>(w);
+	uint4 *yr = reinterpret_cast<uint4 *>(y + (size_t)row * ldy);
+	const int nu = K >> 3;
+	pdl_trigger();
+	uint4 g0 = make_uint4(0u, 0u, 0u, 0u), v0 = make_uint4(0u, 0u, 0u, 0u);
+	if (tid < nu) g0 = __ldg(wr + tid);                 // the weight does not depend on earlier kernels
+	pdl_wait();
+	if (tid < nu) v0 = xr[tid];
+	float ss = rn_sumsq(v0);
+#pragma unroll 1
+	for (int u = tid + RN_THREADS; u < nu; u += RN_THREADS) ss += rn_sumsq(xr[u]);
+	__shared__ float s_part[RN_THREADS / 32];
 #pragma unroll
 	for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
 	if ((tid & 31) == 0) s_part[tid >> 5] = ss;
 	__syncthreads();
 	float tot = 0.f;
 #pragma unroll
-	for (int i = 0; i < 8; ++i) tot += s_part[i];
+	for (int i = 0; i < RN_THREADS / 32; ++i) tot += s_part[i];
 	const float inv = rsqrtf(tot / (float)K + eps);
-	for (int k = tid * 8; k < K; k += 256 * 8) {
-		const uint4 v = *reinterpret_cast<const uint4 *>(xr + k);
-		const uint4 g = *reinterpret_cast<const uint4 *>(w + k);
-		const __half2 *h = reinterpret_cast<const __half2 *>(&v), *gh = reinterpret_cast<const __half2 *>(&g);
-		uint4 o;
-		__half2 *oh = reinterpret_cast<__half2 *>(&o);
-#pragma unroll
-		for (int i = 0; i < 4; ++i) {
-			const float2 f = __half22float2(h[i]), gg = __half22float2(gh[i]);
-			oh[i] = __floats2half2_rn(f.x * inv * gg.x, f.y * inv * gg.y);
-		}
-		*reinterpret_cast<uint4 *>(y + (size_t)row * ldy + k) = o;
-	}
+	if (tid < nu) yr[tid] = rn_scale(v0, g0, inv);
+#pragma unroll 1
+	for (int u = tid + RN_THREADS; u < nu; u += RN_THREADS) yr[u] = rn_scale(xr[u], __ldg(wr + u), inv);
 }
 
 }   // namespace gptq

@@ -96,7 +96,9 @@ struct SkinnyParams {
 #endif
 
 // SPG_T: steps per group known at compile time (1 or 2), or 0 when a group spans whole chunks.
-template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI>
+// PERM_T: 0 = x is read in order, 1 = x is gathered through p.perm (act-order), 2 = decided at
+// run time (the rarely used variants; keeps the common kernels free of the other path's code).
+template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI, int PERM_T>
 __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	skinny_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, const SkinnyParams p) {
 	extern __shared__ __align__(1024) unsigned char smem[];
@@ -225,7 +227,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	auto x_load = [&](int row0, int unit, uint4(&v)[XB]) {
 		if (unit >= units) return;
 		const int k = (c_lo * 16 + unit) * 8;
-		if (p.perm == nullptr) {
+		if (PERM_T == 0 || (PERM_T == 2 && p.perm == nullptr)) {
 #pragma unroll
 			for (int j = 0; j < XB; ++j)
 				if (row0 + j < p.M) v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)(row0 + j) * p.ldx + k));
@@ -296,6 +298,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		const int k_lo = c_lo * 128, k_hi = c_hi * 128;
 		const int sub = lane & 3;
 		const int total = ng * p.M;
+#pragma unroll 1
 		for (int it0 = 0; it0 < total; it0 += NWARP * 8) {       // uniform trip count: shuffles below
 			const int item = it0 + warp * 8 + (lane >> 2);
 			const bool valid = item < total;
@@ -303,6 +306,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			const int ka = max((g_lo + gi) * p.groupsize, k_lo), kb = min((g_lo + gi + 1) * p.groupsize, k_hi);
 			float e = 0.f, o = 0.f;
 			if (valid) {
+#pragma unroll 2
 				for (int u = (ka - k_lo) / 8 + sub; u < (kb - k_lo) / 8; u += 4) {
 					const uint4 v = *reinterpret_cast<const uint4 *>(xs + (size_t)row * p.xs_stride + u * 16);
 					const float2 a0 = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
@@ -561,7 +565,8 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	float *wsp = p.ws_partial + (size_t)(tile * p.splitk + split) * nelem;   // [stream][row < M][128]
 	if (M8) {
 		// few rows: one element per thread and pass
-	for (int e = tid; e < nelem; e += NT) {
+#pragma unroll 1
+		for (int e = tid; e < nelem; e += NT) {
 			const int s = (NSTREAM == 2 && e >= p.M * SK_BN) ? 1 : 0, rc = e - s * (p.M * SK_BN);
 			const int row = rc >> 7, col = rc & 127;
 			float v = 0.f;
@@ -573,6 +578,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 				const __half *zz = s_zz + (size_t)s * p.strip_groups * SK_BN + col;
 				const __half *sc = s_sc + (size_t)s * p.strip_groups * SK_BN + col;
 				float corr = 0.f;
+#pragma unroll 2
 				for (int gi = 0; gi < ng; ++gi) {
 					const float2 cs = s_cs[gi * 16 + row];
 					corr = fmaf(__half2float(sc[(size_t)gi * SK_BN]), fmaf(__half2float(zz[(size_t)gi * SK_BN]), cs.y, cs.x), corr);
@@ -598,6 +604,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		float corr[RPT];
 #pragma unroll
 		for (int i = 0; i < RPT; ++i) corr[i] = 0.f;
+#pragma unroll 1
 		for (int gi = 0; gi < ng; ++gi) {
 			const float sv = __half2float(sc[(size_t)gi * SK_BN]);
 			const float sz = sv * __half2float(zz[(size_t)gi * SK_BN]);
@@ -640,20 +647,26 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		__threadfence();
 		const float *wt = p.ws_partial + (size_t)tile * p.splitk * nelem;
 		if (M8) {
-		for (int e = tid; e < nelem; e += NT) {
+#pragma unroll 1
+			for (int e = tid; e < nelem; e += NT) {
 				const int s = (NSTREAM == 2 && e >= p.M * SK_BN) ? 1 : 0, rc = e - s * (p.M * SK_BN);
 				const int row = rc >> 7, col = rc & 127;
-				float part[16];       // split-K <= 16; loads first, then a fixed-order sum
+				float v = 0.f;        // eight loads in flight, then a fixed-order sum
+#pragma unroll 1
+				for (int k0 = 0; k0 < p.splitk; k0 += 8) {
+					float part[8];
 #pragma unroll
-				for (int k = 0; k < 16; ++k) part[k] = (k < p.splitk) ? __ldcg(wt + (size_t)k * nelem + e) : 0.f;
-				float v = 0.f;
+					for (int k = 0; k < 8; ++k) part[k] = (k0 + k < p.splitk) ? __ldcg(wt + (size_t)(k0 + k) * nelem + e) : 0.f;
 #pragma unroll
-				for (int k = 0; k < 16; ++k) v += part[k];
+					for (int k = 0; k < 8; ++k) v += part[k];
+				}
 				red[((size_t)s * ROWS + row) * SK_BN + col] = v;
 			}
 		} else {
-		for (int e0 = tid; e0 < nelem; e0 += NT * 4) {        // four elements in flight per thread; fixed split order
+#pragma unroll 1
+			for (int e0 = tid; e0 < nelem; e0 += NT * 4) {        // four elements in flight per thread; fixed split order
 				float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
 				for (int k = 0; k < p.splitk; ++k) {
 					float t[4];
 #pragma unroll
@@ -680,6 +693,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	SK_STAMP(5);
 	// ---- epilogue from shared memory ---------------------------------------------------------
 	if (EPI == EPI_PLAIN || EPI == EPI_SILU) {
+#pragma unroll 1
 		for (int e = e_lo + tid; e < e_hi; e += NT) {
 			const int row = e >> 7, col = e & 127, n = n0 + col;
 			if (n >= p.N) continue;
@@ -695,6 +709,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	} else {
 		// rotary: the tile is exactly one head (head_dim == 128) of section Q, K or V
 		const int section = n0 / p.hidden, head = (n0 - section * p.hidden) >> 7;
+#pragma unroll 1
 		for (int e = e_lo + tid; e < e_hi; e += NT) {
 			const int row = e >> 6, d = e & 63;
 			const float a = fin[(size_t)row * SK_BN + d], b = fin[(size_t)row * SK_BN + d + 64];
