@@ -28,6 +28,11 @@ _SIGNATURES = {
 	'gptq_gateup_silu': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P, c_size_t, _P]),
 	'gptq_qkv_rope': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int64, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64,
 							  c_int, c_int, c_int, c_int, c_int, c_int64, _P, c_size_t, _P]),
+	'gptq_qmatmul_sumsq': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P, c_size_t, _P, _P]),
+	'gptq_gateup_silu_rms': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P, c_size_t, _P,
+									 _P, _P, c_int, ctypes.c_float]),
+	'gptq_qkv_rope_rms': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int64, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64,
+								  c_int, c_int, c_int, c_int, c_int, c_int64, _P, c_size_t, _P, _P, _P, c_int, ctypes.c_float]),
 	'gptq_unpack_qweight': (c_int, [_P, _P, c_int, c_int, _P]),
 	'gptq_unpack_qzeros': (c_int, [_P, _P, c_int, c_int, _P]),
 	'gptq_dequantize': (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),
@@ -68,8 +73,8 @@ def lib() -> ctypes.CDLL:
 				fn = getattr(l, name)
 				fn.restype = res
 				fn.argtypes = args
-		if os.environ.get('GPTQ_B200_PDL', '0') == '1' and hasattr(l, 'gptq_debug_set_pdl'):
-			l.gptq_debug_set_pdl(1)      # opt in to programmatic dependent launch (A/B measurements)
+		if os.environ.get('GPTQ_B200_PDL', '1') == '0' and hasattr(l, 'gptq_debug_set_pdl'):
+			l.gptq_debug_set_pdl(0)      # opt out of programmatic dependent launch (A/B measurements)
 		_lib = l
 	return _lib
 

@@ -19,7 +19,7 @@ static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
 static int g_force_kw = 2;
 static int g_attn_splits = 0;     // tuning hook: 0 = heuristic
 static int g_use_tc = 1;          // tensor-core kernel for M > 16
-static int g_pdl = 0;             // programmatic dependent launch for the decode-step kernels (opt-in: measured no gain)
+static int g_pdl = 1;             // programmatic dependent launch for the decode-step kernels (+3 % on the decode step)
 #ifdef GPTQ_SK_TIMING
 static long long *g_dbg = nullptr;
 #endif
@@ -220,6 +220,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 	smem = layout(best_sk, best_kw, best_stage, cps, eff, p.xs_stride, p.xs_bytes, p.strip_groups);
 	p.chunks_per_split = cps;
 	p.splitk = eff;
+	p.pdl = g_pdl;
 	p.nstage = best_stage;
 	kw = best_kw;
 	grid = dim3(tiles, p.splitk, 1);
@@ -290,6 +291,16 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	}
 	return m8 ? launch_skinny_inst<4, NSTREAM, true, 0, EPI, 2>(tm0, tm1, p, grid, smem, stream)
 			  : launch_skinny_inst<4, NSTREAM, false, 0, EPI, 2>(tm0, tm1, p, grid, smem, stream);
+}
+
+// Folded RMSNorm (consumer side): decode kernel only, x read in order, at most 64 producer tiles.
+static int check_rms(const void *rms_weight, const float *sumsq_in, int sumsq_tiles, float eps, int M, const int32_t *g_idx,
+					 const int32_t *perm) {
+	if (!rms_weight) return (sumsq_in == nullptr) ? GPTQ_OK : GPTQ_ERR_INVALID;
+	if (!sumsq_in || sumsq_tiles <= 0 || !(eps >= 0.f)) return GPTQ_ERR_INVALID;
+	if (!aligned16(rms_weight)) return GPTQ_ERR_ALIGN;
+	if (M > 16 || g_idx || perm || sumsq_tiles > 64) return GPTQ_ERR_UNSUPPORTED;
+	return GPTQ_OK;
 }
 
 static int check_common(const void *x, const void *qw, const void *qz, const void *sc, const void *y, int M, int K, int N,
@@ -384,9 +395,10 @@ size_t gptq_workspace_bytes(int M, int K, int N) {
 	return std::max(skinny_ws_bytes(M, N, 2), tc_ws_bytes(M, N));
 }
 
-int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
-				 const int32_t *perm, const void *bias, const void *residual, int64_t ldr, void *y, int M, int K, int N,
-				 int groupsize, int64_t ldx, int64_t ldy, void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+static int qmatmul_impl(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
+						const int32_t *perm, const void *bias, const void *residual, int64_t ldr, void *y, int M, int K, int N,
+						int groupsize, int64_t ldx, int64_t ldy, void *workspace, size_t workspace_bytes, gptq_stream_t stream,
+						float *sumsq_out) {
 	int rc = check_common(x, qweight, qzeros, scales, y, M, K, N, groupsize, ldx, ldy);
 	if (rc != GPTQ_OK) return rc;
 	if (g_idx && perm) return GPTQ_ERR_INVALID;
@@ -394,6 +406,8 @@ int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, c
 	if (M == 0) return GPTQ_OK;
 	cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 	const bool fast = skinny_shape_ok(K, N, groupsize, g_idx) && (!perm || aligned16(perm));
+	// the per-tile sums of squares exist in the decode kernel only (whole 128-column tiles)
+	if (sumsq_out && !(fast && M <= 16 && N % 128 == 0)) return GPTQ_ERR_UNSUPPORTED;
 	if (fast && M <= 16) {
 		SkinnyParams p = {};
 		p.x = (const __half *)x; p.ldx = ldx;
@@ -402,6 +416,7 @@ int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, c
 		p.M = M; p.K = K; p.N = N; p.groupsize = groupsize;
 		p.bias = (const __half *)bias; p.residual = (const __half *)residual; p.ldr = ldr;
 		p.y = (__half *)y; p.ldy = ldy;
+		p.ss_out = sumsq_out;
 		return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, workspace, workspace_bytes, st);
 	}
 	if (fast && !perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
@@ -417,6 +432,22 @@ int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, c
 										  nullptr, g_idx, perm, (const __half *)bias, (const __half *)residual, ldr,
 										  (__half *)y, ldy, M, K, N, groupsize);
 	return cuda_status(cudaGetLastError());
+}
+
+int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
+				 const int32_t *perm, const void *bias, const void *residual, int64_t ldr, void *y, int M, int K, int N,
+				 int groupsize, int64_t ldx, int64_t ldy, void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+	return qmatmul_impl(x, qweight, qzeros, scales, g_idx, perm, bias, residual, ldr, y, M, K, N, groupsize, ldx, ldy, workspace,
+						workspace_bytes, stream, nullptr);
+}
+
+int gptq_qmatmul_sumsq(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
+					   const int32_t *perm, const void *bias, const void *residual, int64_t ldr, void *y, int M, int K, int N,
+					   int groupsize, int64_t ldx, int64_t ldy, void *workspace, size_t workspace_bytes, gptq_stream_t stream,
+					   float *sumsq_out) {
+	if (!sumsq_out) return GPTQ_ERR_INVALID;
+	return qmatmul_impl(x, qweight, qzeros, scales, g_idx, perm, bias, residual, ldr, y, M, K, N, groupsize, ldx, ldy, workspace,
+						workspace_bytes, stream, sumsq_out);
 }
 
 size_t gptq_attn_workspace_bytes(int batch, int heads) {
@@ -501,12 +532,14 @@ int gptq_qmatmul_noalloc(const void *x, const int32_t *qweight, const int32_t *q
 	return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, scratch, skinny_ws_bytes(M, N, 1), st);
 }
 
-int gptq_gateup_silu(const void *x, const int32_t *gate_qweight, const int32_t *gate_qzeros, const void *gate_scales,
-					 const int32_t *up_qweight, const int32_t *up_qzeros, const void *up_scales, const int32_t *g_idx,
-					 const int32_t *perm, void *y, int M, int K, int N, int groupsize, int64_t ldx, int64_t ldy,
-					 void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+static int gateup_impl(const void *x, const int32_t *gate_qweight, const int32_t *gate_qzeros, const void *gate_scales,
+					   const int32_t *up_qweight, const int32_t *up_qzeros, const void *up_scales, const int32_t *g_idx,
+					   const int32_t *perm, void *y, int M, int K, int N, int groupsize, int64_t ldx, int64_t ldy,
+					   void *workspace, size_t workspace_bytes, gptq_stream_t stream, const void *rms_weight,
+					   const float *sumsq_in, int sumsq_tiles, float rms_eps) {
 	int rc = check_common(x, gate_qweight, gate_qzeros, gate_scales, y, M, K, N, groupsize, ldx, ldy);
 	if (rc != GPTQ_OK) return rc;
+	if ((rc = check_rms(rms_weight, sumsq_in, sumsq_tiles, rms_eps, M, g_idx, perm)) != GPTQ_OK) return rc;
 	if (!up_qweight || !up_qzeros || !up_scales) return GPTQ_ERR_INVALID;
 	if (!aligned16(up_qweight) || !aligned16(up_qzeros) || !aligned16(up_scales)) return GPTQ_ERR_ALIGN;
 	if (g_idx && perm) return GPTQ_ERR_INVALID;
@@ -521,8 +554,10 @@ int gptq_gateup_silu(const void *x, const int32_t *gate_qweight, const int32_t *
 		p.perm = perm;
 		p.M = M; p.K = K; p.N = N; p.groupsize = groupsize;
 		p.y = (__half *)y; p.ldy = ldy;
+		p.rms_w = (const __half *)rms_weight; p.ss_in = sumsq_in; p.ss_tiles = sumsq_tiles; p.rms_eps = rms_eps;
 		return launch_skinny<2, EPI_SILU>(p, gate_qweight, up_qweight, workspace, workspace_bytes, st);
 	}
+	if (rms_weight) return GPTQ_ERR_UNSUPPORTED;
 	if (fast && !perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};
 		a.x = (const __half *)x; a.ldx = ldx;
@@ -539,11 +574,30 @@ int gptq_gateup_silu(const void *x, const int32_t *gate_qweight, const int32_t *
 	return cuda_status(cudaGetLastError());
 }
 
-int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
-				  const int32_t *perm, const void *cos, const void *sin, const int32_t *position_ids, int max_pos, void *q_out,
-				  int64_t q_stride_m, void *k_out, void *v_out, int tokens_per_batch, int64_t kv_stride_b,
-				  int64_t kv_stride_t, int64_t kv_stride_h, int64_t kv_stride_pos, int M, int K, int n_heads, int head_dim,
-				  int groupsize, int64_t ldx, void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+int gptq_gateup_silu(const void *x, const int32_t *gate_qweight, const int32_t *gate_qzeros, const void *gate_scales,
+					 const int32_t *up_qweight, const int32_t *up_qzeros, const void *up_scales, const int32_t *g_idx,
+					 const int32_t *perm, void *y, int M, int K, int N, int groupsize, int64_t ldx, int64_t ldy,
+					 void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+	return gateup_impl(x, gate_qweight, gate_qzeros, gate_scales, up_qweight, up_qzeros, up_scales, g_idx, perm, y, M, K, N,
+					   groupsize, ldx, ldy, workspace, workspace_bytes, stream, nullptr, nullptr, 0, 0.f);
+}
+
+int gptq_gateup_silu_rms(const void *x, const int32_t *gate_qweight, const int32_t *gate_qzeros, const void *gate_scales,
+						 const int32_t *up_qweight, const int32_t *up_qzeros, const void *up_scales, const int32_t *g_idx,
+						 const int32_t *perm, void *y, int M, int K, int N, int groupsize, int64_t ldx, int64_t ldy,
+						 void *workspace, size_t workspace_bytes, gptq_stream_t stream, const void *rms_weight,
+						 const float *sumsq_in, int sumsq_tiles, float rms_eps) {
+	if (!rms_weight) return GPTQ_ERR_INVALID;
+	return gateup_impl(x, gate_qweight, gate_qzeros, gate_scales, up_qweight, up_qzeros, up_scales, g_idx, perm, y, M, K, N,
+					   groupsize, ldx, ldy, workspace, workspace_bytes, stream, rms_weight, sumsq_in, sumsq_tiles, rms_eps);
+}
+
+static int qkv_rope_impl(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
+						 const int32_t *perm, const void *cos, const void *sin, const int32_t *position_ids, int max_pos, void *q_out,
+						 int64_t q_stride_m, void *k_out, void *v_out, int tokens_per_batch, int64_t kv_stride_b,
+						 int64_t kv_stride_t, int64_t kv_stride_h, int64_t kv_stride_pos, int M, int K, int n_heads, int head_dim,
+						 int groupsize, int64_t ldx, void *workspace, size_t workspace_bytes, gptq_stream_t stream,
+						 const void *rms_weight, const float *sumsq_in, int sumsq_tiles, float rms_eps) {
 	if (!x || !qweight || !qzeros || !scales || !cos || !sin || !position_ids || !q_out || !k_out || !v_out)
 		return GPTQ_ERR_INVALID;
 	if (M < 0 || K <= 0 || n_heads <= 0 || tokens_per_batch <= 0 || max_pos <= 0) return GPTQ_ERR_INVALID;
@@ -557,10 +611,12 @@ int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, 
 	if (!aligned16(x) || !aligned16(qweight) || !aligned16(qzeros) || !aligned16(scales)) return GPTQ_ERR_ALIGN;
 	if (g_idx) return GPTQ_ERR_UNSUPPORTED;       // act-order must be prepared with gptq_act_order_rows (perm)
 	if (!skinny_shape_ok(K, N, groupsize, nullptr) || (perm && !aligned16(perm))) return GPTQ_ERR_UNSUPPORTED;
+	if (int rc = check_rms(rms_weight, sumsq_in, sumsq_tiles, rms_eps, M, g_idx, perm)) return rc;
 	if (M == 0) return GPTQ_OK;
 	cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 	if (M <= 16) {
 		SkinnyParams p = {};
+		p.rms_w = (const __half *)rms_weight; p.ss_in = sumsq_in; p.ss_tiles = sumsq_tiles; p.rms_eps = rms_eps;
 		p.x = (const __half *)x; p.ldx = ldx;
 		p.qz0 = qzeros; p.sc0 = (const __half *)scales;
 		p.perm = perm;
@@ -582,6 +638,28 @@ int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, 
 		return tc_launch(a, TC_EPI_ROPE, workspace, workspace_bytes, st);
 	}
 	return GPTQ_ERR_UNSUPPORTED;
+}
+
+int gptq_qkv_rope(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
+				  const int32_t *perm, const void *cos, const void *sin, const int32_t *position_ids, int max_pos, void *q_out,
+				  int64_t q_stride_m, void *k_out, void *v_out, int tokens_per_batch, int64_t kv_stride_b,
+				  int64_t kv_stride_t, int64_t kv_stride_h, int64_t kv_stride_pos, int M, int K, int n_heads, int head_dim,
+				  int groupsize, int64_t ldx, void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+	return qkv_rope_impl(x, qweight, qzeros, scales, g_idx, perm, cos, sin, position_ids, max_pos, q_out, q_stride_m, k_out, v_out,
+						 tokens_per_batch, kv_stride_b, kv_stride_t, kv_stride_h, kv_stride_pos, M, K, n_heads, head_dim, groupsize,
+						 ldx, workspace, workspace_bytes, stream, nullptr, nullptr, 0, 0.f);
+}
+
+int gptq_qkv_rope_rms(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
+					  const int32_t *perm, const void *cos, const void *sin, const int32_t *position_ids, int max_pos, void *q_out,
+					  int64_t q_stride_m, void *k_out, void *v_out, int tokens_per_batch, int64_t kv_stride_b,
+					  int64_t kv_stride_t, int64_t kv_stride_h, int64_t kv_stride_pos, int M, int K, int n_heads, int head_dim,
+					  int groupsize, int64_t ldx, void *workspace, size_t workspace_bytes, gptq_stream_t stream,
+					  const void *rms_weight, const float *sumsq_in, int sumsq_tiles, float rms_eps) {
+	if (!rms_weight) return GPTQ_ERR_INVALID;
+	return qkv_rope_impl(x, qweight, qzeros, scales, g_idx, perm, cos, sin, position_ids, max_pos, q_out, q_stride_m, k_out, v_out,
+						 tokens_per_batch, kv_stride_b, kv_stride_t, kv_stride_h, kv_stride_pos, M, K, n_heads, head_dim, groupsize,
+						 ldx, workspace, workspace_bytes, stream, rms_weight, sumsq_in, sumsq_tiles, rms_eps);
 }
 
 int gptq_unpack_qweight(const int32_t *qweight, uint8_t *out, int K, int N, gptq_stream_t stream) {

@@ -59,6 +59,7 @@ struct SkinnyParams {
 	int nstage;
 	int xs_stride;         // bytes between rows of the staged x slice
 	int xs_bytes;          // M * xs_stride rounded up to 128
+	int pdl;               // 1: launched with programmatic stream serialisation (x is loaded after pdl_wait)
 	int strip_groups;      // capacity (groups) of the zero / scale strips per stream
 	float *ws_partial;
 	int *ws_ticket;
@@ -68,6 +69,15 @@ struct SkinnyParams {
 	long long ldr;
 	__half *y;
 	long long ldy;
+	// RMSNorm folded in.  Producer (EPI_PLAIN): ss_out[row][tile] = sum over the tile's 128 columns of
+	// the squared fp16 outputs.  Consumer (EPI_SILU / EPI_ROPE, x read in order): x is scaled by
+	// rsqrt(sum_t ss_in[row][t] / K + eps) * rms_w while it is staged (one fp16 rounding, as the
+	// stand-alone RMSNorm kernel does).
+	float *ss_out;
+	const __half *rms_w;
+	const float *ss_in;
+	int ss_tiles;
+	float rms_eps;
 	// EPI_ROPE
 	const __half *cos_t, *sin_t;
 	const int32_t *pos;
@@ -224,9 +234,13 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	};
 	// x slice: a pass covers XB batch rows of one 16-byte unit per thread (same k for every row,
 	// so the act-order permutation is read once per pass)
-	auto x_load = [&](int row0, int unit, uint4(&v)[XB]) {
+	constexpr bool RMS_OK = (EPI != EPI_PLAIN) && (PERM_T == 0);
+	const bool rms = RMS_OK && p.rms_w != nullptr;
+	__shared__ float s_inv[16];
+	auto x_load = [&](int row0, int unit, uint4(&v)[XB], uint4 &wq) {
 		if (unit >= units) return;
 		const int k = (c_lo * 16 + unit) * 8;
+		if (rms) wq = __ldg(reinterpret_cast<const uint4 *>(p.rms_w + k));
 		if (PERM_T == 0 || (PERM_T == 2 && p.perm == nullptr)) {
 #pragma unroll
 			for (int j = 0; j < XB; ++j)
@@ -245,17 +259,32 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			}
 		}
 	};
-	auto x_store = [&](int row0, int unit, const uint4(&v)[XB]) {
+	auto x_store = [&](int row0, int unit, const uint4(&v)[XB], const uint4 &wq) {
 		// [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7, the (1,5) and (3,7) pairs divided by 16
 		if (unit >= units) return;
 #pragma unroll
 		for (int j = 0; j < XB; ++j) {
 			if (row0 + j < p.M) {
+				uint4 t = v[j];
+				if (rms) {
+					// x * inv_rms * w: fp32 product, one fp16 rounding (same expression as rmsnorm_kernel)
+					const float inv = s_inv[row0 + j];
+					const uint32_t tv[4] = {t.x, t.y, t.z, t.w}, wv[4] = {wq.x, wq.y, wq.z, wq.w};
+					uint32_t ov[4];
+#pragma unroll
+					for (int i = 0; i < 4; ++i) {
+						const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&tv[i]));
+						const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(&wv[i]));
+						const __half2 r = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
+						ov[i] = *reinterpret_cast<const uint32_t *>(&r);
+					}
+					t = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+				}
 				uint4 o;
-				o.x = __byte_perm(v[j].x, v[j].z, 0x5410);                          // (x0, x4)
-				o.y = h2_mul(__byte_perm(v[j].x, v[j].z, 0x7632), 0x2C002C00u);    // (x1, x5) / 16
-				o.z = __byte_perm(v[j].y, v[j].w, 0x5410);                          // (x2, x6)
-				o.w = h2_mul(__byte_perm(v[j].y, v[j].w, 0x7632), 0x2C002C00u);    // (x3, x7) / 16
+				o.x = __byte_perm(t.x, t.z, 0x5410);                          // (x0, x4)
+				o.y = h2_mul(__byte_perm(t.x, t.z, 0x7632), 0x2C002C00u);    // (x1, x5) / 16
+				o.z = __byte_perm(t.y, t.w, 0x5410);                          // (x2, x6)
+				o.w = h2_mul(__byte_perm(t.y, t.w, 0x7632), 0x2C002C00u);    // (x3, x7) / 16
 				*reinterpret_cast<uint4 *>(xs + (size_t)(row0 + j) * p.xs_stride + unit * 16) = o;
 			}
 		}
@@ -265,7 +294,6 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		// weight prefetch).  Straight-line code that runs once costs instruction fetch, and this
 		// prologue used to be more than half of the kernel's code.
 		pdl_trigger();
-		pdl_wait();                                          // x, residual and the workspace come from earlier kernels
 		const int x_passes = ((p.M + XB - 1) / XB) * ((units + NT - 1) / NT);      // (row block, unit block) pairs
 		const int u_blocks = (units + NT - 1) / NT;
 		const int n_it = max(max(1, x_passes), (n_strip + NT * SB - 1) / (NT * SB));
@@ -273,16 +301,35 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 #pragma unroll 1
 		for (int it = 0; it < n_it; ++it) {
 			uint32_t z0[SB];
-			uint4 sv0[SB], v0[XB];
+			uint4 sv0[SB], v0[XB], wq = make_uint4(0u, 0u, 0u, 0u);
 			strip_load(tid + it * NT * SB, z0, sv0);
-			if (it < x_passes) x_load(xr0, xu, v0);          // ahead of the prefetch burst in the memory queues
+			// x comes from the previous kernel: under programmatic dependent launch it may only be
+			// read after pdl_wait(), i.e. after the weight prefetch; otherwise it is issued first,
+			// ahead of the prefetch burst in the memory queues
+			const bool early = !p.pdl || it > 0;
+			if (early && it < x_passes) x_load(xr0, xu, v0, wq);
 			if (it == 0) {
 #pragma unroll 1
 				for (int s = 0; s < p.nstage; ++s) produce();    // weight prefetch: nstage chunks per warp
 				SK_STAMP(1);
+				pdl_wait();
+				if (!early && x_passes > 0) x_load(xr0, xu, v0, wq);
+				if (rms) {
+					// 1/rms of every row from the per-tile sums the producing kernel left (fixed order)
+#pragma unroll 1
+					for (int r = warp; r < p.M; r += NWARP) {
+						const float *sp = p.ss_in + (size_t)r * p.ss_tiles;
+						float t = (lane < p.ss_tiles) ? __ldcg(sp + lane) : 0.f;
+						if (lane + 32 < p.ss_tiles) t += __ldcg(sp + lane + 32);
+#pragma unroll
+						for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
+						if (lane == 0) s_inv[r] = rsqrtf(t / (float)p.K + p.rms_eps);
+					}
+					__syncthreads();
+				}
 			}
 			strip_store(tid + it * NT * SB, z0, sv0);
-			if (it < x_passes) x_store(xr0, xu, v0);
+			if (it < x_passes) x_store(xr0, xu, v0, wq);
 			xu += NT;
 			if (xu - tid >= u_blocks * NT) {
 				xu = tid;
@@ -693,18 +740,34 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	SK_STAMP(5);
 	// ---- epilogue from shared memory ---------------------------------------------------------
 	if (EPI == EPI_PLAIN || EPI == EPI_SILU) {
+		__shared__ float s_ss[64];                           // [row][quarter of the tile]
+		const bool want_ss = (EPI == EPI_PLAIN) && p.ss_out != nullptr;
 #pragma unroll 1
-		for (int e = e_lo + tid; e < e_hi; e += NT) {
+		for (int e = e_lo + tid; e < e_hi; e += NT) {        // whole warps enter or skip (bounds are multiples of 128)
 			const int row = e >> 7, col = e & 127, n = n0 + col;
-			if (n >= p.N) continue;
-			float v = fin[(size_t)row * SK_BN + col];
-			if (EPI == EPI_SILU) {
-				v = silu_f32(v) * fin[((size_t)ROWS + row) * SK_BN + col];
-			} else {
-				if (p.bias) v += __half2float(p.bias[n]);
-				if (p.residual) v += __half2float(p.residual[(size_t)row * p.ldr + n]);
+			float sq = 0.f;
+			if (n < p.N) {
+				float v = fin[(size_t)row * SK_BN + col];
+				if (EPI == EPI_SILU) {
+					v = silu_f32(v) * fin[((size_t)ROWS + row) * SK_BN + col];
+				} else {
+					if (p.bias) v += __half2float(p.bias[n]);
+					if (p.residual) v += __half2float(p.residual[(size_t)row * p.ldr + n]);
+				}
+				const __half hv = __float2half_rn(v);
+				p.y[(size_t)row * p.ldy + n] = hv;
+				const float f = __half2float(hv);
+				sq = f * f;
 			}
-			p.y[(size_t)row * p.ldy + n] = __float2half_rn(v);
+			if (want_ss) {
+#pragma unroll
+				for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+				if (lane == 0) s_ss[e >> 5] = sq;
+			}
+		}
+		if (want_ss) {
+			__syncthreads();
+			if (tid < p.M) p.ss_out[(size_t)tid * gridDim.x + tile] = (s_ss[tid * 4] + s_ss[tid * 4 + 1]) + (s_ss[tid * 4 + 2] + s_ss[tid * 4 + 3]);
 		}
 	} else {
 		// rotary: the tile is exactly one head (head_dim == 128) of section Q, K or V

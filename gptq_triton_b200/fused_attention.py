@@ -30,13 +30,16 @@ def rope_tables(head_dim: int, max_pos: int, theta: float = 10000.0, device=None
 
 def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin, position_ids, n_heads: int, head_dim: int,
 			 perm: Optional[torch.Tensor] = None, kv_cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-			 rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6):
+			 rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6, sumsq_in: Optional[torch.Tensor] = None):
 	"""One kernel: a x deq(Wqkv), rotary on Q and K, scatter to heads.
 
 	a: [b, t, K] fp16 contiguous; position_ids: [b, t] integer.
 	Without kv_cache returns (q, k, v) each [b, n_heads, t, head_dim] (k, v freshly allocated).
 	With kv_cache = (K, V) each [b, n_heads, max_seq, head_dim] contiguous, K/V rows are written
 	in place at their positions and (q, K, V) is returned.
+	With rms_weight the input is RMS-normalised first: inside the decode kernel when `sumsq_in`
+	(fp32 [M, K // 128], left by the projection that produced `a`) is given and the shape allows,
+	else by the RMSNorm kernel.
 	"""
 	assert a.dim() == 3 and a.is_contiguous(), "A must be [b, t, K] and contiguous"
 	assert a.shape[-1] == qweight.shape[0] * 8
@@ -58,7 +61,18 @@ def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin,
 		assert k.is_contiguous() and v.is_contiguous() and k.shape == v.shape and k.shape[0] >= b and k.shape[1] == n_heads and k.shape[3] == head_dim
 		S = k.shape[2]
 		sb, st, sh, sp = n_heads * S * head_dim, 0, S * head_dim, head_dim
-	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available
+	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available, rms_fusable
+	max_pos = min(cos.shape[0], (kv_cache[0].shape[2] if kv_cache is not None else cos.shape[0]))
+	if rms_weight is not None and sumsq_in is not None and rms_fusable(M, K, None, perm):
+		assert sumsq_in.dtype == torch.float32 and sumsq_in.is_contiguous() and sumsq_in.numel() >= M * (K // 128)
+		ws = _lib.workspace(a.device, M, K, 3 * hidden)
+		rc = _lib.lib().gptq_qkv_rope_rms(
+			_lib.ptr(a), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), None, None,
+			_lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), max_pos, _lib.ptr(q), hidden, _lib.ptr(k), _lib.ptr(v), t, sb, st, sh, sp,
+			M, K, n_heads, head_dim, groupsize, K, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device),
+			_lib.ptr(rms_weight), _lib.ptr(sumsq_in), K // 128, float(rms_eps))
+		_lib.check(rc, 'gptq_qkv_rope_rms')
+		return q.transpose(1, 2), k, v
 	if rms_weight is not None:
 		a = rmsnorm(a, rms_weight, rms_eps)          # the norm runs as its own kernel
 	if M > DECODE_MAX_M and perm is not None and prefill_kernel_available(M, K, 3 * hidden, groupsize):
@@ -84,7 +98,7 @@ def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin,
 	ws = _lib.workspace(a.device, M, K, 3 * hidden)
 	rc = _lib.lib().gptq_qkv_rope(
 		_lib.ptr(a), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), None, _lib.ptr(perm),
-		_lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), min(cos.shape[0], (kv_cache[0].shape[2] if kv_cache is not None else cos.shape[0])), _lib.ptr(q), hidden, _lib.ptr(k), _lib.ptr(v), t, sb, st, sh, sp,
+		_lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), max_pos, _lib.ptr(q), hidden, _lib.ptr(k), _lib.ptr(v), t, sb, st, sh, sp,
 		M, K, n_heads, head_dim, groupsize, K, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device))
 	_lib.check(rc, 'gptq_qkv_rope')
 	return q.transpose(1, 2), k, v
@@ -158,7 +172,7 @@ class QuantLlamaAttention(nn.Module):
 			self._tables = rope_tables(self.head_dim, n, self.rope_theta, device=device)
 		return self._tables
 
-	def project_qkv(self, hidden_states, position_ids, kv_cache=None, rms_weight=None, rms_eps=1e-6):
+	def project_qkv(self, hidden_states, position_ids, kv_cache=None, rms_weight=None, rms_eps=1e-6, sumsq_in=None):
 		qw, g_idx, perm = self.qkv_proj.kernel_operands()
 		if g_idx is not None:
 			raise NotImplementedError('fused QKV needs act-order groups of equal size')
@@ -168,7 +182,8 @@ class QuantLlamaAttention(nn.Module):
 		need = 0 if kv_cache is None else kv_cache[0].shape[2]      # a static cache fixes the position range
 		cos, sin = self.tables(hidden_states.device, need)
 		return qkv_rope(self.qkv_proj.groupsize, hidden_states, qw, self.qkv_proj.scales, self.qkv_proj.qzeros, cos, sin,
-						position_ids, self.num_heads, self.head_dim, perm=perm, kv_cache=kv_cache, rms_weight=rms_weight, rms_eps=rms_eps)
+						position_ids, self.num_heads, self.head_dim, perm=perm, kv_cache=kv_cache, rms_weight=rms_weight, rms_eps=rms_eps,
+						sumsq_in=sumsq_in)
 
 	def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
 				position_ids: Optional[torch.LongTensor] = None, past_key_value: Optional[Tuple[torch.Tensor]] = None,

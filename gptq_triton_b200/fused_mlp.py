@@ -41,10 +41,12 @@ def autotune_warmup(model):
 
 def gateup_silu(groupsize: int, a: torch.Tensor, gate_qweight, gate_scales, gate_qzeros, up_qweight, up_scales, up_qzeros,
 				g_idx: Optional[torch.Tensor] = None, perm: Optional[torch.Tensor] = None,
-				rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6) -> torch.Tensor:
+				rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6,
+				sumsq_in: Optional[torch.Tensor] = None) -> torch.Tensor:
 	"""silu(a x deq(gate)) * (a x deq(up)); fp32 until the one fp16 store.  With rms_weight the input is
-	RMS-normalised first by the library's RMSNorm kernel (folding the norm into the decode kernel was
-	tried and measured slower than the separate 2 us kernel)."""
+	RMS-normalised first: inside the decode kernel when `sumsq_in` (fp32 [M, tiles], written by the
+	projection that produced `a`, see quant_linear.qmatmul) is given and the shape allows, else by the
+	library's RMSNorm kernel."""
 	assert gate_qweight.shape == up_qweight.shape and gate_scales.shape == up_scales.shape and gate_qzeros.shape == up_qzeros.shape, "All weights must have the same shape"
 	assert a.shape[-1] == (gate_qweight.shape[0] * 8), "A must be a multiple of 8 in the last dimension"
 	assert a.is_contiguous(), "A must be contiguous"
@@ -57,7 +59,17 @@ def gateup_silu(groupsize: int, a: torch.Tensor, gate_qweight, gate_scales, gate
 	c = torch.empty((M, N), device=a.device, dtype=torch.float16)
 	if M == 0:
 		return c.view(a.shape[:-1] + (N,))
-	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available
+	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available, rms_fusable
+	if rms_weight is not None and sumsq_in is not None and rms_fusable(M, K, g_idx, perm):
+		assert sumsq_in.dtype == torch.float32 and sumsq_in.is_contiguous() and sumsq_in.numel() >= M * (K // 128)
+		ws = _lib.workspace(a.device, M, K, N)
+		rc = _lib.lib().gptq_gateup_silu_rms(
+			_lib.ptr(x), _lib.ptr(gate_qweight), _lib.ptr(gate_qzeros), _lib.ptr(gate_scales),
+			_lib.ptr(up_qweight), _lib.ptr(up_qzeros), _lib.ptr(up_scales), None, None,
+			_lib.ptr(c), M, K, N, groupsize, K, N, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device),
+			_lib.ptr(rms_weight), _lib.ptr(sumsq_in), K // 128, float(rms_eps))
+		_lib.check(rc, 'gptq_gateup_silu_rms')
+		return c.view(a.shape[:-1] + (N,))
 	if rms_weight is not None:
 		from .fused_attention import rmsnorm
 		x = rmsnorm(x.contiguous(), rms_weight, rms_eps)
@@ -132,15 +144,17 @@ class QuantLlamaMLP(nn.Module):
 					self._gidx = self.g_idx
 		self._ao_ready = True
 
-	def intermediate(self, x, rms_weight=None, rms_eps=1e-6):
+	def intermediate(self, x, rms_weight=None, rms_eps=1e-6, sumsq_in=None):
 		if not self._ao_ready:
 			self._prepare()
 		return gateup_silu(self.groupsize, x, self._gate_qw, self.gate_proj_scales, self.gate_proj_qzeros,
 						   self._up_qw, self.up_proj_scales, self.up_proj_qzeros, g_idx=self._gidx, perm=self._perm,
-						   rms_weight=rms_weight, rms_eps=rms_eps)
+						   rms_weight=rms_weight, rms_eps=rms_eps, sumsq_in=sumsq_in)
 
-	def forward(self, x, residual: Optional[torch.Tensor] = None, rms_weight=None, rms_eps=1e-6):
-		h = self.intermediate(x, rms_weight, rms_eps)
-		if residual is None:
+	def forward(self, x, residual: Optional[torch.Tensor] = None, rms_weight=None, rms_eps=1e-6, sumsq_in=None, sumsq_out=None):
+		"""`rms_weight` (+ `sumsq_in`): RMS-normalise x first (inside the kernel when sumsq_in is given);
+		`sumsq_out`: let down_proj leave the per-tile sums of squares of its output (decode sizes)."""
+		h = self.intermediate(x, rms_weight, rms_eps, sumsq_in)
+		if residual is None and sumsq_out is None:
 			return self.down_proj(h)
-		return self.down_proj(h, residual=residual)
+		return self.down_proj(h, residual=residual, sumsq_out=sumsq_out)

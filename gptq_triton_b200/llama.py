@@ -196,23 +196,33 @@ class DecodeEngine:
 		self.tok = torch.zeros((batch, 1), dtype=torch.int64, device=dev)          # token being fed
 		self.mask = torch.full((batch, 1, 1, max_seq), float('-inf'), dtype=torch.float16, device=dev)
 		self.use_graph = use_graph
-		self.fuse_norm = False       # True: pass the norm weights to the QKV / gate-up ops (same kernels underneath)
+		# RMSNorm folded into the decode kernels: o_proj / down_proj leave per-tile sums of squares of
+		# the hidden state, the next QKV / gate-up kernel scales x while staging it (one GPU only)
+		self.fuse_norm = True
+		tiles = max(1, cfg.hidden_size // 128)
+		self.ss_attn = torch.zeros((batch, tiles), dtype=torch.float32, device=dev)
+		self.ss_mlp = torch.zeros((batch, tiles), dtype=torch.float32, device=dev)
 		self.len_hint = max_seq
 		self.graph = None
 		self.launches_per_step = None
 
 	# -- one layer on hidden states h [b, t, hidden]; K/V go to the cache at `pos` --------------
-	def _layer(self, i, h, pos, attn_mask, kv_len):
+	# ss_in: per-tile sums of squares of h left by the projection that produced it (decode steps
+	# with the norms folded into the kernels); returns (h, ss of the new h or None).
+	def _layer(self, i, h, pos, attn_mask, kv_len, ss_in=None):
 		layer = self.model.model.layers[i]
 		attn: QuantLlamaAttention = layer.self_attn
 		decode = h.shape[1] == 1
 		ln1, ln2 = layer.input_layernorm, layer.post_attention_layernorm
-		if self.fuse_norm and decode:
-			q, _, _ = attn.project_qkv(h.contiguous(), pos, kv_cache=(self.kcache[i], self.vcache[i]), rms_weight=ln1.weight, rms_eps=ln1.variance_epsilon)
+		b = h.shape[0]
+		# the sums of squares describe the all-reduced hidden state only on one GPU
+		fold = self.fuse_norm and decode and self.tp_world == 1 and b <= 16 and self.cfg.hidden_size % 128 == 0 and self.cfg.hidden_size // 128 <= 64
+		if fold:
+			q, _, _ = attn.project_qkv(h.contiguous(), pos, kv_cache=(self.kcache[i], self.vcache[i]), rms_weight=ln1.weight,
+									   rms_eps=ln1.variance_epsilon, sumsq_in=ss_in)      # ss_in None (first layer): RMSNorm kernel
 		else:
 			x = rmsnorm_kernel(h.contiguous(), ln1.weight, ln1.variance_epsilon)
 			q, _, _ = attn.project_qkv(x, pos, kv_cache=(self.kcache[i], self.vcache[i]))
-		b = h.shape[0]
 		if decode:
 			# own single-query kernel over the static cache (length read from `pos` on the device)
 			o = attn_decode(q, self.kcache[i], self.vcache[i], pos, self.len_hint)
@@ -222,13 +232,19 @@ class DecodeEngine:
 			o = F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask)
 			o = o.transpose(1, 2).reshape(b, h.shape[1], -1)      # local heads x head_dim
 		res = h if self.tp_rank == 0 else None
-		h = attn.o_proj(o, residual=res)
+		mlp = layer.mlp
+		fold_mlp = fold and isinstance(mlp, QuantLlamaMLP) and attn.o_proj.g_idx is None
+		if fold_mlp:
+			h = attn.o_proj(o, residual=res, sumsq_out=self.ss_attn)
+		else:
+			h = attn.o_proj(o, residual=res)
 		if self.tp_world > 1:
 			all_reduce_(h, self.tp_group)
-		mlp = layer.mlp
 		res = h if self.tp_rank == 0 else None
-		if isinstance(mlp, QuantLlamaMLP) and self.fuse_norm and decode:
-			h = mlp(h, residual=res, rms_weight=ln2.weight, rms_eps=ln2.variance_epsilon)
+		ss_out = None
+		if fold_mlp:
+			ss_out = self.ss_mlp if mlp.down_proj.g_idx is None else None
+			h = mlp(h, residual=res, rms_weight=ln2.weight, rms_eps=ln2.variance_epsilon, sumsq_in=self.ss_attn, sumsq_out=ss_out)
 		elif isinstance(mlp, QuantLlamaMLP):
 			h = mlp(rmsnorm_kernel(h, ln2.weight, ln2.variance_epsilon), residual=res)
 		else:
@@ -236,7 +252,7 @@ class DecodeEngine:
 			h = mlp(x) if res is None else res + mlp(x)
 		if self.tp_world > 1:
 			all_reduce_(h, self.tp_group)
-		return h
+		return h, ss_out
 
 	@torch.no_grad()
 	def prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
@@ -247,7 +263,7 @@ class DecodeEngine:
 		mask = causal_mask(t, 0, self.device)
 		h = self.model.model.embed_tokens(input_ids)
 		for i in range(len(self.model.model.layers)):
-			h = self._layer(i, h, pos, mask, t)
+			h, _ = self._layer(i, h, pos, mask, t)
 		h = rmsnorm(h[:, -1:, :], self.model.model.norm.weight, self.model.model.norm.variance_epsilon)
 		logits = self.model.lm_head(h)
 		self.logits = logits
@@ -260,8 +276,9 @@ class DecodeEngine:
 
 	def _step_body(self):
 		h = self.model.model.embed_tokens(self.tok)
+		ss = None
 		for i in range(len(self.model.model.layers)):
-			h = self._layer(i, h, self.pos, self.mask, self.max_seq)
+			h, ss = self._layer(i, h, self.pos, self.mask, self.max_seq, ss)
 		h = rmsnorm_kernel(h, self.model.model.norm.weight, self.model.model.norm.variance_epsilon)
 		logits = self.model.lm_head(h)
 		self.logits = logits

@@ -86,7 +86,7 @@ def dequant_matmul(x2d: torch.Tensor, groupsize: int, qweight, scales, qzeros, g
 
 def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor,
 			bias: Optional[torch.Tensor] = None, g_idx: Optional[torch.Tensor] = None, perm: Optional[torch.Tensor] = None,
-			residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+			residual: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None) -> torch.Tensor:
 	"""C = A x deq(B) (+ bias) (+ residual).
 
 	A (..., K) fp16 contiguous; qweight (K//8, N) int32; scales (G, N) fp16; qzeros (G, N//8)
@@ -94,6 +94,8 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 	on the current CUDA stream — the contract of the reference op (quant_linear.py:228-283).
 	`g_idx` gives act-order groups for rows in checkpoint order; `perm` says that qweight was
 	re-ordered with act_order_rows().  `residual` (..., N) is added in the epilogue.
+	`sumsq_out` (fp32 [M, N // 128], decode sizes only) receives the per-tile sums of squares of
+	the output, from which the next fused op derives the RMSNorm factor (see rms_fusable()).
 	"""
 	assert a.shape[-1] == (qweight.shape[0] * 8), "A must be a multiple of 8 in the last dimension"
 	assert a.is_contiguous(), "A must be contiguous"
@@ -121,12 +123,26 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 			c = c + res
 		return c.view(a.shape[:-1] + (N,))
 	ws = _lib.workspace(a.device, M, K, N)
+	if sumsq_out is not None:
+		assert sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous() and sumsq_out.numel() >= M * (N // 128)
+		rc = _lib.lib().gptq_qmatmul_sumsq(
+			_lib.ptr(x), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), _lib.ptr(g_idx), _lib.ptr(perm),
+			_lib.ptr(bias), _lib.ptr(res), N, _lib.ptr(c), M, K, N, groupsize, K, N,
+			_lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device), _lib.ptr(sumsq_out))
+		_lib.check(rc, 'gptq_qmatmul_sumsq')
+		return c.view(a.shape[:-1] + (N,))
 	rc = _lib.lib().gptq_qmatmul(
 		_lib.ptr(x), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), _lib.ptr(g_idx), _lib.ptr(perm),
 		_lib.ptr(bias), _lib.ptr(res), N, _lib.ptr(c), M, K, N, groupsize, K, N,
 		_lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device))
 	_lib.check(rc, 'gptq_qmatmul')
 	return c.view(a.shape[:-1] + (N,))
+
+
+def rms_fusable(M: int, N_producer: int, g_idx, perm) -> bool:
+	"""True when the RMSNorm between a producing projection (N_producer outputs) and the next
+	fused op can be folded into the two decode kernels (gptq_qmatmul_sumsq -> *_rms)."""
+	return 0 < M <= DECODE_MAX_M and N_producer % 128 == 0 and N_producer // 128 <= 64 and g_idx is None and perm is None
 
 
 def triton_matmul4(groupsize: int, a: torch.FloatTensor, qweight: torch.IntTensor, scales: torch.FloatTensor,
@@ -240,6 +256,7 @@ class QuantLinear(nn.Module):
 			return self.qweight, self.g_idx, None
 		return self.qweight, None, None
 
-	def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+	def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None) -> torch.Tensor:
 		qw, g_idx, perm = self.kernel_operands()
-		return qmatmul(self.groupsize, x, qw, self.scales, self.qzeros, self.bias, g_idx=g_idx, perm=perm, residual=residual)
+		return qmatmul(self.groupsize, x, qw, self.scales, self.qzeros, self.bias, g_idx=g_idx, perm=perm, residual=residual,
+					   sumsq_out=sumsq_out)

@@ -159,6 +159,42 @@ int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_
                  int M, int K, float eps, gptq_stream_t stream);
 
 /*
+ * RMSNorm folded into the decode kernels (M <= 16).  No counterpart in the reference, whose
+ * decoder layer runs the HF LlamaRMSNorm module between its fused ops.  A decode step otherwise
+ * spends two extra launches per layer on the norm; here the projection that produces the
+ * hidden state also leaves per-tile sums of squares, and the next fused op scales x while it
+ * stages it:
+ *   gptq_qmatmul_sumsq   = gptq_qmatmul, and sumsq_out[row * (N/128) + tile] = sum over the
+ *                          tile's 128 columns of y^2 (y as rounded to fp16).  N % 128 == 0.
+ *   gptq_gateup_silu_rms = gptq_gateup_silu on x * rsqrt(sum_t sumsq_in[row*sumsq_tiles + t] / K
+ *   gptq_qkv_rope_rms      + rms_eps) * rms_weight (fp32 product, one fp16 rounding: the same
+ *                          expression as gptq_rmsnorm).  sumsq_tiles <= 64; no g_idx / perm.
+ * Shapes outside these limits return GPTQ_ERR_UNSUPPORTED; the caller then runs gptq_rmsnorm.
+ */
+int gptq_qmatmul_sumsq(const void *x, const int32_t *qweight, const int32_t *qzeros,
+                       const void *scales, const int32_t *g_idx, const int32_t *perm,
+                       const void *bias, const void *residual, int64_t ldr, void *y,
+                       int M, int K, int N, int groupsize, int64_t ldx, int64_t ldy,
+                       void *workspace, size_t workspace_bytes, gptq_stream_t stream,
+                       float *sumsq_out);
+int gptq_gateup_silu_rms(const void *x, const int32_t *gate_qweight, const int32_t *gate_qzeros,
+                         const void *gate_scales, const int32_t *up_qweight,
+                         const int32_t *up_qzeros, const void *up_scales, const int32_t *g_idx,
+                         const int32_t *perm, void *y, int M, int K, int N, int groupsize,
+                         int64_t ldx, int64_t ldy, void *workspace, size_t workspace_bytes,
+                         gptq_stream_t stream, const void *rms_weight, const float *sumsq_in,
+                         int sumsq_tiles, float rms_eps);
+int gptq_qkv_rope_rms(const void *x, const int32_t *qweight, const int32_t *qzeros,
+                      const void *scales, const int32_t *g_idx, const int32_t *perm,
+                      const void *cos, const void *sin, const int32_t *position_ids, int max_pos,
+                      void *q_out, int64_t q_stride_m, void *k_out, void *v_out,
+                      int tokens_per_batch, int64_t kv_stride_b, int64_t kv_stride_t,
+                      int64_t kv_stride_h, int64_t kv_stride_pos, int M, int K, int n_heads,
+                      int head_dim, int groupsize, int64_t ldx, void *workspace,
+                      size_t workspace_bytes, gptq_stream_t stream, const void *rms_weight,
+                      const float *sumsq_in, int sumsq_tiles, float rms_eps);
+
+/*
  * Allocation-free form of gptq_qmatmul for the decode regime (M <= 16).  No counterpart in the
  * reference.  It exists for callers that cannot provide or obtain scratch memory: a host that has
  * given the whole device to its own memory pool, or a latency-critical serving loop in which

@@ -513,3 +513,53 @@ def test_fused_rmsnorm_in_gateup_and_qkv(G, M, ao):
 						 rms_weight=gamma.cuda(), rms_eps=1e-6)
 	rq, rk, rv = O.qkv_rope_r32(xn, w['qweight'], w['qzeros'], w['scales'], gs, cos, sin, pos, H, D, g_idx=w['g_idx'])
 	assert O.max_rel_err(q.transpose(1, 2), rq) <= TOL and O.max_rel_err(k.transpose(1, 2), rk) <= TOL and O.max_rel_err(v.transpose(1, 2), rv) <= TOL
+
+
+@pytest.mark.parametrize('M', [1, 5, 16])
+def test_rmsnorm_folded_into_decode_kernels(G, M):
+	"""The projection that produces the hidden state leaves per-tile sums of squares; the next
+	fused op turns them into the RMSNorm factor while it stages x.  Checked against the
+	stand-alone norm (oracle arithmetic) and against the RMSNorm kernel path of the same ops."""
+	from gptq_triton_b200 import _lib
+	Kp, hidden, inter, gs, H, D = 512, 1024, 384, 128, 8, 128           # hidden = H * D
+	rng = torch.Generator().manual_seed(100 + M)
+	t = synth(Kp, hidden, gs, 81, bias=True)
+	xin = acts((M, Kp), seed=82)
+	res = (torch.randn((M, hidden), generator=rng) * 1.5).half()
+	ss = torch.zeros((M, hidden // 128), dtype=torch.float32, device='cuda')
+	h = G.qmatmul(gs, xin.cuda(), t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda(), bias=t['bias'].cuda(), residual=res.cuda(), sumsq_out=ss)
+	h_plain = G.qmatmul(gs, xin.cuda(), t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda(), bias=t['bias'].cuda(), residual=res.cuda())
+	assert torch.equal(h, h_plain), 'the extra output must not change y'
+	ss_ref = h.float().pow(2).view(M, hidden // 128, 128).sum(-1)
+	assert torch.allclose(ss, ss_ref, rtol=1e-5, atol=1e-6)
+	# consumers
+	gamma = (torch.rand((hidden,), generator=rng) + 0.5).half()
+	hd = h.cpu().double()
+	xn = (hd * torch.rsqrt(hd.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.double()).half().view(1, M, hidden)
+	g, u = synth(hidden, inter, gs, 83), synth(hidden, inter, gs, 84)
+	args = (h.view(1, M, hidden), g['qweight'].cuda(), g['scales'].cuda(), g['qzeros'].cuda(), u['qweight'].cuda(), u['scales'].cuda(), u['qzeros'].cuda())
+	y = G.gateup_silu(gs, *args, rms_weight=gamma.cuda(), rms_eps=1e-6, sumsq_in=ss)
+	y_sep = G.gateup_silu(gs, *args, rms_weight=gamma.cuda(), rms_eps=1e-6)
+	ref = O.gateup_silu_r32(xn, (g['qweight'], g['qzeros'], g['scales']), (u['qweight'], u['qzeros'], u['scales']), gs)
+	assert O.max_rel_err(y, ref) <= TOL
+	assert O.max_rel_err(y, y_sep.float().cpu()) <= 1e-3
+	w = synth(hidden, 3 * H * D, gs, 85)
+	pos = torch.arange(M).unsqueeze(0)
+	cos, sin = O.rope_tables(D, 64)
+	qa = (h.view(1, M, hidden), w['qweight'].cuda(), w['scales'].cuda(), w['qzeros'].cuda(), cos.cuda(), sin.cuda(), pos.cuda(), H, D)
+	q, k, v = G.qkv_rope(gs, *qa, rms_weight=gamma.cuda(), rms_eps=1e-6, sumsq_in=ss)
+	rq, rk, rv = O.qkv_rope_r32(xn, w['qweight'], w['qzeros'], w['scales'], gs, cos, sin, pos, H, D)
+	assert O.max_rel_err(q.transpose(1, 2), rq) <= TOL and O.max_rel_err(k.transpose(1, 2), rk) <= TOL and O.max_rel_err(v.transpose(1, 2), rv) <= TOL
+	torch.cuda.synchronize()
+	assert _lib.kernel_status() == 0
+
+
+def test_rms_folding_rejects_unsupported_shapes(G):
+	"""More than 64 producer tiles, or a prefill-sized M, are refused (the caller then uses the RMSNorm kernel)."""
+	from gptq_triton_b200 import _lib
+	K, N, gs = 256, 256, 128
+	t = synth(K, N, gs, 90)
+	x = acts((32, K), seed=91).cuda()
+	ss = torch.zeros((32, N // 128), dtype=torch.float32, device='cuda')
+	with pytest.raises(_lib.GptqB200Error):
+		G.qmatmul(gs, x, t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda(), sumsq_out=ss)
