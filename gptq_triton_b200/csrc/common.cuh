@@ -120,11 +120,26 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 	return ok;
 }
 
-// Bounded wait: returns false when the phase did not complete within `limit` polls.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+	unsigned long long t;
+	asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+	return t;
+}
+
+// Bounded wait: returns false when the phase did not complete within `limit` polls or within
+// about two seconds of wall time, whichever comes first (a poll may itself suspend the thread
+// for a while, so the poll count alone does not bound the time).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+	unsigned long long t0 = 0;
 #pragma unroll 1
-	for (uint32_t i = 0; i < limit; ++i)
+	for (uint32_t i = 0; i < limit; ++i) {
 		if (mbar_try_wait(bar, parity)) return true;
+		if ((i & 255u) == 255u) {
+			const unsigned long long now = global_timer_ns();
+			if (t0 == 0) t0 = now;
+			else if (now - t0 > 2000000000ull) return false;
+		}
+	}
 	return false;
 }
 

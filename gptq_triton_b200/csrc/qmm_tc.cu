@@ -1,7 +1,8 @@
 // Prefill-regime (M > 16) quantised matmul on the 5th-generation tensor cores of sm_100a.
 //
 // Y[M,N] = X[M,K] · deq(W)[K,N] with fp16 operands and fp32 accumulation in tensor memory.
-// One CTA computes a 128 (rows of X) x 128 (columns of W) tile; K advances in blocks of 64.
+// One CTA computes a 128 or 256 (rows of X) x 128 or 256 (columns of W) tile; K advances in blocks
+// of 64.  256-row tiles issue two M = 128 MMAs per K step against the same dequantised B stage.
 //
 //   warp 0      TMA producer: X tile [128 x 64] fp16, K-major, 128-byte swizzle (one thread)
 //   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::f16, M=128 N=128 K=16, four per
@@ -31,6 +32,9 @@ constexpr int TC_WORKERS = 512;                             // dequantise / epil
 constexpr int TC_THREADS = 64 + TC_WORKERS;
 constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;            // 16 KB: one A or B stage
 constexpr uint32_t TC_SPIN = 1u << 24;
+// pipeline depth by tile configuration (shared memory: S * (MH * 16 KB + NSTREAM * BN * 128 B) + packed ring)
+__host__ __device__ constexpr int tc_stages(int nstream, int bn, int mh) { return (mh == 2 && nstream * bn == 256) ? 3 : TC_STAGES; }
+__host__ __device__ constexpr int tc_pstages(int nstream, int bn, int mh) { return (mh == 2) ? (nstream * bn == 256 ? 3 : 6) : (nstream * bn == 256 ? 4 : 8); }
 
 // ---- tcgen05 / TMEM wrappers -------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -100,7 +104,7 @@ struct TcParams {
 }   // namespace
 
 // forward declaration of the kernel body (second half of this file)
-template <int NSTREAM, int EPI, int BN>
+template <int NSTREAM, int EPI, int BN, int MH>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw0,
 														   const __grid_constant__ CUtensorMap tmw1, const TcParams p);
 
@@ -112,8 +116,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 namespace gptq {
 
 EncodeTiledFn tensor_map_encoder();      // defined in api.cu
-int g_tc_wide = 1;
+int g_tc_wide = 1, g_tc_tall = 1;      // tuning hooks: allow 256-column / 256-row tiles
 extern "C" void gptq_debug_tc_wide(int on) { g_tc_wide = on ? 1 : 0; }
+extern "C" void gptq_debug_tc_tall(int on) { g_tc_tall = on ? 1 : 0; }
+int g_tc_force = 0;                    // tests: 0 = choose by cost, 1 = 128 x 128, 2 = 128 x 256, 3 = 256-row tiles
+extern "C" void gptq_debug_tc_force(int cfg) { g_tc_force = cfg; }
 #ifdef GPTQ_TC_TIMING
 long long *g_tc_dbg = nullptr;
 extern "C" void gptq_debug_set_tc_timing(long long *b) { g_tc_dbg = b; }
@@ -158,11 +165,12 @@ static int w_tensor_map(const int32_t *qw, int K, int N, int bn, CUtensorMap *ou
 	return GPTQ_OK;
 }
 
-template <int NSTREAM, int EPI, int BN>
+template <int NSTREAM, int EPI, int BN, int MH>
 static int tc_launch_inst(const CUtensorMap &tmx, const TcParams &p, cudaStream_t stream) {
-	auto k = tc_kernel<NSTREAM, EPI, BN>;
-	constexpr int PS = (NSTREAM * BN == 256) ? 4 : 8;
-	const size_t smem = (size_t)TC_STAGES * (TC_TILE_BYTES + NSTREAM * BN * TC_BK * 2) + (size_t)PS * NSTREAM * 8 * BN * 4 + 512;
+	auto k = tc_kernel<NSTREAM, EPI, BN, MH>;
+	constexpr int S = tc_stages(NSTREAM, BN, MH), PS = tc_pstages(NSTREAM, BN, MH);
+	const size_t smem = (size_t)S * (MH * TC_TILE_BYTES + NSTREAM * BN * TC_BK * 2) + (size_t)PS * NSTREAM * 8 * BN * 4 + 512;
+	static_assert((size_t)S * (MH * TC_TILE_BYTES + NSTREAM * BN * TC_BK * 2) + (size_t)PS * NSTREAM * 8 * BN * 4 + 512 <= 232448, "shared memory per CTA");
 	alignas(64) CUtensorMap tmw0, tmw1;
 	if (int rc = w_tensor_map(p.a.qw0, p.a.K, p.a.N, BN, &tmw0)) return rc;
 	if (NSTREAM == 2) {
@@ -178,7 +186,7 @@ static int tc_launch_inst(const CUtensorMap &tmx, const TcParams &p, cudaStream_
 		if (e != cudaSuccess) return cuda_status(e);
 		ready[dev] = true;
 	}
-	dim3 grid(p.a.N / BN, (p.a.M + TC_BM - 1) / TC_BM, 1);
+	dim3 grid(p.a.N / BN, (p.a.M + TC_BM * MH - 1) / (TC_BM * MH), 1);
 	k<<<grid, TC_THREADS, smem, stream>>>(tmx, tmw0, tmw1, p);
 	return cuda_status(cudaGetLastError());
 }
@@ -196,14 +204,30 @@ int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaSt
 #ifdef GPTQ_TC_TIMING
 	p.dbg = g_tc_dbg;
 #endif
-	// 256-column tiles (one N = 256 MMA per K step reads the X tile once for twice the work) when N allows
+	// Tile choice: estimated time = waves * (rows * columns of a tile) / relative speed of the configuration
+	// (measured per busy SM: 128 x 128 tiles 1.0, 128 x 256 tiles 1.7, 256-row tiles 2.5).
 	int dev = 0, sms = 148;
 	if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-	const bool wide = g_tc_wide && (a.N % 256 == 0) && (a.N / 256) * ((a.M + TC_BM - 1) / TC_BM) >= sms;      // else more, narrower CTAs
+	auto cost = [&](int bm, int bn, double speed) {
+		if (a.N % bn != 0) return 1e30;
+		const long long tiles = (long long)(a.N / bn) * ((a.M + bm - 1) / bm);
+		const long long waves = (tiles + sms - 1) / sms;
+		return (double)waves * bm * bn / speed;
+	};
+	if (epi == TC_EPI_SILU) {
+		const bool tall = g_tc_force ? (g_tc_force == 3) : (g_tc_tall && cost(256, 128, 1.5) < cost(128, 128, 1.0));
+		return tall ? tc_launch_inst<2, TC_EPI_SILU, 128, 2>(tmx, p, stream) : tc_launch_inst<2, TC_EPI_SILU, 128, 1>(tmx, p, stream);
+	}
+	const double c_n = cost(128, 128, 1.0), c_w = g_tc_wide ? cost(128, 256, 1.7) : 1e30, c_t = g_tc_tall ? cost(256, 256, 2.5) : 1e30;
+	int pick = (c_t <= c_w && c_t <= c_n) ? 2 : (c_w <= c_n ? 1 : 0);
+	if (g_tc_force) pick = (g_tc_force - 1 >= 1 && a.N % 256 != 0) ? 0 : g_tc_force - 1;
 	switch (epi) {
-		case TC_EPI_PLAIN: return wide ? tc_launch_inst<1, TC_EPI_PLAIN, 256>(tmx, p, stream) : tc_launch_inst<1, TC_EPI_PLAIN, 128>(tmx, p, stream);
-		case TC_EPI_SILU: return tc_launch_inst<2, TC_EPI_SILU, 128>(tmx, p, stream);
-		case TC_EPI_ROPE: return wide ? tc_launch_inst<1, TC_EPI_ROPE, 256>(tmx, p, stream) : tc_launch_inst<1, TC_EPI_ROPE, 128>(tmx, p, stream);
+		case TC_EPI_PLAIN:
+			return pick == 2 ? tc_launch_inst<1, TC_EPI_PLAIN, 256, 2>(tmx, p, stream)
+				 : pick == 1 ? tc_launch_inst<1, TC_EPI_PLAIN, 256, 1>(tmx, p, stream) : tc_launch_inst<1, TC_EPI_PLAIN, 128, 1>(tmx, p, stream);
+		case TC_EPI_ROPE:
+			return pick == 2 ? tc_launch_inst<1, TC_EPI_ROPE, 256, 2>(tmx, p, stream)
+				 : pick == 1 ? tc_launch_inst<1, TC_EPI_ROPE, 256, 1>(tmx, p, stream) : tc_launch_inst<1, TC_EPI_ROPE, 128, 1>(tmx, p, stream);
 	}
 	return GPTQ_ERR_INVALID;
 }

@@ -1,14 +1,23 @@
 // Body of the tcgen05 prefill kernel; included by qmm_tc.cu.
 namespace gptq {
 
-template <int NSTREAM, int EPI, int BN>
+template <int NSTREAM, int EPI, int BN, int MH>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw0,
 																 const __grid_constant__ CUtensorMap tmw1, const TcParams p) {
 	extern __shared__ __align__(1024) unsigned char smem[];
-	constexpr int S = TC_STAGES;
-	static_assert(NSTREAM * BN <= 256, "one accumulator set of at most 256 TMEM columns");
-	constexpr uint32_t TMEM_COLS = NSTREAM * BN;             // 128 or 256 fp32 columns
-	constexpr int PS = (NSTREAM * BN == 256) ? 4 : 8;        // stages of the packed-weight ring
+	// MH = 2: the CTA computes two 128-row halves (256 rows of X) against the same dequantised B
+	// stage: every weight is decoded once per 256 rows, and the MMAs of one stage run twice as long,
+	// which covers the release -> dequantise -> refill latency of a stage with fewer stages.
+	constexpr int S = tc_stages(NSTREAM, BN, MH);
+	// Dequantise groups (of 128 threads): as many as B stages, so that a group always returns to the
+	// same stage exactly one phase later (a group that ran two phases ahead of a stage's barrier would
+	// mistake an old phase for the one it waits for).  With three stages the fourth group only joins
+	// the epilogue.
+	constexpr int NG = S;
+	static_assert(NSTREAM * BN <= 256 && MH * NSTREAM * BN <= 512, "at most 512 TMEM columns");
+	constexpr uint32_t TMEM_COLS = MH * NSTREAM * BN;        // 128, 256 or 512 fp32 columns
+	constexpr int PS = tc_pstages(NSTREAM, BN, MH);          // stages of the packed-weight ring
+	constexpr int A_STAGE = MH * TC_TILE_BYTES;              // X tile(s) of one stage
 	constexpr int PW_BYTES = 8 * BN * 4;                     // packed tile of one K-block: 8 words x BN columns
 	constexpr int B_TILE = BN * TC_BK * 2;                   // dequantised B stage: BN rows x 128 bytes
 	constexpr int CPT = BN / 128;                            // weight columns per dequantise thread
@@ -16,11 +25,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 	const TcArgs &a = p.a;
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-	const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TC_BM;
+	const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (TC_BM * MH);
 	const int nkb = a.K / TC_BK;
 
-	unsigned char *sA = smem;                                              // [S][16 KB]
-	unsigned char *sB = smem + S * TC_TILE_BYTES;                          // [NSTREAM][S][16 KB]
+	unsigned char *sA = smem;                                              // [S][MH][16 KB]
+	unsigned char *sB = smem + S * A_STAGE;                                // [NSTREAM][S][B_TILE]
 	unsigned char *sW = sB + NSTREAM * S * B_TILE;                         // [PS][NSTREAM][PW_BYTES] packed words
 	uint64_t *bars = reinterpret_cast<uint64_t *>(sW + PS * NSTREAM * PW_BYTES);
 	const uint32_t bar_full_a = smem_u32(bars), bar_full_b = smem_u32(bars + S), bar_empty = smem_u32(bars + 2 * S);
@@ -76,8 +85,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				if (!feed_w(kb + PS)) { fail(); break; }
 				const int s = kb % S;
 				if (!mbar_wait_bounded(bar_empty + 8 * s, ((kb / S) & 1) ^ 1, TC_SPIN)) { fail(); break; }
-				mbar_arrive_expect_tx(bar_full_a + 8 * s, TC_TILE_BYTES);
-				tma_load_2d(smem_u32(sA + s * TC_TILE_BYTES), &tmx, kb * TC_BK, m0, bar_full_a + 8 * s);
+				mbar_arrive_expect_tx(bar_full_a + 8 * s, A_STAGE);
+#pragma unroll
+				for (int h = 0; h < MH; ++h)          // rows beyond M are filled with zeros by the copy
+					tma_load_2d(smem_u32(sA + s * A_STAGE + h * TC_TILE_BYTES), &tmx, kb * TC_BK, m0 + h * TC_BM, bar_full_a + 8 * s);
 			}
 		}
 	} else if (warp == 1) {
@@ -98,14 +109,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) { atomicAdd((unsigned long long *)p.dbg + 0, (unsigned long long)(t1 - t0)); atomicAdd((unsigned long long *)p.dbg + 1, (unsigned long long)(clock64() - t1)); }
 #endif
 				tc_fence_after();
-				const uint32_t a_addr = smem_u32(sA + s * TC_TILE_BYTES);
 #pragma unroll
-				for (int st = 0; st < NSTREAM; ++st) {
-					const uint32_t b_addr = smem_u32(sB + (st * S + s) * B_TILE);
+				for (int h = 0; h < MH; ++h) {
+					const uint32_t a_addr = smem_u32(sA + s * A_STAGE + h * TC_TILE_BYTES);
 #pragma unroll
-					for (int k = 0; k < TC_BK / 16; ++k)
-						umma_f16(tmem_base + st * BN, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), IDESC,
-								 (kb > 0 || k > 0) ? 1u : 0u);
+					for (int st = 0; st < NSTREAM; ++st) {
+						const uint32_t b_addr = smem_u32(sB + (st * S + s) * B_TILE);
+#pragma unroll
+						for (int k = 0; k < TC_BK / 16; ++k)
+							umma_f16(tmem_base + (h * NSTREAM + st) * BN, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), IDESC,
+									 (kb > 0 || k > 0) ? 1u : 0u);
+					}
 				}
 #ifdef GPTQ_TC_TIMING
 				const long long t5 = clock64();
@@ -119,8 +133,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 		}
 	} else {
 		// ---------------- dequantise producers, then epilogue ----------------
-		// Four groups of 128 threads; group j dequantises K-blocks j, j+4, ... into B stage j, so the
-		// groups' barrier round trips and proxy fences overlap.  Thread -> weight column wt of the tile.
+		// Four groups of 128 threads; group j dequantises K-blocks j, j+4, ... (into B stage kb % S), so
+		// the groups' barrier round trips and proxy fences overlap.  Thread -> weight column wt of the tile.
 		constexpr int RPT = 8, r0 = 0;
 		const int wt = (tid - 64) & 127, grp = (tid - 64) >> 7;         // columns wt (+128 when BN = 256)
 		const int nz = a.N >> 3, zsh = (wt & 7) * 4;
@@ -142,10 +156,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				sraw[u] = __half_as_ushort(__ldg(sc + (size_t)g * a.N + n));
 			}
 		};
-		fetch_group(min((grp * TC_BK) / a.groupsize, ngroups - 1));
+		if (grp < NG) fetch_group(min((grp * TC_BK) / a.groupsize, ngroups - 1));
 		int g_cur = -1;
 		bool ok = true;
-		for (int kb = grp; kb < nkb; kb += S) {
+		for (int kb = (grp < NG ? grp : nkb); kb < nkb; kb += NG) {
 			const int g = (kb * TC_BK) / a.groupsize;
 			if (g != g_cur) {
 				g_cur = g;
@@ -158,7 +172,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				}
 			}
 			{
-				const int g_next = ((kb + S) * TC_BK) / a.groupsize;      // group of this thread's next K-block
+				const int g_next = ((kb + NG) * TC_BK) / a.groupsize;     // group of this thread's next K-block
 				if (g_next < ngroups) fetch_group(g_next);                 // always: the registers then hold that group's data
 			}
 			{
@@ -223,8 +237,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 			tc_fence_after();
 			const int q = warp & 3;                             // TMEM lane quarter this warp may read
 			const int cq = (warp - 2) >> 2;                     // which 32-column chunk of the tile this warp drains
-			const int row = m0 + q * 32 + lane;
-			const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+			for (int h = 0; h < MH; ++h) {
+			const int row = m0 + h * TC_BM + q * 32 + lane;
+			const uint32_t t_row = tmem_base + (uint32_t)(h * NSTREAM * BN) + ((uint32_t)(q * 32) << 16);
 			const bool live = row < a.M;
 			if (EPI == TC_EPI_ROPE) {
 				// the tile holds BN/128 heads; warp group cq takes head cq>>1, rotary half cq&1
@@ -320,6 +336,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 					}
 				}
 			}
+			}
 		} else if (ok) {
 			fail();
 		}
@@ -327,6 +344,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 	tc_fence_before();
 	__syncthreads();
 	if (warp == 1) {
+		// tensor memory goes back only after every MMA issued above has completed (also when unwinding)
+		if (lane == 0) mbar_wait_bounded(bar_acc, 0, TC_SPIN);
 		__syncwarp();
 		tmem_dealloc(tmem_base, TMEM_COLS);
 	}

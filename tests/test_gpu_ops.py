@@ -462,6 +462,35 @@ def test_prefill_act_order_and_gateup_and_rope(G, M):
 	assert bool((kc[0, :, M:] == 0).all())
 
 
+@pytest.mark.parametrize('cfg', [1, 2, 3])
+@pytest.mark.parametrize('M', [100, 256, 300, 700])
+def test_prefill_every_tile_configuration(G, M, cfg):
+	"""128 x 128, 128 x 256 and 256-row tiles of the tensor-core kernel give the same results
+	(M = 100 / 300 / 700 leave the last 128-row half partly or wholly empty)."""
+	from gptq_triton_b200 import _lib
+	K, N, gs, H, D = 512, 768, 128, 2, 128
+	t = synth(K, N, gs, seed=cfg + M, bias=True)
+	g, u = synth(K, N, gs, 43), synth(K, N, gs, 44)
+	w = synth(K, 3 * H * D, gs, seed=62)
+	x = acts((M, K), seed=7)
+	res = acts((M, N), seed=8)
+	pos = torch.arange(M).unsqueeze(0)
+	cos, sin = O.rope_tables(D, 1024)
+	try:
+		_lib.lib().gptq_debug_tc_force(cfg)
+		y = G.qmatmul(gs, x.cuda(), t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda(), bias=t['bias'].cuda(), residual=res.cuda())
+		h = G.gateup_silu(gs, x.cuda(), g['qweight'].cuda(), g['scales'].cuda(), g['qzeros'].cuda(), u['qweight'].cuda(), u['scales'].cuda(), u['qzeros'].cuda())
+		q, k, v = G.qkv_rope(gs, x.view(1, M, K).cuda(), w['qweight'].cuda(), w['scales'].cuda(), w['qzeros'].cuda(), cos.cuda(), sin.cuda(), pos.cuda(), H, D)
+		torch.cuda.synchronize()
+	finally:
+		_lib.lib().gptq_debug_tc_force(0)
+	assert O.max_rel_err(y, O.qmatmul_r32(x, t['qweight'], t['qzeros'], t['scales'], gs, bias=t['bias'], residual=res)) <= TOL
+	assert O.max_rel_err(h, O.gateup_silu_r32(x, (g['qweight'], g['qzeros'], g['scales']), (u['qweight'], u['qzeros'], u['scales']), gs)) <= TOL
+	rq, rk, rv = O.qkv_rope_r32(x.view(1, M, K), w['qweight'], w['qzeros'], w['scales'], gs, cos, sin, pos, H, D)
+	assert O.max_rel_err(q.transpose(1, 2), rq) <= TOL and O.max_rel_err(k.transpose(1, 2), rk) <= TOL and O.max_rel_err(v.transpose(1, 2), rv) <= TOL
+	assert _lib.kernel_status() == 0
+
+
 def test_qkv_rope_position_outside_tables_is_reported_not_dereferenced(G):
 	"""A position beyond the cos/sin tables must not be used as an index: the kernel computes that
 	row at position 0 and raises status 4 in the workspace."""
