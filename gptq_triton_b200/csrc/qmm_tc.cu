@@ -119,7 +119,8 @@ EncodeTiledFn tensor_map_encoder();      // defined in api.cu
 int g_tc_wide = 1, g_tc_tall = 1;      // tuning hooks: allow 256-column / 256-row tiles
 extern "C" void gptq_debug_tc_wide(int on) { g_tc_wide = on ? 1 : 0; }
 extern "C" void gptq_debug_tc_tall(int on) { g_tc_tall = on ? 1 : 0; }
-int g_tc_force = 0;                    // tests: 0 = choose by cost, 1 = 128 x 128, 2 = 128 x 256, 3 = 256-row tiles
+int g_tc_force = 0;                    // tests: 0 = choose by cost, 1 = 128 x 128, 2 = 128 x 256, 3 = 256 x 256 (256 x 128 for two streams), 4 = 256 x 128
+constexpr double TC_SPEED_256x128 = 1.6;
 extern "C" void gptq_debug_tc_force(int cfg) { g_tc_force = cfg; }
 #ifdef GPTQ_TC_TIMING
 long long *g_tc_dbg = nullptr;
@@ -215,18 +216,24 @@ int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaSt
 		return (double)waves * bm * bn / speed;
 	};
 	if (epi == TC_EPI_SILU) {
-		const bool tall = g_tc_force ? (g_tc_force == 3) : (g_tc_tall && cost(256, 128, 1.5) < cost(128, 128, 1.0));
+		const bool tall = g_tc_force ? (g_tc_force >= 3) : (g_tc_tall && cost(256, 128, 1.5) < cost(128, 128, 1.0));
 		return tall ? tc_launch_inst<2, TC_EPI_SILU, 128, 2>(tmx, p, stream) : tc_launch_inst<2, TC_EPI_SILU, 128, 1>(tmx, p, stream);
 	}
-	const double c_n = cost(128, 128, 1.0), c_w = g_tc_wide ? cost(128, 256, 1.7) : 1e30, c_t = g_tc_tall ? cost(256, 256, 2.5) : 1e30;
-	int pick = (c_t <= c_w && c_t <= c_n) ? 2 : (c_w <= c_n ? 1 : 0);
-	if (g_tc_force) pick = (g_tc_force - 1 >= 1 && a.N % 256 != 0) ? 0 : g_tc_force - 1;
+	// configurations: 0 = 128 x 128, 1 = 128 x 256, 2 = 256 x 256, 3 = 256 x 128
+	const double c[4] = {cost(128, 128, 1.0), g_tc_wide ? cost(128, 256, 1.7) : 1e30, g_tc_tall ? cost(256, 256, 2.5) : 1e30,
+						 g_tc_tall ? cost(256, 128, TC_SPEED_256x128) : 1e30};
+	int pick = 0;
+	for (int i = 1; i < 4; ++i)
+		if (c[i] < c[pick]) pick = i;
+	if (g_tc_force) pick = ((g_tc_force == 2 || g_tc_force == 3) && a.N % 256 != 0) ? 0 : g_tc_force - 1;
 	switch (epi) {
 		case TC_EPI_PLAIN:
-			return pick == 2 ? tc_launch_inst<1, TC_EPI_PLAIN, 256, 2>(tmx, p, stream)
+			return pick == 3 ? tc_launch_inst<1, TC_EPI_PLAIN, 128, 2>(tmx, p, stream)
+				 : pick == 2 ? tc_launch_inst<1, TC_EPI_PLAIN, 256, 2>(tmx, p, stream)
 				 : pick == 1 ? tc_launch_inst<1, TC_EPI_PLAIN, 256, 1>(tmx, p, stream) : tc_launch_inst<1, TC_EPI_PLAIN, 128, 1>(tmx, p, stream);
 		case TC_EPI_ROPE:
-			return pick == 2 ? tc_launch_inst<1, TC_EPI_ROPE, 256, 2>(tmx, p, stream)
+			return pick == 3 ? tc_launch_inst<1, TC_EPI_ROPE, 128, 2>(tmx, p, stream)
+				 : pick == 2 ? tc_launch_inst<1, TC_EPI_ROPE, 256, 2>(tmx, p, stream)
 				 : pick == 1 ? tc_launch_inst<1, TC_EPI_ROPE, 256, 1>(tmx, p, stream) : tc_launch_inst<1, TC_EPI_ROPE, 128, 1>(tmx, p, stream);
 	}
 	return GPTQ_ERR_INVALID;

@@ -462,10 +462,10 @@ def test_prefill_act_order_and_gateup_and_rope(G, M):
 	assert bool((kc[0, :, M:] == 0).all())
 
 
-@pytest.mark.parametrize('cfg', [1, 2, 3])
+@pytest.mark.parametrize('cfg', [1, 2, 3, 4])
 @pytest.mark.parametrize('M', [100, 256, 300, 700])
 def test_prefill_every_tile_configuration(G, M, cfg):
-	"""128 x 128, 128 x 256 and 256-row tiles of the tensor-core kernel give the same results
+	"""128 x 128, 128 x 256, 256 x 256 and 256 x 128 tiles of the tensor-core kernel give the same results
 	(M = 100 / 300 / 700 leave the last 128-row half partly or wholly empty)."""
 	from gptq_triton_b200 import _lib
 	K, N, gs, H, D = 512, 768, 128, 2, 128
