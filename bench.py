@@ -99,14 +99,41 @@ def reference_arm(args):
 # clocks
 # ------------------------------------------------------------------------------------------
 class ClockSampler:
+	"""SM clock and clock-event reasons of one GPU, read (never set) every few milliseconds through
+	NVML while the timed region runs; falls back to an `nvidia-smi -lms` child process."""
 	Q = 'index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap'
+	BITS = {'sw_power_cap': 0x4, 'hw_slowdown': 0x8, 'sw_thermal_slowdown': 0x20, 'hw_thermal_slowdown': 0x40}
 
-	def __init__(self, gpu_index: int):
+	def __init__(self, gpu_index: int, uuid: str = None):
 		self.idx = gpu_index
+		self.uuid = uuid
 		self.proc = None
 		self.lines = []
+		self.nvml = None
+		self.samples = []          # (sm_mhz, reason bits)
+		self.stop_flag = False
+		self.max_mhz = None
 
 	def start(self):
+		try:
+			import pynvml
+			pynvml.nvmlInit()
+			h = None
+			if self.uuid:
+				try:
+					h = pynvml.nvmlDeviceGetHandleByUUID(self.uuid.encode() if hasattr(self.uuid, 'encode') else self.uuid)
+				except Exception:
+					h = None
+			if h is None:
+				h = pynvml.nvmlDeviceGetHandleByIndex(self.idx)
+			self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+			reasons_fn = getattr(pynvml, 'nvmlDeviceGetCurrentClocksEventReasons', None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+			self.nvml = (pynvml, h, reasons_fn)
+			self.thread = threading.Thread(target=self._poll, daemon=True)
+			self.thread.start()
+			return
+		except Exception:
+			self.nvml = None
 		try:
 			self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.idx), '--query-gpu=' + self.Q, '--format=csv,noheader,nounits', '-lms', '100'],
 										 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -115,11 +142,29 @@ class ClockSampler:
 		except Exception:
 			self.proc = None
 
+	def _poll(self):
+		pynvml, h, reasons_fn = self.nvml
+		while not self.stop_flag:
+			try:
+				self.samples.append((float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)), int(reasons_fn(h))))
+			except Exception:
+				pass
+			time.sleep(0.005)
+
 	def _read(self):
 		for line in self.proc.stdout:
 			self.lines.append(line.strip())
 
 	def stop(self):
+		if self.nvml is not None:
+			self.stop_flag = True
+			self.thread.join(timeout=1)
+			sm = sorted(s for s, _ in self.samples)
+			bits = 0
+			for _, r in self.samples:
+				bits |= r
+			reasons = sorted(n for n, b in self.BITS.items() if bits & b)
+			return {'sm_mhz': sm[len(sm) // 2] if sm else None, 'sm_max_mhz': self.max_mhz, 'samples': len(sm), 'reasons': reasons}
 		if self.proc is None:
 			return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
 		self.proc.terminate()
@@ -196,7 +241,11 @@ def gpu_arm(args):
 	# ---- device-timed: K graph replays -------------------------------------------------------
 	for _ in range(args.warmup):
 		engine.step()
-	sampler = ClockSampler(local_rank)
+	try:
+		gpu_uuid = 'GPU-' + str(torch.cuda.get_device_properties(local_rank).uuid)
+	except Exception:
+		gpu_uuid = None
+	sampler = ClockSampler(local_rank, gpu_uuid)
 	barrier()
 	if rank == 0:
 		sampler.start()
@@ -268,7 +317,7 @@ def gpu_arm(args):
 		peak, which = measured_peaks()
 		ach = alg / us / 1e3
 		roof = {'bound': 'hbm', 'kernel': 'skinny_kernel<gate/up, SiLU epilogue> M=%d K=%d N=%d' % (batch, K, N), 'achieved': ach, 'peak': peak, 'unit': 'GB/s',
-				'frac': ach / peak, 'peak_source': which, 'us_per_launch': us, 'algorithmic_bytes': alg, 'traffic': 46.96e6 if (world == 1 and not big) else None}
+				'frac': ach / peak, 'peak_source': which, 'us_per_launch': us, 'algorithmic_bytes': alg, 'traffic': 46.90e6 if (world == 1 and not big) else None}
 		status = _lib.kernel_status(dev)
 
 	# ---- CPU baseline (rank 0, N=1 only) -----------------------------------------------------------
