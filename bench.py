@@ -329,7 +329,10 @@ def gpu_arm(args):
 			   'sample': 'one 4096x4096 g128 projection at M=1 through the CPU oracle (1/%.0f of the quantised weights of a decode step), median of 5' % scale}
 
 	if rank == 0:
-		launches_per_step = 7 * cfg.num_hidden_layers + 1      # per rank      # 4 quantised matmuls, attention, 2 RMSNorm per layer + final norm
+		# own kernels per rank and step: 4 quantised matmuls + attention per layer; RMSNorm is folded into them on one GPU
+		# (first layer's input norm and the final norm stay kernels), two RMSNorm kernels per layer under tensor parallelism
+		folded = world == 1 and engine.fuse_norm and batch <= 16
+		launches_per_step = (5 * cfg.num_hidden_layers + 2) if folded else (7 * cfg.num_hidden_layers + 1)
 		line = {
 			'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
 			'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'strong' if world > 1 else 'weak', 'vs_baseline': None, 'dtype': 'f16',
