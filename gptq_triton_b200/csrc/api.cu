@@ -465,8 +465,8 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 		return GPTQ_ERR_ALIGN;
 	if (batch == 0) return GPTQ_OK;
 	if ((size_t)batch * heads * 4 > (size_t)AT_TICKET_BYTES - 8) return GPTQ_ERR_UNSUPPORTED;
-	// about 2.6 CTAs of 128 threads per SM measured best (12 splits for 32 heads at 2k context)
-	int splits = (13 * sm_count() / 5 + batch * heads - 1) / (batch * heads);
+	// two CTAs (96 KB of staged cache rows each) fit an SM: one wave of at most 2 * SMs CTAs
+	int splits = std::max(1, 2 * sm_count() / (batch * heads));
 	if (g_attn_splits > 0) splits = g_attn_splits;
 	splits = std::max(1, std::min(splits, std::min(AT_MAX_SPLITS, (len_hint + 63) / 64)));
 	if (splits > 1 && (!workspace || workspace_bytes < gptq_attn_workspace_bytes(batch, heads))) return GPTQ_ERR_WORKSPACE;
@@ -478,7 +478,17 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 	p.scale = scale; p.heads = heads; p.splits = splits;
 	p.ws_ticket = reinterpret_cast<int *>(workspace);
 	p.ws_partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + AT_TICKET_BYTES);
-	return launch_ex(attn_decode_kernel, dim3(splits, heads, batch), dim3(AT_THREADS, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), p);
+	{
+		static bool ready[64] = {false};
+		int dev = 0;
+		if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GPTQ_ERR_CUDA;
+		if (!ready[dev]) {
+			cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
+			if (e != cudaSuccess) return cuda_status(e);
+			ready[dev] = true;
+		}
+	}
+	return launch_ex(attn_decode_kernel, dim3(splits, heads, batch), dim3(AT_THREADS, 1, 1), AT_SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream), p);
 }
 
 int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_t ldy, int M, int K, float eps, gptq_stream_t stream) {

@@ -1,12 +1,16 @@
 // Single-query (decode) attention over a static fp16 KV cache: softmax(q·K^T / sqrt(d)) · V
 // for one new token per sequence.  HBM-bound: K and V of every cached position are read once.
 //
-// Grid (splits, heads, batch).  A CTA of 4 warps takes a contiguous range of cache positions;
-// 8 lanes share one key (16 head dims = two 16-byte loads each, a key row is 256 contiguous
-// bytes), so a warp handles 4 keys per step and a CTA 16.  Each 8-lane group keeps an online
-// softmax (running max, running sum, 16 output dims in fp32).  Groups, warps and splits are
-// merged with the usual log-sum-exp rescaling; the last CTA of a (batch, head) to arrive
-// (ticket in the workspace) merges the split partials in fixed order and writes fp16.
+// Grid (splits, heads, batch).  A CTA of 4 warps takes a contiguous range of cache positions and
+// pulls it into shared memory with bulk asynchronous copies (64 keys of K and of V per stage,
+// three stages, mbarrier completion).  The copies are issued BEFORE the kernel waits for its
+// predecessor in the stream: old cache rows do not depend on it, so the cache streams in while
+// the QKV kernel of the same step is still finishing.  Only the newest AT_FRESH positions are
+// read from global memory after the wait (they may have been written by that kernel).
+// 8 lanes share one key (16 head dims each); each 8-lane group keeps an online softmax (running
+// max, running sum, 16 output dims in fp32).  Groups, warps and splits are merged with the usual
+// log-sum-exp rescaling; the last CTA of a (batch, head) to arrive (ticket in the workspace)
+// merges the split partials in fixed order and writes fp16.
 #pragma once
 
 #include "common.cuh"
@@ -17,6 +21,12 @@ constexpr int AT_D = 128;              // head dim
 constexpr int AT_THREADS = 128;
 constexpr int AT_MAX_SPLITS = 32;
 constexpr int AT_TICKET_BYTES = 16384;
+constexpr int AT_STATUS_SLOT = AT_TICKET_BYTES / 4 - 1;      // same word as the matmul kernels' status
+constexpr int AT_CHUNK = 64;           // keys per stage
+constexpr int AT_STAGES = 3;
+constexpr int AT_STAGE_BYTES = 2 * AT_CHUNK * AT_D * 2;      // K rows then V rows: 32 KB
+constexpr int AT_SMEM_BYTES = AT_STAGES * AT_STAGE_BYTES + 64;
+constexpr int AT_FRESH = 16;           // newest positions that are never read ahead of the dependency wait
 
 struct AttnParams {
 	const __half *q;          // [b, heads, 128] (row stride q_stride_b)
@@ -32,25 +42,52 @@ struct AttnParams {
 	int *ws_ticket;           // [b*heads]
 };
 
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+	asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+				 "r"(bar)
+				 : "memory");
+}
+
 __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParams p) {
+	extern __shared__ __align__(128) unsigned char at_smem[];
 	const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int grp = lane >> 3, sub = lane & 7;           // 4 key groups per warp, 8 lanes per key
+	const int g16 = warp * 4 + grp;
 	pdl_trigger();
-	pdl_wait();                                          // q, the cache row of this step and pos come from earlier kernels
 	// positions beyond the cache are never read: the length is clamped to the rows a head owns
 	const int len = max(1, min(p.pos[b] + 1, (int)(p.kv_stride_h / AT_D)));
 	const int per = (len + p.splits - 1) / p.splits;
-	const int k_lo = split * per, k_hi = min(k_lo + per, len);
+	const int k_lo = min(split * per, len), k_hi = min(k_lo + per, len);
+	const int nchunks = (k_hi - k_lo + AT_CHUNK - 1) / AT_CHUNK;
+	const __half *kbase = p.kc + (size_t)b * p.kv_stride_b + (size_t)head * p.kv_stride_h;
+	const __half *vbase = p.vc + (size_t)b * p.kv_stride_b + (size_t)head * p.kv_stride_h;
 
 	__shared__ float s_m[16], s_l[16], s_acc[16][AT_D];
 	__shared__ int s_last;
+	const uint32_t bar0 = smem_u32(at_smem + AT_STAGES * AT_STAGE_BYTES);
+	if (tid == 0) {
+		for (int s = 0; s < AT_STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+		fence_mbar_init();
+	}
+	__syncthreads();
+	auto issue = [&](int c) {                // one thread: K and V rows of chunk c into stage c % AT_STAGES
+		const int stage = c % AT_STAGES, key0 = k_lo + c * AT_CHUNK;
+		const uint32_t bytes = (uint32_t)min(AT_CHUNK, k_hi - key0) * AT_D * 2u;
+		const uint32_t dst = smem_u32(at_smem + stage * AT_STAGE_BYTES), bar = bar0 + 8 * stage;
+		mbar_arrive_expect_tx(bar, 2u * bytes);
+		bulk_load_1d(dst, kbase + (size_t)key0 * AT_D, bytes, bar);
+		bulk_load_1d(dst + AT_STAGE_BYTES / 2, vbase + (size_t)key0 * AT_D, bytes, bar);
+	};
+	if (tid == 0)
+		for (int c = 0; c < min(nchunks, AT_STAGES); ++c) issue(c);
+	pdl_wait();                                          // q and the newest cache rows come from earlier kernels
 
-	// this lane's 16 query dims, pre-scaled
+	// this lane's 16 query dims (sub*8 .. +7 and 64 + sub*8 .. +7), pre-scaled
 	float qf[16];
 	{
-		const __half *qp = p.q + (size_t)b * p.q_stride_b + head * AT_D + sub * 16;
-		const uint4 a = *reinterpret_cast<const uint4 *>(qp), c = *reinterpret_cast<const uint4 *>(qp + 8);
+		const __half *qp = p.q + (size_t)b * p.q_stride_b + head * AT_D + sub * 8;
+		const uint4 a = *reinterpret_cast<const uint4 *>(qp), c = *reinterpret_cast<const uint4 *>(qp + 64);
 		const __half2 *ha = reinterpret_cast<const __half2 *>(&a), *hc = reinterpret_cast<const __half2 *>(&c);
 #pragma unroll
 		for (int i = 0; i < 4; ++i) {
@@ -61,33 +98,41 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 			qf[8 + 2 * i + 1] = g.y * p.scale;
 		}
 	}
-	const __half *kbase = p.kc + (size_t)b * p.kv_stride_b + (size_t)head * p.kv_stride_h + sub * 16;
-	const __half *vbase = p.vc + (size_t)b * p.kv_stride_b + (size_t)head * p.kv_stride_h + sub * 16;
+	const int fresh_lo = len - AT_FRESH;
 
 	float m = -INFINITY, l = 0.f, acc[16];
 #pragma unroll
 	for (int i = 0; i < 16; ++i) acc[i] = 0.f;
 
-	constexpr int UNROLL = 4;          // keys in flight per 8-lane group
+	constexpr int KPG = AT_CHUNK / 16;       // keys per 8-lane group and chunk
+	bool failed = false;
 #pragma unroll 1
-	for (int base = k_lo + warp * 4; base < k_hi; base += 16 * UNROLL) {      // trip count uniform within the warp
-		const int k0 = base + grp;
-		uint4 kr[UNROLL][2], vr[UNROLL][2];
+	for (int c = 0; c < nchunks; ++c) {
+		const int stage = c % AT_STAGES, key0 = k_lo + c * AT_CHUNK;
+		const int n = min(AT_CHUNK, k_hi - key0);
+		const bool got = mbar_wait_bounded(bar0 + 8 * stage, (c / AT_STAGES) & 1);
+		if (!__syncthreads_and(got)) {       // the same verdict for every thread
+			failed = true;
+			break;
+		}
+		const unsigned char *sK = at_smem + stage * AT_STAGE_BYTES, *sV = sK + AT_STAGE_BYTES / 2;
+		uint4 kr[KPG][2], vr[KPG][2];
 #pragma unroll
-		for (int u = 0; u < UNROLL; ++u) {
-			const int key = k0 + u * 16;
-			if (key < k_hi) {
-				const __half *kp = kbase + (size_t)key * AT_D, *vp = vbase + (size_t)key * AT_D;
-				kr[u][0] = ld_nc_v4(kp);
-				kr[u][1] = ld_nc_v4(kp + 8);
-				vr[u][0] = ld_nc_v4(vp);
-				vr[u][1] = ld_nc_v4(vp + 8);
+		for (int u = 0; u < KPG; ++u) {
+			const int kk = g16 + 16 * u, key = key0 + kk;
+			if (kk < n) {
+				const bool fresh = key >= fresh_lo;
+				const __half *kp = fresh ? kbase + (size_t)key * AT_D : reinterpret_cast<const __half *>(sK) + kk * AT_D;
+				const __half *vp = fresh ? vbase + (size_t)key * AT_D : reinterpret_cast<const __half *>(sV) + kk * AT_D;
+				kr[u][0] = *reinterpret_cast<const uint4 *>(kp + sub * 8);
+				kr[u][1] = *reinterpret_cast<const uint4 *>(kp + 64 + sub * 8);
+				vr[u][0] = *reinterpret_cast<const uint4 *>(vp + sub * 8);
+				vr[u][1] = *reinterpret_cast<const uint4 *>(vp + 64 + sub * 8);
 			}
 		}
 #pragma unroll
-		for (int u = 0; u < UNROLL; ++u) {
-			const int key = k0 + u * 16;
-			const bool valid = key < k_hi;            // uniform within an 8-lane group
+		for (int u = 0; u < KPG; ++u) {
+			const bool valid = g16 + 16 * u < n;          // uniform within an 8-lane group
 			float s = 0.f;
 			if (valid) {
 				const __half2 *h0 = reinterpret_cast<const __half2 *>(&kr[u][0]), *h1 = reinterpret_cast<const __half2 *>(&kr[u][1]);
@@ -120,16 +165,23 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 				m = mn;
 			}
 		}
+		if (c + AT_STAGES < nchunks) {       // the stage is refilled once every thread has read it
+			__syncthreads();
+			if (tid == 0) issue(c + AT_STAGES);
+		}
 	}
+	if (failed && tid == 0 && p.ws_ticket) atomicExch(p.ws_ticket + AT_STATUS_SLOT, 1);      // a bulk copy never completed
 
 	// ---- merge the 16 groups of the CTA (fixed order) -------------------------------------------
-	const int g16 = warp * 4 + grp;
 	if (sub == 0) {
 		s_m[g16] = m;
 		s_l[g16] = l;
 	}
 #pragma unroll
-	for (int i = 0; i < 16; ++i) s_acc[g16][sub * 16 + i] = acc[i];
+	for (int i = 0; i < 8; ++i) {
+		s_acc[g16][sub * 8 + i] = acc[i];
+		s_acc[g16][64 + sub * 8 + i] = acc[8 + i];
+	}
 	__syncthreads();
 	float M = -INFINITY;
 #pragma unroll
