@@ -337,6 +337,17 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			}
 		}
 	}
+	// Bias and residual of the first epilogue pass (element tid of the M x 128 tile) are fetched now:
+	// only the last CTA of a tile uses them, but it then finds them in registers instead of paying
+	// a global round trip at the very end of the kernel.
+	float pre_bias = 0.f, pre_res = 0.f;
+	if (EPI == EPI_PLAIN && tid < p.M * SK_BN) {
+		const int n = n0 + (tid & 127);
+		if (n < p.N) {
+			if (p.bias) pre_bias = __half2float(__ldg(p.bias + n));
+			if (p.residual) pre_res = __half2float(p.residual[(size_t)(tid >> 7) * p.ldr + n]);
+		}
+	}
 	__syncthreads();
 
 	// ---- group sums of the staged x: C = 1024*(SXe + SXo'), S = SXe + 16*SXo' per (group, row) ----
@@ -750,6 +761,9 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 				float v = fin[(size_t)row * SK_BN + col];
 				if (EPI == EPI_SILU) {
 					v = silu_f32(v) * fin[((size_t)ROWS + row) * SK_BN + col];
+				} else if (e == tid) {
+					if (p.bias) v += pre_bias;
+					if (p.residual) v += pre_res;
 				} else {
 					if (p.bias) v += __half2float(p.bias[n]);
 					if (p.residual) v += __half2float(p.residual[(size_t)row * p.ldr + n]);
