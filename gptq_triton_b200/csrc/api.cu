@@ -20,6 +20,15 @@ static int g_force_kw = 2;
 static int g_attn_splits = 0;     // tuning hook: 0 = heuristic
 static int g_use_tc = 1;          // tensor-core kernel for M > 16
 static int g_pdl = 1;             // programmatic dependent launch for the decode-step kernels (+3 % on the decode step)
+#ifdef GPTQ_TRACE
+static TraceSlot *g_trace = nullptr;      // [4096] slots in device memory, handed in by the debug script
+static int g_trace_n = 0;
+static TraceSlot *trace_slot(int kind) {
+	if (!g_trace || g_trace_n >= 4096) return nullptr;
+	(void)kind;
+	return g_trace + g_trace_n++;
+}
+#endif
 #ifdef GPTQ_SK_TIMING
 static long long *g_dbg = nullptr;
 #endif
@@ -258,6 +267,9 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	if (smem > (size_t)SK_SMEM_LIMIT - 1024) return GPTQ_ERR_UNSUPPORTED;
 	const size_t need = skinny_ws_bytes(p.M, p.N, NSTREAM);
 	if (workspace == nullptr || ws_bytes < need) return GPTQ_ERR_WORKSPACE;
+#ifdef GPTQ_TRACE
+	p.trace = trace_slot(EPI);
+#endif
 #ifdef GPTQ_SK_TIMING
 	p.dbg = g_dbg;
 	p.raw0 = qw0;
@@ -385,6 +397,10 @@ int gptq_debug_plan(int M, int K, int N, int groupsize, int nstream, int *out) {
 	out[6] = p.chunks_per_split; out[7] = 0;
 	return GPTQ_OK;
 }
+#ifdef GPTQ_TRACE
+// buf: 4096 slots of 4 x u64, begin preset to ~0 and end to 0 by the caller; returns the slots handed out so far
+int gptq_debug_trace(void *buf) { g_trace = reinterpret_cast<TraceSlot *>(buf); const int n = g_trace_n; g_trace_n = 0; return n; }
+#endif
 #ifdef GPTQ_SK_TIMING
 void gptq_debug_set_timing(long long *buf) { g_dbg = buf; }
 #endif
@@ -478,6 +494,9 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 	p.scale = scale; p.heads = heads; p.splits = splits;
 	p.ws_ticket = reinterpret_cast<int *>(workspace);
 	p.ws_partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + AT_TICKET_BYTES);
+#ifdef GPTQ_TRACE
+	p.trace = trace_slot(3);
+#endif
 	{
 		static bool ready[64] = {false};
 		int dev = 0;

@@ -40,6 +40,9 @@ struct AttnParams {
 	int heads, splits;
 	float *ws_partial;        // [b*heads][splits][130]
 	int *ws_ticket;           // [b*heads]
+#ifdef GPTQ_TRACE
+	TraceSlot *trace;
+#endif
 };
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -54,6 +57,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int grp = lane >> 3, sub = lane & 7;           // 4 key groups per warp, 8 lanes per key
 	const int g16 = warp * 4 + grp;
+	GPTQ_TRACE_BEGIN(p.trace);
 	pdl_trigger();
 	// positions beyond the cache are never read: the length is clamped to the rows a head owns
 	const int len = max(1, min(p.pos[b] + 1, (int)(p.kv_stride_h / AT_D)));
@@ -197,6 +201,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	const int bh = b * p.heads + head;
 	if (p.splits == 1) {
 		p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(o / L);
+		GPTQ_TRACE_END(p.trace);
 		return;
 	}
 	float *wp = p.ws_partial + ((size_t)bh * p.splits + split) * 130;
@@ -214,7 +219,10 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		s_last = last;
 	}
 	__syncthreads();
-	if (!s_last) return;
+	if (!s_last) {
+		GPTQ_TRACE_END(p.trace);
+		return;
+	}
 	__threadfence();
 	const float *wb = p.ws_partial + (size_t)bh * p.splits * 130;
 	float Mg = -INFINITY;
@@ -229,6 +237,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		og = fmaf(__ldcg(wb + s * 130 + 2 + tid), w, og);
 	}
 	p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(og / Lg);
+	GPTQ_TRACE_END(p.trace);
 }
 
 // ---- RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, fp32 inside, one fp16 rounding ----------------

@@ -84,6 +84,9 @@ struct SkinnyParams {
 	__half *q_out, *k_out, *v_out;
 	long long q_stride_m, kv_sb, kv_st, kv_sh, kv_sp;
 	int tokens_per_batch, hidden, max_pos;
+#ifdef GPTQ_TRACE
+	TraceSlot *trace;
+#endif
 #ifdef GPTQ_SK_TIMING
 	long long *dbg;        // [cta][8] phase timestamps (debug builds only)
 	const int32_t *raw0, *raw1;
@@ -121,6 +124,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	const int wn = warp & 3, kw = warp >> 2, gid = lane >> 2, tig = lane & 3;
 	const int tile = blockIdx.x, split = blockIdx.y;
 	SK_STAMP(0);
+	GPTQ_TRACE_BEGIN(p.trace);
 	const int n0 = tile * SK_BN, n0w = n0 + wn * 32;
 	const bool warp_active = n0w < p.N;
 
@@ -701,7 +705,10 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		}
 		__syncthreads();
 		SK_STAMP(4);
-		if (!s_last) return;
+		if (!s_last) {
+			GPTQ_TRACE_END(p.trace);
+			return;
+		}
 		__threadfence();
 		const float *wt = p.ws_partial + (size_t)tile * p.splitk * nelem;
 		if (M8) {
@@ -814,6 +821,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		}
 	}
 	SK_STAMP(6);
+	GPTQ_TRACE_END(p.trace);
 }
 
 // ---- general kernel: any M, any g_idx, N % 8 == 0, K % 8 == 0 ---------------------------
