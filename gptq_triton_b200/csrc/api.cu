@@ -130,6 +130,10 @@ static bool skinny_shape_ok(int K, int N, int groupsize, const int32_t *g_idx) {
 		   (N / SK_BN + 2) * 4 <= SK_TICKET_BYTES - 4;
 }
 
+// scratch for x[:, perm] of an act-order decode call, placed behind the partial sums
+static size_t gather_offset(size_t base) { return (base + 255) & ~(size_t)255; }
+static size_t gather_bytes(int M, int K) { return (size_t)std::min(M, 16) * (size_t)K * sizeof(__half); }
+
 static size_t skinny_ws_bytes(int M, int N, int nstream) {
 	const size_t tiles = (size_t)(N + SK_BN - 1) / SK_BN;
 	return SK_TICKET_BYTES + tiles * SK_MAX_SPLITK * nstream * (size_t)std::min(M, 16) * SK_BN * sizeof(float);
@@ -248,10 +252,10 @@ static int ensure_smem_attr(Kern k, bool (&ready)[64]) {
 	return GPTQ_OK;
 }
 
-template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI, int PERM_T>
+template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI>
 static int launch_skinny_inst(const CUtensorMap &tm0, const CUtensorMap &tm1, const SkinnyParams &p, dim3 grid, size_t smem,
 							  cudaStream_t stream) {
-	auto k = skinny_kernel<KW, NSTREAM, M8, SPG_T, EPI, PERM_T>;
+	auto k = skinny_kernel<KW, NSTREAM, M8, SPG_T, EPI>;
 	static bool ready[64] = {false};
 	if (int rc = ensure_smem_attr(k, ready)) return rc;
 	return launch_ex(k, grid, dim3(KW * 128, 1, 1), smem, stream, tm0, tm1, p);
@@ -259,7 +263,7 @@ static int launch_skinny_inst(const CUtensorMap &tm0, const CUtensorMap &tm1, co
 
 template <int NSTREAM, int EPI>
 static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1, void *workspace, size_t ws_bytes,
-						 cudaStream_t stream) {
+						 cudaStream_t stream, size_t gather_off = (size_t)-1) {
 	dim3 grid;
 	size_t smem;
 	int kw;
@@ -267,6 +271,17 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	if (smem > (size_t)SK_SMEM_LIMIT - 1024) return GPTQ_ERR_UNSUPPORTED;
 	const size_t need = skinny_ws_bytes(p.M, p.N, NSTREAM);
 	if (workspace == nullptr || ws_bytes < need) return GPTQ_ERR_WORKSPACE;
+	if (p.perm) {
+		// act-order: x[:, perm] once, into the workspace behind the partial sums (or at the offset the caller planned)
+		const size_t off = (gather_off != (size_t)-1) ? gather_off : gather_offset(need);
+		if (ws_bytes < off + gather_bytes(p.M, p.K)) return GPTQ_ERR_WORKSPACE;
+		__half *xp = reinterpret_cast<__half *>(reinterpret_cast<unsigned char *>(workspace) + off);
+		const dim3 gg((unsigned)((p.K / 8 + 255) / 256), (unsigned)p.M, 1);
+		if (int rc = launch_ex(gather_x_kernel, gg, dim3(256, 1, 1), 0, stream, p.x, p.ldx, p.perm, xp, p.K)) return rc;
+		p.x = xp;
+		p.ldx = p.K;
+		p.perm = nullptr;
+	}
 #ifdef GPTQ_TRACE
 	p.trace = trace_slot(EPI);
 #endif
@@ -286,23 +301,19 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	}
 	const bool m8 = p.M <= 8;
 	if (p.spg == 1) {
-		return m8 ? launch_skinny_inst<2, NSTREAM, true, 1, EPI, 2>(tm0, tm1, p, grid, smem, stream)
-				  : launch_skinny_inst<2, NSTREAM, false, 1, EPI, 2>(tm0, tm1, p, grid, smem, stream);
+		return m8 ? launch_skinny_inst<2, NSTREAM, true, 1, EPI>(tm0, tm1, p, grid, smem, stream)
+				  : launch_skinny_inst<2, NSTREAM, false, 1, EPI>(tm0, tm1, p, grid, smem, stream);
 	}
 	if (p.spg == 2) {
-		return m8 ? launch_skinny_inst<2, NSTREAM, true, 2, EPI, 2>(tm0, tm1, p, grid, smem, stream)
-				  : launch_skinny_inst<2, NSTREAM, false, 2, EPI, 2>(tm0, tm1, p, grid, smem, stream);
+		return m8 ? launch_skinny_inst<2, NSTREAM, true, 2, EPI>(tm0, tm1, p, grid, smem, stream)
+				  : launch_skinny_inst<2, NSTREAM, false, 2, EPI>(tm0, tm1, p, grid, smem, stream);
 	}
 	if (kw == 2) {
-		// the common kernels are compiled once per x addressing mode (less code per kernel)
-		if (p.perm == nullptr)
-			return m8 ? launch_skinny_inst<2, NSTREAM, true, 0, EPI, 0>(tm0, tm1, p, grid, smem, stream)
-					  : launch_skinny_inst<2, NSTREAM, false, 0, EPI, 0>(tm0, tm1, p, grid, smem, stream);
-		return m8 ? launch_skinny_inst<2, NSTREAM, true, 0, EPI, 1>(tm0, tm1, p, grid, smem, stream)
-				  : launch_skinny_inst<2, NSTREAM, false, 0, EPI, 1>(tm0, tm1, p, grid, smem, stream);
+		return m8 ? launch_skinny_inst<2, NSTREAM, true, 0, EPI>(tm0, tm1, p, grid, smem, stream)
+				  : launch_skinny_inst<2, NSTREAM, false, 0, EPI>(tm0, tm1, p, grid, smem, stream);
 	}
-	return m8 ? launch_skinny_inst<4, NSTREAM, true, 0, EPI, 2>(tm0, tm1, p, grid, smem, stream)
-			  : launch_skinny_inst<4, NSTREAM, false, 0, EPI, 2>(tm0, tm1, p, grid, smem, stream);
+	return m8 ? launch_skinny_inst<4, NSTREAM, true, 0, EPI>(tm0, tm1, p, grid, smem, stream)
+			  : launch_skinny_inst<4, NSTREAM, false, 0, EPI>(tm0, tm1, p, grid, smem, stream);
 }
 
 // Folded RMSNorm (consumer side): decode kernel only, x read in order, at most 64 producer tiles.
@@ -406,9 +417,8 @@ void gptq_debug_set_timing(long long *buf) { g_dbg = buf; }
 #endif
 
 size_t gptq_workspace_bytes(int M, int K, int N) {
-	(void)K;
 	if (M <= 0 || N <= 0) return SK_TICKET_BYTES;
-	return std::max(skinny_ws_bytes(M, N, 2), tc_ws_bytes(M, N));
+	return std::max(gather_offset(skinny_ws_bytes(M, N, 2)) + gather_bytes(M, std::max(K, 0)), tc_ws_bytes(M, N));
 }
 
 static int qmatmul_impl(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
@@ -529,7 +539,7 @@ size_t gptq_noalloc_scratch_bytes(int M, int K, int N, int groupsize) {
 	size_t smem;
 	int kw;
 	plan_skinny(p, 1, kw, grid, smem);
-	return noalloc_need(p);
+	return gather_offset(noalloc_need(p)) + gather_bytes(M, K);      // with room for the act-order gather of x
 }
 
 int gptq_qmatmul_noalloc(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *perm,
@@ -557,8 +567,15 @@ int gptq_qmatmul_noalloc(const void *x, const int32_t *qweight, const int32_t *q
 	p.bias = (const __half *)bias; p.residual = (const __half *)residual; p.ldr = ldr;
 	p.y = (__half *)y; p.ldy = ldy;
 	// launch_skinny only checks that the buffer is at least as large as the generic upper bound;
-	// the array was checked against the exact need above, so pass that bound as the size
-	return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, scratch, skinny_ws_bytes(M, N, 1), st);
+	// the array was checked against the exact need above (partial sums of the planned split, then
+	// the gathered x), so pass sizes that satisfy those checks and the planned offset of the gather
+	dim3 grid;
+	size_t smem;
+	int kw;
+	SkinnyParams plan = p;
+	plan_skinny(plan, 1, kw, grid, smem);
+	const size_t off = gather_offset(noalloc_need(plan));
+	return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, scratch, std::max(skinny_ws_bytes(M, N, 1), off + gather_bytes(M, K)), st, off);
 }
 
 static int gateup_impl(const void *x, const int32_t *gate_qweight, const int32_t *gate_qzeros, const void *gate_scales,

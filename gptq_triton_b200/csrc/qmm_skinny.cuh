@@ -50,7 +50,7 @@ struct SkinnyParams {
 	long long ldx;
 	const int32_t *qz0, *qz1;
 	const __half *sc0, *sc1;
-	const int32_t *perm;
+	const int32_t *perm;   // host side only: request for the gather pass; the kernel reads x in order
 	int M, K, N, groupsize;
 	int spg;               // 32-row steps per group (1, 2 or a multiple of 4)
 	int total_chunks;      // K / 128
@@ -109,9 +109,9 @@ struct SkinnyParams {
 #endif
 
 // SPG_T: steps per group known at compile time (1 or 2), or 0 when a group spans whole chunks.
-// PERM_T: 0 = x is read in order, 1 = x is gathered through p.perm (act-order), 2 = decided at
-// run time (the rarely used variants; keeps the common kernels free of the other path's code).
-template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI, int PERM_T>
+// x is always read in order: for act-order weights the host gathers x[:, perm] once per call with
+// gather_x_kernel (every CTA of every tile would otherwise repeat the gather with 2-byte loads).
+template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI>
 __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	skinny_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, const SkinnyParams p) {
 	extern __shared__ __align__(1024) unsigned char smem[];
@@ -236,32 +236,17 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			}
 		}
 	};
-	// x slice: a pass covers XB batch rows of one 16-byte unit per thread (same k for every row,
-	// so the act-order permutation is read once per pass)
-	constexpr bool RMS_OK = (EPI != EPI_PLAIN) && (PERM_T == 0);
+	// x slice: a pass covers XB batch rows of one 16-byte unit per thread
+	constexpr bool RMS_OK = (EPI != EPI_PLAIN);
 	const bool rms = RMS_OK && p.rms_w != nullptr;
 	__shared__ float s_inv[16];
 	auto x_load = [&](int row0, int unit, uint4(&v)[XB], uint4 &wq) {
 		if (unit >= units) return;
 		const int k = (c_lo * 16 + unit) * 8;
 		if (rms) wq = __ldg(reinterpret_cast<const uint4 *>(p.rms_w + k));
-		if (PERM_T == 0 || (PERM_T == 2 && p.perm == nullptr)) {
 #pragma unroll
-			for (int j = 0; j < XB; ++j)
-				if (row0 + j < p.M) v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)(row0 + j) * p.ldx + k));
-		} else {
-			const int4 pa = __ldg(reinterpret_cast<const int4 *>(p.perm + k));
-			const int4 pb = __ldg(reinterpret_cast<const int4 *>(p.perm + k + 4));
-#pragma unroll
-			for (int j = 0; j < XB; ++j) {
-				if (row0 + j < p.M) {
-					const unsigned short *xr = reinterpret_cast<const unsigned short *>(p.x) + (size_t)(row0 + j) * p.ldx;
-					const uint32_t h0 = __ldg(xr + pa.x), h1 = __ldg(xr + pa.y), h2 = __ldg(xr + pa.z), h3 = __ldg(xr + pa.w);
-					const uint32_t h4 = __ldg(xr + pb.x), h5 = __ldg(xr + pb.y), h6 = __ldg(xr + pb.z), h7 = __ldg(xr + pb.w);
-					v[j] = make_uint4(h0 | (h1 << 16), h2 | (h3 << 16), h4 | (h5 << 16), h6 | (h7 << 16));
-				}
-			}
-		}
+		for (int j = 0; j < XB; ++j)
+			if (row0 + j < p.M) v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)(row0 + j) * p.ldx + k));
 	};
 	auto x_store = [&](int row0, int unit, const uint4(&v)[XB], const uint4 &wq) {
 		// [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7, the (1,5) and (3,7) pairs divided by 16
@@ -822,6 +807,21 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	}
 	SK_STAMP(6);
 	GPTQ_TRACE_END(p.trace);
+}
+
+// ---- act-order gather: out[m][k] = x[m][perm[k]], 8 elements per thread -------------------
+__global__ void __launch_bounds__(256) gather_x_kernel(const __half *__restrict__ x, long long ldx, const int32_t *__restrict__ perm,
+														__half *__restrict__ out, int K) {
+	const int unit = blockIdx.x * 256 + threadIdx.x, row = blockIdx.y;
+	pdl_trigger();
+	if (unit * 8 >= K) return;
+	const int4 pa = __ldg(reinterpret_cast<const int4 *>(perm + unit * 8));       // the permutation does not depend on earlier kernels
+	const int4 pb = __ldg(reinterpret_cast<const int4 *>(perm + unit * 8 + 4));
+	pdl_wait();
+	const unsigned short *xr = reinterpret_cast<const unsigned short *>(x) + (size_t)row * ldx;
+	const uint32_t h0 = xr[pa.x], h1 = xr[pa.y], h2 = xr[pa.z], h3 = xr[pa.w];
+	const uint32_t h4 = xr[pb.x], h5 = xr[pb.y], h6 = xr[pb.z], h7 = xr[pb.w];
+	*reinterpret_cast<uint4 *>(out + (size_t)row * K + unit * 8) = make_uint4(h0 | (h1 << 16), h2 | (h3 << 16), h4 | (h5 << 16), h6 | (h7 << 16));
 }
 
 // ---- general kernel: any M, any g_idx, N % 8 == 0, K % 8 == 0 ---------------------------

@@ -49,7 +49,8 @@ int gptq_last_cuda_error(void);
 
 /*
  * Bytes of scratch that gptq_qmatmul / gptq_gateup_silu / gptq_qkv_rope need for a
- * problem of this size (split-K partial sums + per-tile arrival counters).  The
+ * problem of this size (split-K partial sums, per-tile arrival counters, and for act-order
+ * decode calls the gathered copy of x).  The
  * caller allocates it once per stream, ZEROES it once, and hands it to every call;
  * the kernels leave the counter area zeroed again.  Two calls that overlap on the
  * GPU must not share one workspace.  Replaces the `torch.empty` + 1-D launch grid
