@@ -239,6 +239,37 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 	grid = dim3(tiles, p.splitk, 1);
 }
 
+// Narrow geometry (one 32-column strip and the whole of K per CTA, no split-K): worth it when
+// N / 32 CTAs fill most of the chip in one wave and the x rows of the whole K fit in shared memory.
+static int g_allow_narrow = 0;      // opt-in (gptq_debug_allow_narrow): measured slower than the tiled split-K form
+static bool plan_narrow(SkinnyParams &p, dim3 &grid, size_t &smem) {
+	if (!g_allow_narrow || g_force_splitk > 0) return false;
+	if (p.groupsize % 128 != 0 || p.N % 32 != 0) return false;
+	const int strips32 = p.N / 32, sms = sm_count();
+	if (strips32 * 10 < sms * 6 || strips32 > 2 * sms) return false;
+	p.spg = p.groupsize / 32;
+	p.total_chunks = p.K / 128;
+	const int xs_stride = p.K * 2 + 16;
+	const int xs_bytes = (p.M * xs_stride + 127) / 128 * 128;
+	const int strip_groups = p.K / p.groupsize + 1;
+	const size_t strips = (size_t)strip_groups * 32 * 2 * 2 + (size_t)strip_groups * 16 * 8;
+	const size_t cap = strips32 > sms ? (size_t)113 * 1024 : (size_t)SK_SMEM_LIMIT - 2048;      // two CTAs per SM when there are more strips than SMs
+	int nstage = 4;
+	auto total = [&](int st) { return (size_t)8 * st * SK_CHUNK_BYTES + SK_BAR_BYTES + (size_t)xs_bytes + strips; };
+	while (nstage > 2 && total(nstage) > cap) --nstage;
+	if (total(nstage) > cap) return false;
+	p.xs_stride = xs_stride;
+	p.xs_bytes = xs_bytes;
+	p.strip_groups = strip_groups;
+	p.chunks_per_split = p.total_chunks;
+	p.splitk = 1;
+	p.pdl = g_pdl;
+	p.nstage = nstage;
+	smem = total(nstage);
+	grid = dim3(strips32, 1, 1);
+	return true;
+}
+
 // Opt the kernel in to the full dynamic shared memory once per device.
 template <typename Kern>
 static int ensure_smem_attr(Kern k, bool (&ready)[64]) {
@@ -258,7 +289,18 @@ static int launch_skinny_inst(const CUtensorMap &tm0, const CUtensorMap &tm1, co
 	auto k = skinny_kernel<KW, NSTREAM, M8, SPG_T, EPI>;
 	static bool ready[64] = {false};
 	if (int rc = ensure_smem_attr(k, ready)) return rc;
-	return launch_ex(k, grid, dim3(KW * 128, 1, 1), smem, stream, tm0, tm1, p);
+	return launch_ex(k, grid, dim3(KW == 8 ? 256 : KW * 128, 1, 1), smem, stream, tm0, tm1, p);
+}
+
+// the narrow kernel exists for the plain epilogue with one weight stream only
+template <int NSTREAM, int EPI>
+static int launch_narrow(const CUtensorMap &tm0, const CUtensorMap &tm1, const SkinnyParams &p, dim3 grid, size_t smem, cudaStream_t stream) {
+	if constexpr (NSTREAM == 1 && EPI == EPI_PLAIN) {
+		return p.M <= 8 ? launch_skinny_inst<8, 1, true, 0, EPI_PLAIN>(tm0, tm1, p, grid, smem, stream)
+						: launch_skinny_inst<8, 1, false, 0, EPI_PLAIN>(tm0, tm1, p, grid, smem, stream);
+	} else {
+		return GPTQ_ERR_UNSUPPORTED;
+	}
 }
 
 template <int NSTREAM, int EPI>
@@ -267,7 +309,8 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	dim3 grid;
 	size_t smem;
 	int kw;
-	plan_skinny(p, NSTREAM, kw, grid, smem);
+	const bool narrow = (EPI == EPI_PLAIN && NSTREAM == 1) && plan_narrow(p, grid, smem);
+	if (!narrow) plan_skinny(p, NSTREAM, kw, grid, smem);
 	if (smem > (size_t)SK_SMEM_LIMIT - 1024) return GPTQ_ERR_UNSUPPORTED;
 	const size_t need = skinny_ws_bytes(p.M, p.N, NSTREAM);
 	if (workspace == nullptr || ws_bytes < need) return GPTQ_ERR_WORKSPACE;
@@ -300,6 +343,7 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 		tm1 = tm0;
 	}
 	const bool m8 = p.M <= 8;
+	if (narrow) return launch_narrow<NSTREAM, EPI>(tm0, tm1, p, grid, smem, stream);
 	if (p.spg == 1) {
 		return m8 ? launch_skinny_inst<2, NSTREAM, true, 1, EPI>(tm0, tm1, p, grid, smem, stream)
 				  : launch_skinny_inst<2, NSTREAM, false, 1, EPI>(tm0, tm1, p, grid, smem, stream);
@@ -316,13 +360,13 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 			  : launch_skinny_inst<4, NSTREAM, false, 0, EPI>(tm0, tm1, p, grid, smem, stream);
 }
 
-// Folded RMSNorm (consumer side): decode kernel only, x read in order, at most 64 producer tiles.
+// Folded RMSNorm (consumer side): decode kernel only, x read in order, at most 256 partial sums per row.
 static int check_rms(const void *rms_weight, const float *sumsq_in, int sumsq_tiles, float eps, int M, const int32_t *g_idx,
 					 const int32_t *perm) {
 	if (!rms_weight) return (sumsq_in == nullptr) ? GPTQ_OK : GPTQ_ERR_INVALID;
 	if (!sumsq_in || sumsq_tiles <= 0 || !(eps >= 0.f)) return GPTQ_ERR_INVALID;
 	if (!aligned16(rms_weight)) return GPTQ_ERR_ALIGN;
-	if (M > 16 || g_idx || perm || sumsq_tiles > 64) return GPTQ_ERR_UNSUPPORTED;
+	if (M > 16 || g_idx || perm || sumsq_tiles > 256) return GPTQ_ERR_UNSUPPORTED;
 	return GPTQ_OK;
 }
 
@@ -391,6 +435,7 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
 void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+void gptq_debug_allow_narrow(int on) { g_allow_narrow = on ? 1 : 0; }
 void gptq_debug_use_tc(int on) { g_use_tc = on ? 1 : 0; }
 void gptq_debug_attn_splits(int n) { g_attn_splits = n; }
 // Host-only: the launch plan of the decode kernel for a shape.  out[0..7] = split-K, K-warps, ring stages,

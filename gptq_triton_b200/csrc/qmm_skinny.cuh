@@ -69,7 +69,7 @@ struct SkinnyParams {
 	long long ldr;
 	__half *y;
 	long long ldy;
-	// RMSNorm folded in.  Producer (EPI_PLAIN): ss_out[row][tile] = sum over the tile's 128 columns of
+	// RMSNorm folded in.  Producer (EPI_PLAIN): ss_out[row][c] = sum over columns 32c .. 32c+31 of
 	// the squared fp16 outputs.  Consumer (EPI_SILU / EPI_ROPE, x read in order): x is scaled by
 	// rsqrt(sum_t ss_in[row][t] / K + eps) * rms_w while it is staged (one fp16 rounding, as the
 	// stand-alone RMSNorm kernel does).
@@ -111,21 +111,31 @@ struct SkinnyParams {
 // SPG_T: steps per group known at compile time (1 or 2), or 0 when a group spans whole chunks.
 // x is always read in order: for act-order weights the host gathers x[:, perm] once per call with
 // gather_x_kernel (every CTA of every tile would otherwise repeat the gather with 2-byte loads).
+// KW = 2 or 4: CTA of 4 column-warps x KW K-warps on a 128-column tile, split-K over grid.y.
+// KW = 8: "narrow" CTA of 8 K-warps on ONE 32-column strip and the whole of K (grid.y = 1): the
+// K-warps are reduced in shared memory only, so the partial sums, the arrival ticket and the
+// second pass of a split-K tail disappear; for small outputs (N / 32 CTAs fill the chip).
 template <int KW, int NSTREAM, bool M8, int SPG_T, int EPI>
-__global__ void __launch_bounds__(KW * 128, 4 / KW)
+__global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW)
 	skinny_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, const SkinnyParams p) {
 	extern __shared__ __align__(1024) unsigned char smem[];
-	constexpr int NT = KW * 128;
-	constexpr int NWARP = KW * 4;
+	constexpr bool NARROW = (KW == 8);
+	static_assert(!NARROW || (EPI == EPI_PLAIN && NSTREAM == 1), "narrow CTAs: plain epilogue, one weight stream");
+	constexpr int NWN = NARROW ? 1 : 4;          // column-warps per CTA
+	constexpr int BN = NWN * 32;                 // columns per CTA
+	constexpr int BSH = NARROW ? 5 : 7;          // log2(BN)
+	constexpr int SU = BN / 8, SUSH = NARROW ? 2 : 4;      // 8-column strip units per group row
+	constexpr int NT = NARROW ? 256 : KW * 128;
+	constexpr int NWARP = NT / 32;
 	constexpr int ROWS = M8 ? 8 : 16;
 	constexpr int MB = M8 ? 1 : 2;             // batch-row blocks of 8
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-	const int wn = warp & 3, kw = warp >> 2, gid = lane >> 2, tig = lane & 3;
+	const int wn = NARROW ? 0 : (warp & 3), kw = NARROW ? warp : (warp >> 2), gid = lane >> 2, tig = lane & 3;
 	const int tile = blockIdx.x, split = blockIdx.y;
 	SK_STAMP(0);
 	GPTQ_TRACE_BEGIN(p.trace);
-	const int n0 = tile * SK_BN, n0w = n0 + wn * 32;
+	const int n0 = tile * BN, n0w = n0 + wn * 32;
 	const bool warp_active = n0w < p.N;
 
 	// shared memory: [ ring | mbarriers | x slice | zero strips | scale strips ]; the ring
@@ -135,8 +145,8 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	uint64_t *bars = reinterpret_cast<uint64_t *>(smem + ring_bytes);
 	unsigned char *xs = smem + ring_bytes + SK_BAR_BYTES;
 	__half *s_zz = reinterpret_cast<__half *>(xs + p.xs_bytes);                  // [stream][group][128] zero point (stored + 1)
-	__half *s_sc = s_zz + NSTREAM * p.strip_groups * SK_BN;                      // [stream][group][128] scale
-	float2 *s_cs = reinterpret_cast<float2 *>(s_sc + NSTREAM * p.strip_groups * SK_BN);   // [group][16 rows] (C, S) of x
+	__half *s_sc = s_zz + NSTREAM * p.strip_groups * BN;                      // [stream][group][128] scale
+	float2 *s_cs = reinterpret_cast<float2 *>(s_sc + NSTREAM * p.strip_groups * BN);   // [group][16 rows] (C, S) of x
 	float *red = reinterpret_cast<float *>(smem);
 	__shared__ int s_last;
 
@@ -169,7 +179,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 #ifdef GPTQ_SK_BULK1D
 				{
 					const unsigned char *src = reinterpret_cast<const unsigned char *>((NSTREAM == 2 && pr_stream) ? p.raw1 : p.raw0) +
-											   ((size_t)(tile * 4 + wn) * p.total_chunks + pr_chunk) * SK_CHUNK_BYTES;
+											   ((size_t)(tile * NWN + wn) * p.total_chunks + pr_chunk) * SK_CHUNK_BYTES;
 					asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
 									 ring_w + pr_stage * SK_CHUNK_BYTES),
 								 "l"(src), "r"(SK_CHUNK_BYTES), "r"(bar)
@@ -193,7 +203,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	// not queue behind 100+ KB of weight prefetch per SM; the values are stored afterwards.
 	const int g_lo = (c_lo * 128) / p.groupsize;
 	const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
-	const int n_strip = NSTREAM * ng * 16;              // items of 8 columns
+	const int n_strip = NSTREAM * ng * SU;              // items of 8 columns
 	const int units = (c_hi - c_lo) * 16;               // 16-byte units per x row
 	constexpr int SB = 2, XB = 4;
 	// strips: item -> (stream, group, 8-column unit) without a division (NSTREAM <= 2)
@@ -203,7 +213,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		for (int j = 0; j < SB; ++j) {
 			const int idx = base + j * NT;
 			if (idx < n_strip) {
-				const int r = idx >> 4, c = idx & 15;
+				const int r = idx >> SUSH, c = idx & (SU - 1);
 				const int s = (NSTREAM == 2 && r >= ng) ? 1 : 0, gi = r - s * ng;
 				if (n0 + c * 8 < p.N) {
 					const int32_t *qz = s ? p.qz1 : p.qz0;
@@ -219,7 +229,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		for (int j = 0; j < SB; ++j) {
 			const int idx = base + j * NT;
 			if (idx < n_strip) {
-				const int r = idx >> 4, c = idx & 15;
+				const int r = idx >> SUSH, c = idx & (SU - 1);
 				const int s = (NSTREAM == 2 && r >= ng) ? 1 : 0, gi = r - s * ng;
 				if (n0 + c * 8 < p.N) {
 					// zero point (stored + 1) as fp16, two per word: (0x6401 + nibble) - 1024
@@ -229,7 +239,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 					ze.y = h2_sub(0x64016401u + (((zv >> 8) & 0xFu) | (((zv >> 8) & 0xF0u) << 12)), MAGIC_1024);
 					ze.z = h2_sub(0x64016401u + (((zv >> 16) & 0xFu) | (((zv >> 16) & 0xF0u) << 12)), MAGIC_1024);
 					ze.w = h2_sub(0x64016401u + (((zv >> 24) & 0xFu) | (((zv >> 24) & 0xF0u) << 12)), MAGIC_1024);
-					const size_t o = (size_t)(s * p.strip_groups + gi) * SK_BN + c * 8;
+					const size_t o = (size_t)(s * p.strip_groups + gi) * BN + c * 8;
 					*reinterpret_cast<uint4 *>(s_zz + o) = ze;
 					*reinterpret_cast<uint4 *>(s_sc + o) = sv[j];
 				}
@@ -240,32 +250,43 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	constexpr bool RMS_OK = (EPI != EPI_PLAIN);
 	const bool rms = RMS_OK && p.rms_w != nullptr;
 	__shared__ float s_inv[16];
-	auto x_load = [&](int row0, int unit, uint4(&v)[XB], uint4 &wq) {
-		if (unit >= units) return;
-		const int k = (c_lo * 16 + unit) * 8;
-		if (rms) wq = __ldg(reinterpret_cast<const uint4 *>(p.rms_w + k));
-#pragma unroll
-		for (int j = 0; j < XB; ++j)
-			if (row0 + j < p.M) v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)(row0 + j) * p.ldx + k));
-	};
-	auto x_store = [&](int row0, int unit, const uint4(&v)[XB], const uint4 &wq) {
-		// [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7, the (1,5) and (3,7) pairs divided by 16
-		if (unit >= units) return;
+	// x slice: the (row, block of NT units) items of the CTA's slice in row-major order; a pass covers
+	// XB consecutive items, so XB loads are in flight per thread whatever the shape (many rows of a
+	// short slice, or one row of a long one)
+	const int u_blocks = (units + NT - 1) / NT;
+	auto x_load = [&](int r, int ub, uint4(&v)[XB], uint4(&wq)[XB]) {
 #pragma unroll
 		for (int j = 0; j < XB; ++j) {
-			if (row0 + j < p.M) {
+			const int unit = ub * NT + tid;
+			if (r < p.M && unit < units) {
+				const int k = (c_lo * 16 + unit) * 8;
+				if (rms) wq[j] = __ldg(reinterpret_cast<const uint4 *>(p.rms_w + k));
+				v[j] = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)r * p.ldx + k));
+			}
+			if (++ub == u_blocks) {
+				ub = 0;
+				++r;
+			}
+		}
+	};
+	auto x_store = [&](int &r, int &ub, const uint4(&v)[XB], const uint4(&wq)[XB]) {
+		// [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7, the (1,5) and (3,7) pairs divided by 16
+#pragma unroll
+		for (int j = 0; j < XB; ++j) {
+			const int unit = ub * NT + tid;
+			if (r < p.M && unit < units) {
 				uint4 t = v[j];
 				if (rms) {
 					// x * inv_rms * w: fp32 product, one fp16 rounding (same expression as rmsnorm_kernel)
-					const float inv = s_inv[row0 + j];
-					const uint32_t tv[4] = {t.x, t.y, t.z, t.w}, wv[4] = {wq.x, wq.y, wq.z, wq.w};
+					const float inv = s_inv[r];
+					const uint32_t tv[4] = {t.x, t.y, t.z, t.w}, wv[4] = {wq[j].x, wq[j].y, wq[j].z, wq[j].w};
 					uint32_t ov[4];
 #pragma unroll
 					for (int i = 0; i < 4; ++i) {
 						const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&tv[i]));
 						const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(&wv[i]));
-						const __half2 r = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
-						ov[i] = *reinterpret_cast<const uint32_t *>(&r);
+						const __half2 h = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
+						ov[i] = *reinterpret_cast<const uint32_t *>(&h);
 					}
 					t = make_uint4(ov[0], ov[1], ov[2], ov[3]);
 				}
@@ -274,7 +295,11 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 				o.y = h2_mul(__byte_perm(t.x, t.z, 0x7632), 0x2C002C00u);    // (x1, x5) / 16
 				o.z = __byte_perm(t.y, t.w, 0x5410);                          // (x2, x6)
 				o.w = h2_mul(__byte_perm(t.y, t.w, 0x7632), 0x2C002C00u);    // (x3, x7) / 16
-				*reinterpret_cast<uint4 *>(xs + (size_t)(row0 + j) * p.xs_stride + unit * 16) = o;
+				*reinterpret_cast<uint4 *>(xs + (size_t)r * p.xs_stride + unit * 16) = o;
+			}
+			if (++ub == u_blocks) {
+				ub = 0;
+				++r;
 			}
 		}
 	};
@@ -283,33 +308,33 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		// weight prefetch).  Straight-line code that runs once costs instruction fetch, and this
 		// prologue used to be more than half of the kernel's code.
 		pdl_trigger();
-		const int x_passes = ((p.M + XB - 1) / XB) * ((units + NT - 1) / NT);      // (row block, unit block) pairs
-		const int u_blocks = (units + NT - 1) / NT;
+		const int x_passes = (p.M * u_blocks + XB - 1) / XB;
 		const int n_it = max(max(1, x_passes), (n_strip + NT * SB - 1) / (NT * SB));
-		int xr0 = 0, xu = tid;                               // row block / unit of the current x pass
+		int xr = 0, xub = 0;                                 // first (row, unit block) item of the current x pass
 #pragma unroll 1
 		for (int it = 0; it < n_it; ++it) {
 			uint32_t z0[SB];
-			uint4 sv0[SB], v0[XB], wq = make_uint4(0u, 0u, 0u, 0u);
+			uint4 sv0[SB], v0[XB], wq[XB];
 			strip_load(tid + it * NT * SB, z0, sv0);
 			// x comes from the previous kernel: under programmatic dependent launch it may only be
 			// read after pdl_wait(), i.e. after the weight prefetch; otherwise it is issued first,
 			// ahead of the prefetch burst in the memory queues
 			const bool early = !p.pdl || it > 0;
-			if (early && it < x_passes) x_load(xr0, xu, v0, wq);
+			if (early && it < x_passes) x_load(xr, xub, v0, wq);
 			if (it == 0) {
 #pragma unroll 1
 				for (int s = 0; s < p.nstage; ++s) produce();    // weight prefetch: nstage chunks per warp
 				SK_STAMP(1);
 				pdl_wait();
-				if (!early && x_passes > 0) x_load(xr0, xu, v0, wq);
+				if (!early && x_passes > 0) x_load(xr, xub, v0, wq);
 				if (rms) {
 					// 1/rms of every row from the per-tile sums the producing kernel left (fixed order)
 #pragma unroll 1
 					for (int r = warp; r < p.M; r += NWARP) {
 						const float *sp = p.ss_in + (size_t)r * p.ss_tiles;
-						float t = (lane < p.ss_tiles) ? __ldcg(sp + lane) : 0.f;
-						if (lane + 32 < p.ss_tiles) t += __ldcg(sp + lane + 32);
+						float t = 0.f;
+#pragma unroll 4
+						for (int i = lane; i < p.ss_tiles; i += 32) t += __ldcg(sp + i);
 #pragma unroll
 						for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
 						if (lane == 0) s_inv[r] = rsqrtf(t / (float)p.K + p.rms_eps);
@@ -318,23 +343,18 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 				}
 			}
 			strip_store(tid + it * NT * SB, z0, sv0);
-			if (it < x_passes) x_store(xr0, xu, v0, wq);
-			xu += NT;
-			if (xu - tid >= u_blocks * NT) {
-				xu = tid;
-				xr0 += XB;
-			}
+			if (it < x_passes) x_store(xr, xub, v0, wq);      // advances (xr, xub) by XB items
 		}
 	}
 	// Bias and residual of the first epilogue pass (element tid of the M x 128 tile) are fetched now:
 	// only the last CTA of a tile uses them, but it then finds them in registers instead of paying
 	// a global round trip at the very end of the kernel.
 	float pre_bias = 0.f, pre_res = 0.f;
-	if (EPI == EPI_PLAIN && tid < p.M * SK_BN) {
-		const int n = n0 + (tid & 127);
+	if (EPI == EPI_PLAIN && tid < p.M * BN) {
+		const int n = n0 + (tid & (BN - 1));
 		if (n < p.N) {
 			if (p.bias) pre_bias = __half2float(__ldg(p.bias + n));
-			if (p.residual) pre_res = __half2float(p.residual[(size_t)(tid >> 7) * p.ldr + n]);
+			if (p.residual) pre_res = __half2float(p.residual[(size_t)(tid >> BSH) * p.ldr + n]);
 		}
 	}
 	__syncthreads();
@@ -409,7 +429,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		// instruction fetch is the largest stall of a kernel this short, so code size is kept down.
 #pragma unroll 1
 		for (int s = 0; s < NSTREAM; ++s) {
-			const __half *sc_s = s_sc + (size_t)s * p.strip_groups * SK_BN + strip_col;
+			const __half *sc_s = s_sc + (size_t)s * p.strip_groups * BN + strip_col;
 			float accw[MB][4][2];
 #pragma unroll
 			for (int b = 0; b < MB; ++b)
@@ -425,7 +445,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 					for (int c = 0; c < 4; ++c) g[b][c][0] = g[b][c][1] = 0.f;
 			};
 			auto flush = [&](float(&g)[MB][4][2], int gi) {
-				const uint2 sr = *reinterpret_cast<const uint2 *>(sc_s + (size_t)gi * SK_BN);
+				const uint2 sr = *reinterpret_cast<const uint2 *>(sc_s + (size_t)gi * BN);
 				const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.x));
 				const float2 s23 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.y));
 				const float sf[4] = {s01.x, s01.y, s23.x, s23.y};
@@ -601,39 +621,39 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		for (int b = 0; b < MB; ++b)
 #pragma unroll
 			for (int h = 0; h < 2; ++h) {
-				float *r = red + ((size_t)(kw * NSTREAM + s) * ROWS + (b * 8 + 2 * tig + h)) * SK_BN + wn * 32 + gid * 4;
+				float *r = red + ((size_t)(kw * NSTREAM + s) * ROWS + (b * 8 + 2 * tig + h)) * BN + wn * 32 + gid * 4;
 				*reinterpret_cast<float4 *>(r) = make_float4(acc[s][b][0][h], acc[s][b][1][h], acc[s][b][2][h], acc[s][b][3][h]);
 			}
 	__syncthreads();
 
 	// tile sums land in red[0][stream][row][col] (slot of warp-row 0); with split-K they are
 	// first exchanged through the workspace.
-	const int nelem = NSTREAM * p.M * SK_BN;        // only rows < M matter
+	const int nelem = NSTREAM * p.M * BN;        // only rows < M matter
 	float *wsp = p.ws_partial + (size_t)(tile * p.splitk + split) * nelem;   // [stream][row < M][128]
 	if (M8) {
 		// few rows: one element per thread and pass
 #pragma unroll 1
 		for (int e = tid; e < nelem; e += NT) {
-			const int s = (NSTREAM == 2 && e >= p.M * SK_BN) ? 1 : 0, rc = e - s * (p.M * SK_BN);
-			const int row = rc >> 7, col = rc & 127;
+			const int s = (NSTREAM == 2 && e >= p.M * BN) ? 1 : 0, rc = e - s * (p.M * BN);
+			const int row = rc >> BSH, col = rc & (BN - 1);
 			float v = 0.f;
 #pragma unroll
-			for (int k = 0; k < KW; ++k) v += red[((size_t)(k * NSTREAM + s) * ROWS + row) * SK_BN + col];
+			for (int k = 0; k < KW; ++k) v += red[((size_t)(k * NSTREAM + s) * ROWS + row) * BN + col];
 			{
 				// remove the 1024-offsets and the zero points of this CTA's K-slice
 				const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
-				const __half *zz = s_zz + (size_t)s * p.strip_groups * SK_BN + col;
-				const __half *sc = s_sc + (size_t)s * p.strip_groups * SK_BN + col;
+				const __half *zz = s_zz + (size_t)s * p.strip_groups * BN + col;
+				const __half *sc = s_sc + (size_t)s * p.strip_groups * BN + col;
 				float corr = 0.f;
 #pragma unroll 2
 				for (int gi = 0; gi < ng; ++gi) {
 					const float2 cs = s_cs[gi * 16 + row];
-					corr = fmaf(__half2float(sc[(size_t)gi * SK_BN]), fmaf(__half2float(zz[(size_t)gi * SK_BN]), cs.y, cs.x), corr);
+					corr = fmaf(__half2float(sc[(size_t)gi * BN]), fmaf(__half2float(zz[(size_t)gi * BN]), cs.y, cs.x), corr);
 				}
 				v -= corr;
 			}
 			if (p.splitk == 1)
-				red[((size_t)s * ROWS + row) * SK_BN + col] = v;
+				red[((size_t)s * ROWS + row) * BN + col] = v;
 			else
 				__stcg(wsp + e, v);
 		}
@@ -642,19 +662,19 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		// A thread owns one (stream, column) pair and every tpp-th batch row.  It first builds the
 		// correction sum_g s*(C + z*S) of its rows (scale and zero are read once per group), then
 		// adds the KW warp-row partials and subtracts it.
-		constexpr int PAIRS = NSTREAM * SK_BN, TPP = NT / PAIRS, RPT = 16 / TPP;
+		constexpr int PAIRS = NSTREAM * BN, TPP = NT / PAIRS, RPT = 16 / TPP;
 		const int pair = tid % PAIRS, sub = tid / PAIRS;
-		const int s = pair >> 7, col = pair & 127;
+		const int s = pair >> BSH, col = pair & (BN - 1);
 		const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
-		const __half *zz = s_zz + (size_t)s * p.strip_groups * SK_BN + col;
-		const __half *sc = s_sc + (size_t)s * p.strip_groups * SK_BN + col;
+		const __half *zz = s_zz + (size_t)s * p.strip_groups * BN + col;
+		const __half *sc = s_sc + (size_t)s * p.strip_groups * BN + col;
 		float corr[RPT];
 #pragma unroll
 		for (int i = 0; i < RPT; ++i) corr[i] = 0.f;
 #pragma unroll 1
 		for (int gi = 0; gi < ng; ++gi) {
-			const float sv = __half2float(sc[(size_t)gi * SK_BN]);
-			const float sz = sv * __half2float(zz[(size_t)gi * SK_BN]);
+			const float sv = __half2float(sc[(size_t)gi * BN]);
+			const float sz = sv * __half2float(zz[(size_t)gi * BN]);
 #pragma unroll
 			for (int i = 0; i < RPT; ++i) {
 				const int row = sub + i * TPP;
@@ -670,12 +690,12 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 			if (row < p.M) {
 				float v = 0.f;
 #pragma unroll
-				for (int k = 0; k < KW; ++k) v += red[((size_t)(k * NSTREAM + s) * ROWS + row) * SK_BN + col];
+				for (int k = 0; k < KW; ++k) v += red[((size_t)(k * NSTREAM + s) * ROWS + row) * BN + col];
 				v -= corr[i];
 				if (p.splitk == 1)
-					red[((size_t)s * ROWS + row) * SK_BN + col] = v;
+					red[((size_t)s * ROWS + row) * BN + col] = v;
 				else
-					__stcg(wsp + (size_t)s * p.M * SK_BN + row * SK_BN + col, v);
+					__stcg(wsp + (size_t)s * p.M * BN + row * BN + col, v);
 			}
 		}
 	}
@@ -699,8 +719,8 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		if (M8) {
 #pragma unroll 1
 			for (int e = tid; e < nelem; e += NT) {
-				const int s = (NSTREAM == 2 && e >= p.M * SK_BN) ? 1 : 0, rc = e - s * (p.M * SK_BN);
-				const int row = rc >> 7, col = rc & 127;
+				const int s = (NSTREAM == 2 && e >= p.M * BN) ? 1 : 0, rc = e - s * (p.M * BN);
+				const int row = rc >> BSH, col = rc & (BN - 1);
 				float v = 0.f;        // eight loads in flight, then a fixed-order sum
 #pragma unroll 1
 				for (int k0 = 0; k0 < p.splitk; k0 += 8) {
@@ -710,7 +730,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 #pragma unroll
 					for (int k = 0; k < 8; ++k) v += part[k];
 				}
-				red[((size_t)s * ROWS + row) * SK_BN + col] = v;
+				red[((size_t)s * ROWS + row) * BN + col] = v;
 			}
 		} else {
 #pragma unroll 1
@@ -728,8 +748,8 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 				for (int j = 0; j < 4; ++j) {
 					const int e = e0 + j * NT;
 					if (e < nelem) {
-						const int s = (NSTREAM == 2 && e >= p.M * SK_BN) ? 1 : 0, rc = e - s * (p.M * SK_BN);
-						red[((size_t)s * ROWS + (rc >> 7)) * SK_BN + (rc & 127)] = v[j];
+						const int s = (NSTREAM == 2 && e >= p.M * BN) ? 1 : 0, rc = e - s * (p.M * BN);
+						red[((size_t)s * ROWS + (rc >> BSH)) * BN + (rc & (BN - 1))] = v[j];
 					}
 				}
 			}
@@ -737,7 +757,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 	}
 	__syncthreads();
 
-	const int epi_n = (EPI == EPI_ROPE) ? p.M * 64 : p.M * SK_BN;
+	const int epi_n = (EPI == EPI_ROPE) ? p.M * 64 : p.M * BN;
 	const int e_lo = 0, e_hi = epi_n;
 	const float *fin = red;
 	SK_STAMP(5);
@@ -746,13 +766,13 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		__shared__ float s_ss[64];                           // [row][quarter of the tile]
 		const bool want_ss = (EPI == EPI_PLAIN) && p.ss_out != nullptr;
 #pragma unroll 1
-		for (int e = e_lo + tid; e < e_hi; e += NT) {        // whole warps enter or skip (bounds are multiples of 128)
-			const int row = e >> 7, col = e & 127, n = n0 + col;
+		for (int e = e_lo + tid; e < e_hi; e += NT) {        // whole warps enter or skip (bounds are multiples of 32)
+			const int row = e >> BSH, col = e & (BN - 1), n = n0 + col;
 			float sq = 0.f;
 			if (n < p.N) {
-				float v = fin[(size_t)row * SK_BN + col];
+				float v = fin[(size_t)row * BN + col];
 				if (EPI == EPI_SILU) {
-					v = silu_f32(v) * fin[((size_t)ROWS + row) * SK_BN + col];
+					v = silu_f32(v) * fin[((size_t)ROWS + row) * BN + col];
 				} else if (e == tid) {
 					if (p.bias) v += pre_bias;
 					if (p.residual) v += pre_res;
@@ -773,7 +793,8 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 		}
 		if (want_ss) {
 			__syncthreads();
-			if (tid < p.M) p.ss_out[(size_t)tid * gridDim.x + tile] = (s_ss[tid * 4] + s_ss[tid * 4 + 1]) + (s_ss[tid * 4 + 2] + s_ss[tid * 4 + 3]);
+			// one value per (row, 32 columns): [row][N / 32]
+			if (tid < p.M * NWN) p.ss_out[(size_t)(tid / NWN) * (gridDim.x * NWN) + tile * NWN + (tid % NWN)] = s_ss[tid];
 		}
 	} else {
 		// rotary: the tile is exactly one head (head_dim == 128) of section Q, K or V
@@ -781,7 +802,7 @@ __global__ void __launch_bounds__(KW * 128, 4 / KW)
 #pragma unroll 1
 		for (int e = e_lo + tid; e < e_hi; e += NT) {
 			const int row = e >> 6, d = e & 63;
-			const float a = fin[(size_t)row * SK_BN + d], b = fin[(size_t)row * SK_BN + d + 64];
+			const float a = fin[(size_t)row * BN + d], b = fin[(size_t)row * BN + d + 64];
 			int pos = p.pos[row];
 			if (pos < 0 || pos >= p.max_pos) {          // never index the tables / the cache out of range
 				atomicExch(p.ws_ticket + SK_STATUS_SLOT, 4);

@@ -38,7 +38,7 @@ def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin,
 	With kv_cache = (K, V) each [b, n_heads, max_seq, head_dim] contiguous, K/V rows are written
 	in place at their positions and (q, K, V) is returned.
 	With rms_weight the input is RMS-normalised first: inside the decode kernel when `sumsq_in`
-	(fp32 [M, K // 128], left by the projection that produced `a`) is given and the shape allows,
+	(fp32 [M, K // 32], left by the projection that produced `a`) is given and the shape allows,
 	else by the RMSNorm kernel.
 	"""
 	assert a.dim() == 3 and a.is_contiguous(), "A must be [b, t, K] and contiguous"
@@ -64,13 +64,13 @@ def qkv_rope(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin,
 	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available, rms_fusable
 	max_pos = min(cos.shape[0], (kv_cache[0].shape[2] if kv_cache is not None else cos.shape[0]))
 	if rms_weight is not None and sumsq_in is not None and rms_fusable(M, K, None, perm):
-		assert sumsq_in.dtype == torch.float32 and sumsq_in.is_contiguous() and sumsq_in.numel() >= M * (K // 128)
+		assert sumsq_in.dtype == torch.float32 and sumsq_in.is_contiguous() and sumsq_in.numel() >= M * (K // 32)
 		ws = _lib.workspace(a.device, M, K, 3 * hidden)
 		rc = _lib.lib().gptq_qkv_rope_rms(
 			_lib.ptr(a), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), None, None,
 			_lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), max_pos, _lib.ptr(q), hidden, _lib.ptr(k), _lib.ptr(v), t, sb, st, sh, sp,
 			M, K, n_heads, head_dim, groupsize, K, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device),
-			_lib.ptr(rms_weight), _lib.ptr(sumsq_in), K // 128, float(rms_eps))
+			_lib.ptr(rms_weight), _lib.ptr(sumsq_in), K // 32, float(rms_eps))
 		_lib.check(rc, 'gptq_qkv_rope_rms')
 		return q.transpose(1, 2), k, v
 	if rms_weight is not None:

@@ -44,7 +44,7 @@ def gateup_silu(groupsize: int, a: torch.Tensor, gate_qweight, gate_scales, gate
 				rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6,
 				sumsq_in: Optional[torch.Tensor] = None) -> torch.Tensor:
 	"""silu(a x deq(gate)) * (a x deq(up)); fp32 until the one fp16 store.  With rms_weight the input is
-	RMS-normalised first: inside the decode kernel when `sumsq_in` (fp32 [M, tiles], written by the
+	RMS-normalised first: inside the decode kernel when `sumsq_in` (fp32 [M, K // 32], written by the
 	projection that produced `a`, see quant_linear.qmatmul) is given and the shape allows, else by the
 	library's RMSNorm kernel."""
 	assert gate_qweight.shape == up_qweight.shape and gate_scales.shape == up_scales.shape and gate_qzeros.shape == up_qzeros.shape, "All weights must have the same shape"
@@ -61,13 +61,13 @@ def gateup_silu(groupsize: int, a: torch.Tensor, gate_qweight, gate_scales, gate
 		return c.view(a.shape[:-1] + (N,))
 	from .quant_linear import DECODE_MAX_M, dequant_matmul, prefill_kernel_available, rms_fusable
 	if rms_weight is not None and sumsq_in is not None and rms_fusable(M, K, g_idx, perm):
-		assert sumsq_in.dtype == torch.float32 and sumsq_in.is_contiguous() and sumsq_in.numel() >= M * (K // 128)
+		assert sumsq_in.dtype == torch.float32 and sumsq_in.is_contiguous() and sumsq_in.numel() >= M * (K // 32)
 		ws = _lib.workspace(a.device, M, K, N)
 		rc = _lib.lib().gptq_gateup_silu_rms(
 			_lib.ptr(x), _lib.ptr(gate_qweight), _lib.ptr(gate_qzeros), _lib.ptr(gate_scales),
 			_lib.ptr(up_qweight), _lib.ptr(up_qzeros), _lib.ptr(up_scales), None, None,
 			_lib.ptr(c), M, K, N, groupsize, K, N, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device),
-			_lib.ptr(rms_weight), _lib.ptr(sumsq_in), K // 128, float(rms_eps))
+			_lib.ptr(rms_weight), _lib.ptr(sumsq_in), K // 32, float(rms_eps))
 		_lib.check(rc, 'gptq_gateup_silu_rms')
 		return c.view(a.shape[:-1] + (N,))
 	if rms_weight is not None:

@@ -199,7 +199,7 @@ class DecodeEngine:
 		# RMSNorm folded into the decode kernels: o_proj / down_proj leave per-tile sums of squares of
 		# the hidden state, the next QKV / gate-up kernel scales x while staging it (one GPU only)
 		self.fuse_norm = True
-		tiles = max(1, cfg.hidden_size // 128)
+		tiles = max(1, cfg.hidden_size // 32)
 		self.ss_attn = torch.zeros((batch, tiles), dtype=torch.float32, device=dev)
 		self.ss_mlp = torch.zeros((batch, tiles), dtype=torch.float32, device=dev)
 		self.len_hint = max_seq
@@ -216,7 +216,7 @@ class DecodeEngine:
 		ln1, ln2 = layer.input_layernorm, layer.post_attention_layernorm
 		b = h.shape[0]
 		# the sums of squares describe the all-reduced hidden state only on one GPU
-		fold = self.fuse_norm and decode and self.tp_world == 1 and b <= 16 and self.cfg.hidden_size % 128 == 0 and self.cfg.hidden_size // 128 <= 64
+		fold = self.fuse_norm and decode and self.tp_world == 1 and b <= 16 and self.cfg.hidden_size % 128 == 0 and self.cfg.hidden_size // 32 <= 256
 		if fold:
 			q, _, _ = attn.project_qkv(h.contiguous(), pos, kv_cache=(self.kcache[i], self.vcache[i]), rms_weight=ln1.weight,
 									   rms_eps=ln1.variance_epsilon, sumsq_in=ss_in)      # ss_in None (first layer): RMSNorm kernel

@@ -94,7 +94,7 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 	on the current CUDA stream — the contract of the reference op (quant_linear.py:228-283).
 	`g_idx` gives act-order groups for rows in checkpoint order; `perm` says that qweight was
 	re-ordered with act_order_rows().  `residual` (..., N) is added in the epilogue.
-	`sumsq_out` (fp32 [M, N // 128], decode sizes only) receives the per-tile sums of squares of
+	`sumsq_out` (fp32 [M, N // 32], decode sizes only) receives the sums of squares per 32 columns of
 	the output, from which the next fused op derives the RMSNorm factor (see rms_fusable()).
 	"""
 	assert a.shape[-1] == (qweight.shape[0] * 8), "A must be a multiple of 8 in the last dimension"
@@ -124,7 +124,7 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 		return c.view(a.shape[:-1] + (N,))
 	ws = _lib.workspace(a.device, M, K, N)
 	if sumsq_out is not None:
-		assert sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous() and sumsq_out.numel() >= M * (N // 128)
+		assert sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous() and sumsq_out.numel() >= M * (N // 32)
 		rc = _lib.lib().gptq_qmatmul_sumsq(
 			_lib.ptr(x), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), _lib.ptr(g_idx), _lib.ptr(perm),
 			_lib.ptr(bias), _lib.ptr(res), N, _lib.ptr(c), M, K, N, groupsize, K, N,
@@ -142,7 +142,7 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 def rms_fusable(M: int, N_producer: int, g_idx, perm) -> bool:
 	"""True when the RMSNorm between a producing projection (N_producer outputs) and the next
 	fused op can be folded into the two decode kernels (gptq_qmatmul_sumsq -> *_rms)."""
-	return 0 < M <= DECODE_MAX_M and N_producer % 128 == 0 and N_producer // 128 <= 64 and g_idx is None and perm is None
+	return 0 < M <= DECODE_MAX_M and N_producer % 128 == 0 and N_producer // 32 <= 256 and g_idx is None and perm is None
 
 
 def triton_matmul4(groupsize: int, a: torch.FloatTensor, qweight: torch.IntTensor, scales: torch.FloatTensor,

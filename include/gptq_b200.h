@@ -165,11 +165,12 @@ int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_
  * spends two extra launches per layer on the norm; here the projection that produces the
  * hidden state also leaves per-tile sums of squares, and the next fused op scales x while it
  * stages it:
- *   gptq_qmatmul_sumsq   = gptq_qmatmul, and sumsq_out[row * (N/128) + tile] = sum over the
- *                          tile's 128 columns of y^2 (y as rounded to fp16).  N % 128 == 0.
+ *   gptq_qmatmul_sumsq   = gptq_qmatmul, and sumsq_out[row * (N/32) + c] = sum over columns
+ *                          32c .. 32c+31 of y^2 (y as rounded to fp16).  N % 128 == 0.
  *   gptq_gateup_silu_rms = gptq_gateup_silu on x * rsqrt(sum_t sumsq_in[row*sumsq_tiles + t] / K
  *   gptq_qkv_rope_rms      + rms_eps) * rms_weight (fp32 product, one fp16 rounding: the same
- *                          expression as gptq_rmsnorm).  sumsq_tiles <= 64; no g_idx / perm.
+ *                          expression as gptq_rmsnorm).  sumsq_tiles (= K/32 after
+ *                          gptq_qmatmul_sumsq) <= 256; no g_idx / perm.
  * Shapes outside these limits return GPTQ_ERR_UNSUPPORTED; the caller then runs gptq_rmsnorm.
  */
 int gptq_qmatmul_sumsq(const void *x, const int32_t *qweight, const int32_t *qzeros,

@@ -555,11 +555,11 @@ def test_rmsnorm_folded_into_decode_kernels(G, M):
 	t = synth(Kp, hidden, gs, 81, bias=True)
 	xin = acts((M, Kp), seed=82)
 	res = (torch.randn((M, hidden), generator=rng) * 1.5).half()
-	ss = torch.zeros((M, hidden // 128), dtype=torch.float32, device='cuda')
+	ss = torch.zeros((M, hidden // 32), dtype=torch.float32, device='cuda')
 	h = G.qmatmul(gs, xin.cuda(), t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda(), bias=t['bias'].cuda(), residual=res.cuda(), sumsq_out=ss)
 	h_plain = G.qmatmul(gs, xin.cuda(), t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda(), bias=t['bias'].cuda(), residual=res.cuda())
 	assert torch.equal(h, h_plain), 'the extra output must not change y'
-	ss_ref = h.float().pow(2).view(M, hidden // 128, 128).sum(-1)
+	ss_ref = h.float().pow(2).view(M, hidden // 32, 32).sum(-1)
 	assert torch.allclose(ss, ss_ref, rtol=1e-5, atol=1e-6)
 	# consumers
 	gamma = (torch.rand((hidden,), generator=rng) + 0.5).half()
@@ -589,6 +589,33 @@ def test_rms_folding_rejects_unsupported_shapes(G):
 	K, N, gs = 256, 256, 128
 	t = synth(K, N, gs, 90)
 	x = acts((32, K), seed=91).cuda()
-	ss = torch.zeros((32, N // 128), dtype=torch.float32, device='cuda')
+	ss = torch.zeros((32, N // 32), dtype=torch.float32, device='cuda')
 	with pytest.raises(_lib.GptqB200Error):
 		G.qmatmul(gs, x, t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda(), sumsq_out=ss)
+
+
+@pytest.mark.parametrize('M', [1, 4, 9, 16])
+@pytest.mark.parametrize('K,gs', [(512, 128), (1536, 128), (1024, -1)])
+def test_decode_narrow_geometry(G, M, K, gs):
+	"""Opt-in geometry: one 32-column strip per CTA over the whole of K (no split-K); same results as the
+	tiled split-K form, with bias, residual and the sums of squares."""
+	from gptq_triton_b200 import _lib
+	N = 4096
+	t = synth(K, N, gs, seed=K + M, bias=True)
+	x = acts((M, K), seed=M + 3)
+	res = acts((M, N), seed=M + 4)
+	d = {k: dev(v) for k, v in t.items() if isinstance(v, torch.Tensor)}
+	ss = torch.zeros((M, N // 32), dtype=torch.float32, device='cuda')
+	ss2 = torch.zeros_like(ss)
+	y2 = G.qmatmul(gs, x.cuda(), d['qweight'], d['scales'], d['qzeros'], bias=d['bias'], residual=res.cuda(), sumsq_out=ss2)      # tiled split-K form
+	try:
+		_lib.lib().gptq_debug_allow_narrow(1)
+		y = G.qmatmul(gs, x.cuda(), d['qweight'], d['scales'], d['qzeros'], bias=d['bias'], residual=res.cuda(), sumsq_out=ss)
+	finally:
+		_lib.lib().gptq_debug_allow_narrow(0)
+	r32 = O.qmatmul_r32(x, t['qweight'], t['qzeros'], t['scales'], gs, bias=t['bias'], residual=res)
+	assert O.max_rel_err(y, r32) <= 6e-4 and O.max_rel_err(y2, r32) <= 6e-4
+	assert torch.allclose(ss, y.float().pow(2).view(M, N // 32, 32).sum(-1), rtol=1e-5, atol=1e-6)
+	assert torch.allclose(ss2, y2.float().pow(2).view(M, N // 32, 32).sum(-1), rtol=1e-5, atol=1e-6)
+	torch.cuda.synchronize()
+	assert _lib.kernel_status() == 0
