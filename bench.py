@@ -331,14 +331,14 @@ def gpu_arm(args):
 	if rank == 0:
 		# own kernels per rank and step: 4 quantised matmuls + attention per layer; RMSNorm is folded into them on one GPU
 		# (first layer's input norm and the final norm stay kernels), two RMSNorm kernels per layer under tensor parallelism
-		folded = world == 1 and engine.fuse_norm and batch <= 16
+		folded = engine.fuse_norm and batch <= 16 and (world == 1 or engine.ar_o is not None)
 		launches_per_step = (5 * cfg.num_hidden_layers + 2) if folded else (7 * cfg.num_hidden_layers + 1)
 		line = {
 			'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
 			'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'strong' if world > 1 else 'weak', 'vs_baseline': None, 'dtype': 'f16',
 			'data': 'synthetic',
 			'config': {'workload': WORKLOAD if not big else 'llama65b-arch 4-bit g128 greedy decode, batch 16, 2048-token prompts', 'layers': cfg.num_hidden_layers, 'hidden': cfg.hidden_size, 'groupsize': GROUPSIZE,
-					   'parallelism': ('tp%d: QKV and gate/up by columns, o_proj and down by rows, one NCCL all-reduce after each' % world) if world > 1 else 'single GPU',
+					   'parallelism': (('tp%d: QKV and gate/up by columns, o_proj and down by rows, ' % world) + ('all-reduce fused into those kernels over peer memory' if engine.ar_o is not None else 'one NCCL all-reduce after each')) if world > 1 else 'single GPU',
 					   'l2': 'inputs larger than L2: 3.6 GB of weights + KV cache are streamed every step'},
 			'e2e': {'value': e2e_tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 8 * batch, 'd2h_bytes_per_step': 8 * batch},
 			'gpu_launches': launches_per_step * args.steps,

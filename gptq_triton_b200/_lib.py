@@ -33,6 +33,15 @@ _SIGNATURES = {
 									 _P, _P, c_int, ctypes.c_float]),
 	'gptq_qkv_rope_rms': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int64, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64,
 								  c_int, c_int, c_int, c_int, c_int, c_int64, _P, c_size_t, _P, _P, _P, c_int, ctypes.c_float]),
+	'gptq_ar_partial_bytes': (c_size_t, [c_int]),
+	'gptq_ar_flag_bytes': (c_size_t, [c_int]),
+	'gptq_qmatmul_ar': (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P, c_size_t, _P, _P,
+								c_int, c_int, _P, _P]),
+	'gptq_peer_alloc': (c_int, [c_size_t, ctypes.POINTER(c_void_p)]),
+	'gptq_peer_free': (c_int, [_P]),
+	'gptq_peer_export': (c_int, [_P, _P]),
+	'gptq_peer_open': (c_int, [_P, ctypes.POINTER(c_void_p)]),
+	'gptq_peer_close': (c_int, [_P]),
 	'gptq_unpack_qweight': (c_int, [_P, _P, c_int, c_int, _P]),
 	'gptq_unpack_qzeros': (c_int, [_P, _P, c_int, c_int, _P]),
 	'gptq_dequantize': (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),

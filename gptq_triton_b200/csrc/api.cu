@@ -309,7 +309,7 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	dim3 grid;
 	size_t smem;
 	int kw;
-	const bool narrow = (EPI == EPI_PLAIN && NSTREAM == 1) && plan_narrow(p, grid, smem);
+	const bool narrow = (EPI == EPI_PLAIN && NSTREAM == 1) && p.ar_world <= 1 && plan_narrow(p, grid, smem);
 	if (!narrow) plan_skinny(p, NSTREAM, kw, grid, smem);
 	if (smem > (size_t)SK_SMEM_LIMIT - 1024) return GPTQ_ERR_UNSUPPORTED;
 	const size_t need = skinny_ws_bytes(p.M, p.N, NSTREAM);
@@ -466,10 +466,16 @@ size_t gptq_workspace_bytes(int M, int K, int N) {
 	return std::max(gather_offset(skinny_ws_bytes(M, N, 2)) + gather_bytes(M, std::max(K, 0)), tc_ws_bytes(M, N));
 }
 
+struct ArArgs {
+	int world, rank;
+	void *const *partials;
+	void *const *flags;
+};
+
 static int qmatmul_impl(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
 						const int32_t *perm, const void *bias, const void *residual, int64_t ldr, void *y, int M, int K, int N,
 						int groupsize, int64_t ldx, int64_t ldy, void *workspace, size_t workspace_bytes, gptq_stream_t stream,
-						float *sumsq_out) {
+						float *sumsq_out, const ArArgs *ar = nullptr) {
 	int rc = check_common(x, qweight, qzeros, scales, y, M, K, N, groupsize, ldx, ldy);
 	if (rc != GPTQ_OK) return rc;
 	if (g_idx && perm) return GPTQ_ERR_INVALID;
@@ -479,6 +485,13 @@ static int qmatmul_impl(const void *x, const int32_t *qweight, const int32_t *qz
 	const bool fast = skinny_shape_ok(K, N, groupsize, g_idx) && (!perm || aligned16(perm));
 	// the per-tile sums of squares exist in the decode kernel only (whole 128-column tiles)
 	if (sumsq_out && !(fast && M <= 16 && N % 128 == 0)) return GPTQ_ERR_UNSUPPORTED;
+	if (ar) {
+		// the fused all-reduce lives in the decode kernel's epilogue
+		if (ar->world < 2 || ar->world > 8 || ar->rank < 0 || ar->rank >= ar->world || !ar->partials || !ar->flags) return GPTQ_ERR_INVALID;
+		if (!(fast && M <= 16 && N % 128 == 0)) return GPTQ_ERR_UNSUPPORTED;
+		for (int r = 0; r < ar->world; ++r)
+			if (!ar->partials[r] || !ar->flags[r] || !aligned16(ar->partials[r])) return GPTQ_ERR_INVALID;
+	}
 	if (fast && M <= 16) {
 		SkinnyParams p = {};
 		p.x = (const __half *)x; p.ldx = ldx;
@@ -488,6 +501,12 @@ static int qmatmul_impl(const void *x, const int32_t *qweight, const int32_t *qz
 		p.bias = (const __half *)bias; p.residual = (const __half *)residual; p.ldr = ldr;
 		p.y = (__half *)y; p.ldy = ldy;
 		p.ss_out = sumsq_out;
+		if (ar) {
+			p.ar_world = ar->world;
+			p.ar_rank = ar->rank;
+			for (int r = 0; r < ar->world; ++r) p.ar_buf[r] = reinterpret_cast<unsigned long long *>(ar->partials[r]);
+			p.ar_seq = reinterpret_cast<unsigned *>(ar->flags[ar->rank]);
+		}
 		return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, workspace, workspace_bytes, st);
 	}
 	if (fast && !perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
@@ -510,6 +529,19 @@ int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, c
 				 int groupsize, int64_t ldx, int64_t ldy, void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
 	return qmatmul_impl(x, qweight, qzeros, scales, g_idx, perm, bias, residual, ldr, y, M, K, N, groupsize, ldx, ldy, workspace,
 						workspace_bytes, stream, nullptr);
+}
+
+// ---- tensor parallelism: row-parallel projection with the all-reduce in its epilogue ----------------------
+size_t gptq_ar_partial_bytes(int N) { return N <= 0 ? 0 : (size_t)8 * ((N + SK_BN - 1) / SK_BN) * 16 * SK_BN * sizeof(unsigned long long); }
+size_t gptq_ar_flag_bytes(int N) { return N <= 0 ? 0 : (((size_t)((N + SK_BN - 1) / SK_BN) * sizeof(unsigned)) + 255) & ~(size_t)255; }
+
+int gptq_qmatmul_ar(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
+					const int32_t *perm, const void *bias, const void *residual, int64_t ldr, void *y, int M, int K, int N,
+					int groupsize, int64_t ldx, int64_t ldy, void *workspace, size_t workspace_bytes, gptq_stream_t stream,
+					float *sumsq_out, int world, int rank, void *const *partials, void *const *flags) {
+	ArArgs ar = {world, rank, partials, flags};
+	return qmatmul_impl(x, qweight, qzeros, scales, g_idx, perm, bias, residual, ldr, y, M, K, N, groupsize, ldx, ldy, workspace,
+						workspace_bytes, stream, sumsq_out, &ar);
 }
 
 int gptq_qmatmul_sumsq(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,

@@ -78,6 +78,14 @@ struct SkinnyParams {
 	const float *ss_in;
 	int ss_tiles;
 	float rms_eps;
+	// Tensor parallelism, row-parallel projection (EPI_PLAIN): the all-reduce of the partial sums is part
+	// of the epilogue.  Every rank PUSHES its tile (fp32, bias included) into the receive buffers of its
+	// peers as 8-byte words {value, sequence number} (one store carries the data and its own flag, so no
+	// fence and no separate signal is needed), then polls its OWN receive buffer until the words of every
+	// peer carry this launch's sequence number, and adds the tiles in rank order: the same bits on every rank.
+	int ar_world, ar_rank;
+	unsigned long long *ar_buf[8];     // receive buffer of every rank: [source rank][tile][16 rows][128] words
+	unsigned *ar_seq;                  // this rank's sequence number per tile (same on every rank: same launches)
 	// EPI_ROPE
 	const __half *cos_t, *sin_t;
 	const int32_t *pos;
@@ -765,6 +773,56 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 	if (EPI == EPI_PLAIN || EPI == EPI_SILU) {
 		__shared__ float s_ss[64];                           // [row][quarter of the tile]
 		const bool want_ss = (EPI == EPI_PLAIN) && p.ss_out != nullptr;
+		const bool ar = (EPI == EPI_PLAIN) && !NARROW && p.ar_world > 1;
+		if (ar) {
+			__shared__ unsigned s_seq;
+			if (tid == 0) s_seq = p.ar_seq[tile] + 1u;           // written by the previous launch on this buffer, long complete
+			__syncthreads();
+			const unsigned seq = s_seq;
+			const size_t slot = ((size_t)p.ar_rank * gridDim.x + tile) * (16 * BN);      // where this rank's words go in a peer's buffer
+#pragma unroll 1
+			for (int e = e_lo + tid; e < e_hi; e += NT) {
+				const int n = n0 + (e & (BN - 1));
+				float v = 0.f;
+				if (n < p.N) {
+					v = fin[e];                                  // [row][BN] is contiguous: e = row * BN + col
+					if (p.bias) v += __half2float(p.bias[n]);
+				}
+				red[e] = v;                                      // own share, read back by the same thread below
+				const unsigned long long w = ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(v);
+#pragma unroll 1
+				for (int r = 0; r < p.ar_world; ++r)
+					if (r != p.ar_rank) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.ar_buf[r] + slot + e), "l"(w) : "memory");
+			}
+			const unsigned long long t0 = global_timer_ns();
+			bool ok = true;
+#pragma unroll 1
+			for (int e = e_lo + tid; e < e_hi; e += NT) {
+				float v = 0.f;
+#pragma unroll 1
+				for (int r = 0; r < p.ar_world; ++r) {           // rank order: identical sums everywhere
+					if (r == p.ar_rank) {
+						v += red[e];
+						continue;
+					}
+					const unsigned long long *src = p.ar_buf[p.ar_rank] + ((size_t)r * gridDim.x + tile) * (16 * BN) + e;
+					unsigned long long w;
+#pragma unroll 1
+					for (;;) {
+						asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+						if ((unsigned)(w >> 32) == seq) break;
+						if (global_timer_ns() - t0 > 2000000000ull) {        // a peer never arrived
+							ok = false;
+							break;
+						}
+					}
+					v += __uint_as_float((unsigned)w);
+				}
+				red[e] = v;
+			}
+			if (!ok) atomicExch(p.ws_ticket + SK_STATUS_SLOT, 5);
+			if (tid == 0) p.ar_seq[tile] = seq;
+		}
 #pragma unroll 1
 		for (int e = e_lo + tid; e < e_hi; e += NT) {        // whole warps enter or skip (bounds are multiples of 32)
 			const int row = e >> BSH, col = e & (BN - 1), n = n0 + col;
@@ -774,10 +832,10 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 				if (EPI == EPI_SILU) {
 					v = silu_f32(v) * fin[((size_t)ROWS + row) * BN + col];
 				} else if (e == tid) {
-					if (p.bias) v += pre_bias;
+					if (p.bias && !ar) v += pre_bias;
 					if (p.residual) v += pre_res;
 				} else {
-					if (p.bias) v += __half2float(p.bias[n]);
+					if (p.bias && !ar) v += __half2float(p.bias[n]);
 					if (p.residual) v += __half2float(p.residual[(size_t)row * p.ldr + n]);
 				}
 				const __half hv = __float2half_rn(v);

@@ -151,10 +151,10 @@ class QuantLlamaMLP(nn.Module):
 						   self._up_qw, self.up_proj_scales, self.up_proj_qzeros, g_idx=self._gidx, perm=self._perm,
 						   rms_weight=rms_weight, rms_eps=rms_eps, sumsq_in=sumsq_in)
 
-	def forward(self, x, residual: Optional[torch.Tensor] = None, rms_weight=None, rms_eps=1e-6, sumsq_in=None, sumsq_out=None):
+	def forward(self, x, residual: Optional[torch.Tensor] = None, rms_weight=None, rms_eps=1e-6, sumsq_in=None, sumsq_out=None, ar=None):
 		"""`rms_weight` (+ `sumsq_in`): RMS-normalise x first (inside the kernel when sumsq_in is given);
 		`sumsq_out`: let down_proj leave the per-tile sums of squares of its output (decode sizes)."""
 		h = self.intermediate(x, rms_weight, rms_eps, sumsq_in)
-		if residual is None and sumsq_out is None:
+		if residual is None and sumsq_out is None and ar is None:
 			return self.down_proj(h)
-		return self.down_proj(h, residual=residual, sumsq_out=sumsq_out)
+		return self.down_proj(h, residual=residual, sumsq_out=sumsq_out, ar=ar)      # ar: tensor-parallel exchange (tp.PeerExchange)

@@ -12,6 +12,8 @@ Two ways to run it:
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
 
@@ -195,6 +197,13 @@ class DecodeEngine:
 		self.pos = torch.zeros((batch, 1), dtype=torch.int32, device=dev)          # position of the token being fed
 		self.tok = torch.zeros((batch, 1), dtype=torch.int64, device=dev)          # token being fed
 		self.mask = torch.full((batch, 1, 1, max_seq), float('-inf'), dtype=torch.float16, device=dev)
+		# tensor parallelism, decode steps: the all-reduce after o_proj / down_proj is fused into those kernels
+		# over peer memory (one exchange buffer per projection); GPTQ_B200_TP_FUSED=0 keeps NCCL
+		self.ar_o = self.ar_down = None
+		if self.tp_world > 1 and batch <= 16 and cfg.hidden_size % 128 == 0 and os.environ.get('GPTQ_B200_TP_FUSED', '1') != '0':
+			from .tp import PeerExchange
+			self.ar_o = PeerExchange(cfg.hidden_size, self.tp_rank, self.tp_world, tp_group)
+			self.ar_down = PeerExchange(cfg.hidden_size, self.tp_rank, self.tp_world, tp_group)
 		self.use_graph = use_graph
 		# RMSNorm folded into the decode kernels: o_proj / down_proj leave per-tile sums of squares of
 		# the hidden state, the next QKV / gate-up kernel scales x while staging it (one GPU only)
@@ -215,8 +224,10 @@ class DecodeEngine:
 		decode = h.shape[1] == 1
 		ln1, ln2 = layer.input_layernorm, layer.post_attention_layernorm
 		b = h.shape[0]
-		# the sums of squares describe the all-reduced hidden state only on one GPU
-		fold = self.fuse_norm and decode and self.tp_world == 1 and b <= 16 and self.cfg.hidden_size % 128 == 0 and self.cfg.hidden_size // 32 <= 256
+		# tensor parallelism: with the all-reduce inside the projection kernels every rank holds the reduced
+		# hidden state (and its sums of squares); with NCCL the norms stay separate kernels
+		fused_ar = decode and self.ar_o is not None and b <= 16
+		fold = self.fuse_norm and decode and (self.tp_world == 1 or fused_ar) and b <= 16 and self.cfg.hidden_size % 128 == 0 and self.cfg.hidden_size // 32 <= 256
 		if fold:
 			q, _, _ = attn.project_qkv(h.contiguous(), pos, kv_cache=(self.kcache[i], self.vcache[i]), rms_weight=ln1.weight,
 									   rms_eps=ln1.variance_epsilon, sumsq_in=ss_in)      # ss_in None (first layer): RMSNorm kernel
@@ -231,26 +242,29 @@ class DecodeEngine:
 			v = self.vcache[i][:b, :, :kv_len]
 			o = F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask)
 			o = o.transpose(1, 2).reshape(b, h.shape[1], -1)      # local heads x head_dim
-		res = h if self.tp_rank == 0 else None
 		mlp = layer.mlp
+		fused_ar = fused_ar and isinstance(mlp, QuantLlamaMLP)
+		res = h if (self.tp_rank == 0 or fused_ar) else None          # the fused exchange adds the residual on every rank
 		fold_mlp = fold and isinstance(mlp, QuantLlamaMLP) and attn.o_proj.g_idx is None
+		ar_o = self.ar_o if fused_ar else None
 		if fold_mlp:
-			h = attn.o_proj(o, residual=res, sumsq_out=self.ss_attn)
+			h = attn.o_proj(o, residual=res, sumsq_out=self.ss_attn, ar=ar_o)
 		else:
-			h = attn.o_proj(o, residual=res)
-		if self.tp_world > 1:
+			h = attn.o_proj(o, residual=res, ar=ar_o)
+		if self.tp_world > 1 and not fused_ar:
 			all_reduce_(h, self.tp_group)
-		res = h if self.tp_rank == 0 else None
+		res = h if (self.tp_rank == 0 or fused_ar) else None
 		ss_out = None
 		if fold_mlp:
 			ss_out = self.ss_mlp if mlp.down_proj.g_idx is None else None
-			h = mlp(h, residual=res, rms_weight=ln2.weight, rms_eps=ln2.variance_epsilon, sumsq_in=self.ss_attn, sumsq_out=ss_out)
+			h = mlp(h, residual=res, rms_weight=ln2.weight, rms_eps=ln2.variance_epsilon, sumsq_in=self.ss_attn, sumsq_out=ss_out,
+					ar=self.ar_down if fused_ar else None)
 		elif isinstance(mlp, QuantLlamaMLP):
-			h = mlp(rmsnorm_kernel(h, ln2.weight, ln2.variance_epsilon), residual=res)
+			h = mlp(rmsnorm_kernel(h, ln2.weight, ln2.variance_epsilon), residual=res, ar=self.ar_down if fused_ar else None)
 		else:
 			x = rmsnorm_kernel(h, ln2.weight, ln2.variance_epsilon)
 			h = mlp(x) if res is None else res + mlp(x)
-		if self.tp_world > 1:
+		if self.tp_world > 1 and not fused_ar:
 			all_reduce_(h, self.tp_group)
 		return h, ss_out
 
@@ -294,6 +308,11 @@ class DecodeEngine:
 			self._step_body()
 			return self.tok
 		if self.graph is None:
+			if self.ar_o is not None:
+				# the fused exchange waits at most two seconds for a peer: start the ranks together
+				import torch.distributed as dist
+				torch.cuda.synchronize()
+				dist.barrier(group=self.tp_group)
 			# warm up on a side stream (allocations, workspaces), then capture
 			saved = (self.tok.clone(), self.pos.clone(), self.mask.clone())
 			s = torch.cuda.Stream()

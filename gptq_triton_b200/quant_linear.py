@@ -86,7 +86,7 @@ def dequant_matmul(x2d: torch.Tensor, groupsize: int, qweight, scales, qzeros, g
 
 def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor,
 			bias: Optional[torch.Tensor] = None, g_idx: Optional[torch.Tensor] = None, perm: Optional[torch.Tensor] = None,
-			residual: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+			residual: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None, ar=None) -> torch.Tensor:
 	"""C = A x deq(B) (+ bias) (+ residual).
 
 	A (..., K) fp16 contiguous; qweight (K//8, N) int32; scales (G, N) fp16; qzeros (G, N//8)
@@ -96,6 +96,9 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 	re-ordered with act_order_rows().  `residual` (..., N) is added in the epilogue.
 	`sumsq_out` (fp32 [M, N // 32], decode sizes only) receives the sums of squares per 32 columns of
 	the output, from which the next fused op derives the RMSNorm factor (see rms_fusable()).
+	`ar` (tp.PeerExchange, decode sizes only): this call is one rank's share of a row-parallel
+	projection; the partial sums of all ranks are added inside the kernel (every rank gets the
+	full result, residual included).
 	"""
 	assert a.shape[-1] == (qweight.shape[0] * 8), "A must be a multiple of 8 in the last dimension"
 	assert a.is_contiguous(), "A must be contiguous"
@@ -123,6 +126,16 @@ def qmatmul(groupsize: int, a: torch.Tensor, qweight: torch.Tensor, scales: torc
 			c = c + res
 		return c.view(a.shape[:-1] + (N,))
 	ws = _lib.workspace(a.device, M, K, N)
+	if ar is not None:
+		if sumsq_out is not None:
+			assert sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous() and sumsq_out.numel() >= M * (N // 32)
+		rc = _lib.lib().gptq_qmatmul_ar(
+			_lib.ptr(x), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), _lib.ptr(g_idx), _lib.ptr(perm),
+			_lib.ptr(bias), _lib.ptr(res), N, _lib.ptr(c), M, K, N, groupsize, K, N,
+			_lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device), _lib.ptr(sumsq_out),
+			ar.world, ar.rank, ar.partials, ar.flags)
+		_lib.check(rc, 'gptq_qmatmul_ar')
+		return c.view(a.shape[:-1] + (N,))
 	if sumsq_out is not None:
 		assert sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous() and sumsq_out.numel() >= M * (N // 32)
 		rc = _lib.lib().gptq_qmatmul_sumsq(
@@ -256,7 +269,7 @@ class QuantLinear(nn.Module):
 			return self.qweight, self.g_idx, None
 		return self.qweight, None, None
 
-	def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+	def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None, ar=None) -> torch.Tensor:
 		qw, g_idx, perm = self.kernel_operands()
 		return qmatmul(self.groupsize, x, qw, self.scales, self.qzeros, self.bias, g_idx=g_idx, perm=perm, residual=residual,
-					   sumsq_out=sumsq_out)
+					   sumsq_out=sumsq_out, ar=ar)

@@ -101,3 +101,51 @@ def all_reduce_(t: torch.Tensor, group=None) -> torch.Tensor:
 	if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
 		dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
 	return t
+
+
+class PeerExchange:
+	"""Exchange buffers of one row-parallel projection for the all-reduce fused into the decode
+	kernel's epilogue (gptq_qmatmul_ar): every rank allocates a partial-sum buffer and arrival
+	counters with cudaMalloc, the ranks of the node trade CUDA IPC handles through the process
+	group and map each other's buffers.  `partials` / `flags` are the pointer arrays the C ABI takes."""
+
+	def __init__(self, n_out: int, rank: int, world: int, group=None):
+		import ctypes
+		import torch.distributed as dist
+		from . import _lib
+		L = _lib.lib()
+		self.rank, self.world = rank, world
+		self.flag_bytes = int(L.gptq_ar_flag_bytes(n_out))
+		self.bytes = self.flag_bytes + int(L.gptq_ar_partial_bytes(n_out))
+		own = ctypes.c_void_p()
+		_lib.check(L.gptq_peer_alloc(self.bytes, ctypes.byref(own)), 'gptq_peer_alloc')
+		self._own = own
+		handle = (ctypes.c_ubyte * 64)()
+		_lib.check(L.gptq_peer_export(own, handle), 'gptq_peer_export')
+		handles = [None] * world
+		dist.all_gather_object(handles, bytes(handle), group=group)
+		base = []
+		self._opened = []
+		for r in range(world):
+			if r == rank:
+				base.append(own.value)
+				continue
+			buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
+			ptr = ctypes.c_void_p()
+			_lib.check(L.gptq_peer_open(buf, ctypes.byref(ptr)), 'gptq_peer_open')
+			self._opened.append(ptr)
+			base.append(ptr.value)
+		# layout of a buffer: [arrival counters][partial sums]
+		self.flags = (ctypes.c_void_p * 8)(*([b for b in base] + [None] * (8 - world)))
+		self.partials = (ctypes.c_void_p * 8)(*([b + self.flag_bytes for b in base] + [None] * (8 - world)))
+		dist.barrier(group=group)          # every rank has mapped every buffer before the first launch
+
+	def close(self):
+		from . import _lib
+		L = _lib.lib()
+		for ptr in self._opened:
+			L.gptq_peer_close(ptr)
+		self._opened = []
+		if self._own is not None:
+			L.gptq_peer_free(self._own)
+			self._own = None

@@ -197,6 +197,40 @@ int gptq_qkv_rope_rms(const void *x, const int32_t *qweight, const int32_t *qzer
                       const float *sumsq_in, int sumsq_tiles, float rms_eps);
 
 /*
+ * Tensor parallelism on one node: a row-parallel projection (o_proj, down_proj: this rank holds
+ * rows [k_lo, k_hi) of the weight) whose all-reduce is part of the kernel's epilogue.  No
+ * counterpart in the reference, which has no multi-GPU code.  Decode sizes only (M <= 16,
+ * N % 128 == 0); larger M uses gptq_qmatmul + an NCCL all-reduce.
+ *   partials[r]   receive buffer of rank r as mapped into THIS process (own buffer for r == rank),
+ *                 gptq_ar_partial_bytes(N) bytes, zeroed once.
+ *   flags[rank]   this rank's per-tile sequence numbers, gptq_ar_flag_bytes(N) bytes, zeroed once
+ *                 (the other entries of flags are not used).
+ * One pair per projection that alternates in a layer (o_proj and down_proj must not share one).
+ * Every rank calls with the same arguments in the same order.  Each rank pushes its tile in fp32
+ * (bias included: pass it on one rank only) into its peers' receive buffers as 8-byte words
+ * {value, sequence number}, polls its own buffer (at most two seconds, then status word 5) until
+ * the words of every peer carry this call's sequence number, and adds the tiles of all ranks in
+ * rank order, then residual, fp16 rounding and (optionally) the sums of squares as in
+ * gptq_qmatmul_sumsq: every rank ends with the same bits.  `residual` is added on every rank.
+ * gptq_peer_* allocate such buffers outside any caching allocator (cudaMalloc) and pass them
+ * between the processes of a node as CUDA IPC handles (64 bytes).
+ */
+size_t gptq_ar_partial_bytes(int N);
+size_t gptq_ar_flag_bytes(int N);
+int gptq_qmatmul_ar(const void *x, const int32_t *qweight, const int32_t *qzeros,
+                    const void *scales, const int32_t *g_idx, const int32_t *perm,
+                    const void *bias, const void *residual, int64_t ldr, void *y,
+                    int M, int K, int N, int groupsize, int64_t ldx, int64_t ldy,
+                    void *workspace, size_t workspace_bytes, gptq_stream_t stream,
+                    float *sumsq_out, int world, int rank, void *const *partials,
+                    void *const *flags);
+int gptq_peer_alloc(size_t bytes, void **ptr);
+int gptq_peer_free(void *ptr);
+int gptq_peer_export(void *ptr, void *handle64);
+int gptq_peer_open(const void *handle64, void **ptr);
+int gptq_peer_close(void *ptr);
+
+/*
  * Allocation-free form of gptq_qmatmul for the decode regime (M <= 16).  No counterpart in the
  * reference.  It exists for callers that cannot provide or obtain scratch memory: a host that has
  * given the whole device to its own memory pool, or a latency-critical serving loop in which
