@@ -140,7 +140,9 @@ _retired = []
 
 def kernel_status(device=None) -> int:
 	"""OR of the status words that the decode kernels keep in their workspaces (0 = healthy;
-	1 = a TMA load never completed within the bounded wait; 2 = shared memory misaligned)."""
+	1 = a TMA / bulk load never completed within the bounded wait; 2 = shared memory misaligned;
+	3 = a wait inside the tensor-core kernel ran out; 4 = position outside the rotary table / cache;
+	5 = a peer never arrived in the fused tensor-parallel all-reduce)."""
 	st = 0
 	for (dev, _), ws in _workspaces.items():
 		if device is None or dev == (device.index if isinstance(device, torch.device) else device):

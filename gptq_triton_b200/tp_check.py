@@ -15,7 +15,7 @@ import torch.distributed as dist
 
 def main():
 	import gptq_triton_b200 as G
-	from gptq_triton_b200 import tp
+	from gptq_triton_b200 import _lib, tp
 	from gptq_triton_b200.llama import LlamaConfig
 	rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])
 	local = int(os.environ.get('LOCAL_RANK', rank))
@@ -26,6 +26,7 @@ def main():
 					  max_position_embeddings=256)
 	steps, prompt_len = 16, 40
 	ok = True
+	engines = []          # kept alive: their exchange buffers are mapped by the peers until the end
 	for seed in range(6):
 		whole = G.synthetic_quantized_llama(cfg, groupsize=128, seed=seed, device=dev, fuse=True)
 		part = G.synthetic_quantized_llama(cfg, groupsize=128, seed=seed, device=dev, fuse=False)
@@ -37,6 +38,7 @@ def main():
 			"""Greedy generation; returns tokens [b, steps] and the top-1/top-2 logit margin before every
 			token."""
 			e = G.DecodeEngine(model, batch=2, max_seq=prompt_len + steps + 4, use_graph=use_graph)
+			engines.append(e)
 			toks = [e.prefill(prompt)]
 			top2 = e.logits.float().topk(2, dim=-1).values
 			margins = [float((top2[..., 0] - top2[..., 1]).min())]
@@ -46,7 +48,9 @@ def main():
 				margins.append(float((top2[..., 0] - top2[..., 1]).min()))
 			return torch.cat(toks, dim=1), margins
 		t1, margins = run(whole, False)
-		for use_graph in (False, True):
+		# both forms of the all-reduce: fused into the projection kernels over peer memory, and NCCL
+		for use_graph, fused in ((False, True), (True, True), (True, False)):
+			os.environ['GPTQ_B200_TP_FUSED'] = '1' if fused else '0'
 			t2, _ = run(part, use_graph)
 			diff = (t1 != t2).any(dim=0).nonzero()
 			first = int(diff[0]) if diff.numel() else -1
@@ -54,11 +58,16 @@ def main():
 			# error (and everything after the first flip legitimately differs)
 			tie = first >= 0 and margins[first] < 0.05
 			if rank == 0:
-				print(f'seed {seed} graph={use_graph}: first differing step {first} (margin there {margins[first] if first >= 0 else 0:.3f})'
+				print(f'seed {seed} graph={use_graph} fused={fused}: first differing step {first} (margin there {margins[first] if first >= 0 else 0:.3f})'
 					  f' -> {"identical" if first < 0 else ("tie" if tie else "MISMATCH")}', flush=True)
 			if first >= 0 and not tie:
 				ok = False
 		del whole, part
+	torch.cuda.synchronize()
+	status = _lib.kernel_status(dev)
+	if status != 0:
+		print(f'rank {rank}: kernel status word {status} (5 = a peer never arrived in the fused all-reduce)', flush=True)
+		ok = False
 	flag = torch.tensor([1 if ok else 0], device=dev)
 	dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 	res = int(flag.item())
