@@ -58,6 +58,7 @@ _OPTIONAL = {
 	'gptq_debug_force_kw': (None, [c_int]),
 	'gptq_debug_set_pdl': (None, [c_int]),
 	'gptq_debug_allow_narrow': (None, [c_int]),
+	'gptq_debug_allow_words': (None, [c_int]),
 	'gptq_debug_tc_force': (None, [c_int]),
 }
 
@@ -142,7 +143,7 @@ def kernel_status(device=None) -> int:
 	"""OR of the status words that the decode kernels keep in their workspaces (0 = healthy;
 	1 = a TMA / bulk load never completed within the bounded wait; 2 = shared memory misaligned;
 	3 = a wait inside the tensor-core kernel ran out; 4 = position outside the rotary table / cache;
-	5 = a peer never arrived in the fused tensor-parallel all-reduce)."""
+	5 = a peer never arrived in the fused tensor-parallel all-reduce; 6 = a split-K partial sum never arrived)."""
 	st = 0
 	for (dev, _), ws in _workspaces.items():
 		if device is None or dev == (device.index if isinstance(device, torch.device) else device):

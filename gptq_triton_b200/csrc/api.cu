@@ -133,6 +133,9 @@ static bool skinny_shape_ok(int K, int N, int groupsize, const int32_t *g_idx) {
 // scratch for x[:, perm] of an act-order decode call, placed behind the partial sums
 static size_t gather_offset(size_t base) { return (base + 255) & ~(size_t)255; }
 static size_t gather_bytes(int M, int K) { return (size_t)std::min(M, 16) * (size_t)K * sizeof(__half); }
+// Workspace of a decode call: [counters | fp32 partial sums][8-byte words of the ticket-free exchange, M <= 8][gathered x]
+static size_t words_offset(size_t base) { return (base + 255) & ~(size_t)255; }
+static size_t words_bytes(int M, size_t base) { return M <= 8 ? 2 * (base - SK_TICKET_BYTES) : 0; }
 
 static size_t skinny_ws_bytes(int M, int N, int nstream) {
 	const size_t tiles = (size_t)(N + SK_BN - 1) / SK_BN;
@@ -241,6 +244,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 
 // Narrow geometry (one 32-column strip and the whole of K per CTA, no split-K): worth it when
 // N / 32 CTAs fill most of the chip in one wave and the x rows of the whole K fit in shared memory.
+static int g_allow_words = 1;       // ticket-free split-K exchange (gptq_debug_allow_words)
 static int g_allow_narrow = 0;      // opt-in (gptq_debug_allow_narrow): measured slower than the tiled split-K form
 static bool plan_narrow(SkinnyParams &p, dim3 &grid, size_t &smem) {
 	if (!g_allow_narrow || g_force_splitk > 0) return false;
@@ -314,9 +318,13 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	if (smem > (size_t)SK_SMEM_LIMIT - 1024) return GPTQ_ERR_UNSUPPORTED;
 	const size_t need = skinny_ws_bytes(p.M, p.N, NSTREAM);
 	if (workspace == nullptr || ws_bytes < need) return GPTQ_ERR_WORKSPACE;
+	// ticket-free split-K exchange: M <= 8, one wave of co-resident CTAs (the polling CTA is the last one dispatched)
+	if (gather_off == (size_t)-1 && !narrow && p.M <= 8 && p.splitk > 1 && g_allow_words &&
+		(int)(grid.x * grid.y) <= sm_count() * (kw == 2 ? 2 : 1) && ws_bytes >= words_offset(need) + words_bytes(p.M, need))
+		p.ws_words = reinterpret_cast<unsigned long long *>(reinterpret_cast<unsigned char *>(workspace) + words_offset(need));
 	if (p.perm) {
 		// act-order: x[:, perm] once, into the workspace behind the partial sums (or at the offset the caller planned)
-		const size_t off = (gather_off != (size_t)-1) ? gather_off : gather_offset(need);
+		const size_t off = (gather_off != (size_t)-1) ? gather_off : gather_offset(words_offset(need) + words_bytes(p.M, need));
 		if (ws_bytes < off + gather_bytes(p.M, p.K)) return GPTQ_ERR_WORKSPACE;
 		__half *xp = reinterpret_cast<__half *>(reinterpret_cast<unsigned char *>(workspace) + off);
 		const dim3 gg((unsigned)((p.K / 8 + 255) / 256), (unsigned)p.M, 1);
@@ -436,6 +444,7 @@ void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
 void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 void gptq_debug_allow_narrow(int on) { g_allow_narrow = on ? 1 : 0; }
+void gptq_debug_allow_words(int on) { g_allow_words = on ? 1 : 0; }
 void gptq_debug_use_tc(int on) { g_use_tc = on ? 1 : 0; }
 void gptq_debug_attn_splits(int n) { g_attn_splits = n; }
 // Host-only: the launch plan of the decode kernel for a shape.  out[0..7] = split-K, K-warps, ring stages,
@@ -463,7 +472,8 @@ void gptq_debug_set_timing(long long *buf) { g_dbg = buf; }
 
 size_t gptq_workspace_bytes(int M, int K, int N) {
 	if (M <= 0 || N <= 0) return SK_TICKET_BYTES;
-	return std::max(gather_offset(skinny_ws_bytes(M, N, 2)) + gather_bytes(M, std::max(K, 0)), tc_ws_bytes(M, N));
+	const size_t base = skinny_ws_bytes(M, N, 2);
+	return std::max(gather_offset(words_offset(base) + words_bytes(M, base)) + gather_bytes(M, std::max(K, 0)), tc_ws_bytes(M, N));
 }
 
 struct ArArgs {

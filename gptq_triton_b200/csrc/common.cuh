@@ -120,6 +120,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 	return ok;
 }
 
+// Upper half of the 8-byte {value, tag} words that carry partial sums between CTAs without a fence or a
+// counter: a quiet-NaN bit pattern, so that a stale fp32 value in the same memory can never look like it.
+constexpr unsigned WORD_TAG = 0x7FC0DE01u;
+
 __device__ __forceinline__ unsigned long long global_timer_ns() {
 	unsigned long long t;
 	asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

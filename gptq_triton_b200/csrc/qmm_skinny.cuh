@@ -63,6 +63,12 @@ struct SkinnyParams {
 	int strip_groups;      // capacity (groups) of the zero / scale strips per stream
 	float *ws_partial;
 	int *ws_ticket;
+	// Split-K exchange without a ticket (M <= 8, all CTAs of the launch co-resident): every split but the
+	// last writes its partial sums as 8-byte words {value, tag} (the store carries its own flag: no fence, no
+	// counter; the tag is a NaN bit pattern, which no partial sum left in the workspace by another kernel
+	// can show in that half of a word); the CTA of the LAST split polls for them, adds them in split order
+	// and zeroes the words again, so the area is clean for the next launch.
+	unsigned long long *ws_words;      // nullptr: ticket protocol
 	// EPI_PLAIN / EPI_SILU
 	const __half *bias;
 	const __half *residual;
@@ -660,10 +666,14 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 				}
 				v -= corr;
 			}
-			if (p.splitk == 1)
+			if (p.splitk == 1 || (p.ws_words && split == p.splitk - 1)) {
 				red[((size_t)s * ROWS + row) * BN + col] = v;
-			else
+			} else if (p.ws_words) {
+				const unsigned long long w = ((unsigned long long)WORD_TAG << 32) | (unsigned long long)__float_as_uint(v);
+				asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.ws_words + (size_t)(tile * p.splitk + split) * nelem + e), "l"(w) : "memory");
+			} else {
 				__stcg(wsp + e, v);
+			}
 		}
 	} else
 	{
@@ -707,7 +717,46 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			}
 		}
 	}
-	if (p.splitk > 1) {
+	if (M8 && p.splitk > 1 && p.ws_words) {
+		if (split != p.splitk - 1) {                         // partial sums are on their way: done
+			GPTQ_TRACE_END(p.trace);
+			return;
+		}
+		SK_STAMP(4);
+		unsigned long long *wt = p.ws_words + (size_t)tile * p.splitk * nelem;
+		const unsigned long long t0 = global_timer_ns();
+		bool ok = true;
+#pragma unroll 1
+		for (int e = tid; e < nelem; e += NT) {              // same thread -> element mapping as above and below
+			const int s = (NSTREAM == 2 && e >= p.M * BN) ? 1 : 0, rc = e - s * (p.M * BN);
+			float *own = red + ((size_t)s * ROWS + (rc >> BSH)) * BN + (rc & (BN - 1));
+			float v = 0.f;
+#pragma unroll 1
+			for (int k0 = 0; k0 < p.splitk - 1; k0 += 8) {
+				unsigned long long w[8];
+#pragma unroll
+				for (int k = 0; k < 8; ++k)
+					if (k0 + k < p.splitk - 1) asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[k]) : "l"(wt + (size_t)(k0 + k) * nelem + e) : "memory");
+#pragma unroll
+				for (int k = 0; k < 8; ++k) {
+					if (k0 + k < p.splitk - 1) {
+						unsigned long long *src = wt + (size_t)(k0 + k) * nelem + e;
+						while ((unsigned)(w[k] >> 32) != WORD_TAG) {   // not there yet: poll this word (bounded in time)
+							if (global_timer_ns() - t0 > 2000000000ull) {
+								ok = false;
+								break;
+							}
+							asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[k]) : "l"(src) : "memory");
+						}
+						v += __uint_as_float((unsigned)w[k]);        // split order: 0, 1, ..., then this CTA's own share
+						asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(src), "l"(0ull) : "memory");
+					}
+				}
+			}
+			*own = v + *own;
+		}
+		if (!ok) atomicExch(p.ws_ticket + SK_STATUS_SLOT, 6);      // a split never delivered its partial sums
+	} else if (p.splitk > 1) {
 		__threadfence();
 		__syncthreads();
 		if (tid == 0) {
