@@ -202,8 +202,13 @@ class DecodeEngine:
 		self.ar_o = self.ar_down = None
 		if self.tp_world > 1 and batch <= 16 and cfg.hidden_size % 128 == 0 and os.environ.get('GPTQ_B200_TP_FUSED', '1') != '0':
 			from .tp import PeerExchange
-			self.ar_o = PeerExchange(cfg.hidden_size, self.tp_rank, self.tp_world, tp_group)
-			self.ar_down = PeerExchange(cfg.hidden_size, self.tp_rank, self.tp_world, tp_group)
+			try:          # collective: fails on every rank or on none
+				self.ar_o = PeerExchange(cfg.hidden_size, self.tp_rank, self.tp_world, tp_group)
+				self.ar_down = PeerExchange(cfg.hidden_size, self.tp_rank, self.tp_world, tp_group)
+			except RuntimeError:
+				if self.ar_o is not None:
+					self.ar_o.close()
+				self.ar_o = self.ar_down = None          # NCCL all-reduce instead
 		self.use_graph = use_graph
 		# RMSNorm folded into the decode kernels: o_proj / down_proj leave per-tile sums of squares of
 		# the hidden state, the next QKV / gate-up kernel scales x while staging it (one GPU only)

@@ -110,35 +110,50 @@ class PeerExchange:
 	group and map each other's buffers.  `partials` / `flags` are the pointer arrays the C ABI takes."""
 
 	def __init__(self, n_out: int, rank: int, world: int, group=None):
+		"""Collective: every rank of `group` must call it.  A failure on any rank (allocation, IPC export or
+		open) makes EVERY rank raise RuntimeError after the collectives have completed, so the callers can
+		fall back together (to NCCL) without leaving a rank behind in a collective."""
 		import ctypes
 		import torch.distributed as dist
 		from . import _lib
 		L = _lib.lib()
 		self.rank, self.world = rank, world
+		self._opened = []
+		self._own = None
 		self.flag_bytes = int(L.gptq_ar_flag_bytes(n_out))
 		self.bytes = self.flag_bytes + int(L.gptq_ar_partial_bytes(n_out))
-		own = ctypes.c_void_p()
-		_lib.check(L.gptq_peer_alloc(self.bytes, ctypes.byref(own)), 'gptq_peer_alloc')
-		self._own = own
 		handle = (ctypes.c_ubyte * 64)()
-		_lib.check(L.gptq_peer_export(own, handle), 'gptq_peer_export')
-		handles = [None] * world
-		dist.all_gather_object(handles, bytes(handle), group=group)
+		own = ctypes.c_void_p()
+		ok = world <= 8
+		if ok and L.gptq_peer_alloc(self.bytes, ctypes.byref(own)) == 0:
+			self._own = own
+			ok = L.gptq_peer_export(own, handle) == 0
+		else:
+			ok = False
+		gathered = [None] * world
+		dist.all_gather_object(gathered, (bool(ok), bytes(handle)), group=group)
+		ok = all(g[0] for g in gathered)
 		base = []
-		self._opened = []
-		for r in range(world):
-			if r == rank:
-				base.append(own.value)
-				continue
-			buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
-			ptr = ctypes.c_void_p()
-			_lib.check(L.gptq_peer_open(buf, ctypes.byref(ptr)), 'gptq_peer_open')
-			self._opened.append(ptr)
-			base.append(ptr.value)
-		# layout of a buffer: [arrival counters][partial sums]
+		if ok:
+			for r in range(world):
+				if r == rank:
+					base.append(own.value)
+					continue
+				buf = (ctypes.c_ubyte * 64).from_buffer_copy(gathered[r][1])
+				ptr = ctypes.c_void_p()
+				if L.gptq_peer_open(buf, ctypes.byref(ptr)) != 0:
+					ok = False
+					break
+				self._opened.append(ptr)
+				base.append(ptr.value)
+		verdict = [None] * world
+		dist.all_gather_object(verdict, bool(ok), group=group)      # also: every rank has mapped every buffer before the first launch
+		if not all(verdict):
+			self.close()
+			raise RuntimeError('peer exchange buffers could not be set up on every rank')
+		# layout of a buffer: [sequence numbers][receive area]
 		self.flags = (ctypes.c_void_p * 8)(*([b for b in base] + [None] * (8 - world)))
 		self.partials = (ctypes.c_void_p * 8)(*([b + self.flag_bytes for b in base] + [None] * (8 - world)))
-		dist.barrier(group=group)          # every rank has mapped every buffer before the first launch
 
 	def close(self):
 		from . import _lib
