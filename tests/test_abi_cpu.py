@@ -58,6 +58,29 @@ def test_argument_errors_before_any_launch(lib):
 	assert lib.gptq_qmatmul(*args(gs=0)) == -1
 
 
+def test_extension_entry_points_validate_on_the_host(lib):
+	"""The entry points without a reference counterpart (folded RMSNorm, fused tensor-parallel all-reduce)
+	reject bad arguments before anything touches the GPU; their sizing helpers are pure host code."""
+	fake = ctypes.c_void_p(0x1000)
+	base = (fake, fake, fake, fake, None, None, None, None, 0, fake, 1, 256, 256, 128, 256, 256, None, 0, None)
+	assert lib.gptq_qmatmul_sumsq(*base, None) == -1                      # the extra output is required
+	ptrs = (ctypes.c_void_p * 8)(*([0x2000] * 2 + [None] * 6))
+	assert lib.gptq_qmatmul_ar(*base, None, 1, 0, ptrs, ptrs) == -1       # a world of one has nothing to exchange
+	assert lib.gptq_qmatmul_ar(*base, None, 2, 2, ptrs, ptrs) == -1       # rank outside the world
+	assert lib.gptq_qmatmul_ar(*base, None, 9, 0, ptrs, ptrs) == -1       # more than eight ranks
+	assert lib.gptq_qmatmul_ar(*base, None, 2, 0, None, ptrs) == -1
+	wide = tuple(base[:10]) + (32,) + tuple(base[11:])                     # M = 32: no decode kernel, no fused exchange
+	assert lib.gptq_qmatmul_ar(*wide, None, 2, 0, ptrs, ptrs) == -6
+	gu = (fake, fake, fake, fake, fake, fake, fake, None, None, fake, 1, 256, 256, 128, 256, 256, None, 0, None)
+	assert lib.gptq_gateup_silu_rms(*gu, None, None, 0, 1e-6) == -1      # norm weight required
+	assert lib.gptq_gateup_silu_rms(*gu, fake, None, 8, 1e-6) == -1      # ... and the sums of squares
+	assert lib.gptq_gateup_silu_rms(*gu, fake, fake, 300, 1e-6) == -6    # more partial sums than the kernel folds
+	assert lib.gptq_ar_partial_bytes(4096) == 8 * 32 * 16 * 128 * 8
+	assert lib.gptq_ar_flag_bytes(4096) % 256 == 0 and lib.gptq_ar_flag_bytes(4096) >= 32 * 4
+	assert lib.gptq_peer_alloc(0, None) == -1 and lib.gptq_peer_export(None, None) == -1 and lib.gptq_peer_open(None, None) == -1
+	assert lib.gptq_peer_free(None) == 0 and lib.gptq_peer_close(None) == 0
+
+
 def test_python_ops_refuse_cpu_tensors():
 	import torch
 	import gptq_triton_b200 as g
