@@ -1,7 +1,7 @@
 // Single-query (decode) attention over a static fp16 KV cache: softmax(q·K^T / sqrt(d)) · V
 // for one new token per sequence.  HBM-bound: K and V of every cached position are read once.
 //
-// Grid (splits, heads, batch).  A CTA of 4 warps takes a contiguous range of cache positions and
+// Grid (splits, heads, batch).  A CTA of 8 warps takes a contiguous range of cache positions and
 // pulls it into shared memory with bulk asynchronous copies (64 keys of K and of V per stage,
 // three stages, mbarrier completion).  The copies are issued BEFORE the kernel waits for its
 // predecessor in the stream: old cache rows do not depend on it, so the cache streams in while
@@ -18,7 +18,8 @@
 namespace gptq {
 
 constexpr int AT_D = 128;              // head dim
-constexpr int AT_THREADS = 128;
+constexpr int AT_THREADS = 256;         // 8 warps = 32 key groups of 8 lanes
+constexpr int AT_GROUPS = AT_THREADS / 8;
 constexpr int AT_MAX_SPLITS = 32;
 constexpr int AT_TICKET_BYTES = 16384;
 constexpr int AT_STATUS_SLOT = AT_TICKET_BYTES / 4 - 1;      // same word as the matmul kernels' status
@@ -56,7 +57,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int grp = lane >> 3, sub = lane & 7;           // 4 key groups per warp, 8 lanes per key
-	const int g16 = warp * 4 + grp;
+	const int g16 = warp * 4 + grp;                      // key group 0..31
 	GPTQ_TRACE_BEGIN(p.trace);
 	pdl_trigger();
 	// positions beyond the cache are never read: the length is clamped to the rows a head owns
@@ -67,7 +68,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	const __half *kbase = p.kc + (size_t)b * p.kv_stride_b + (size_t)head * p.kv_stride_h;
 	const __half *vbase = p.vc + (size_t)b * p.kv_stride_b + (size_t)head * p.kv_stride_h;
 
-	__shared__ float s_m[16], s_l[16], s_acc[16][AT_D];
+	__shared__ float s_m[AT_GROUPS], s_l[AT_GROUPS];
+	float(*s_acc)[AT_D] = reinterpret_cast<float(*)[AT_D]>(at_smem);      // [AT_GROUPS][128], over the drained stages
 	__shared__ int s_last;
 	const uint32_t bar0 = smem_u32(at_smem + AT_STAGES * AT_STAGE_BYTES);
 	if (tid == 0) {
@@ -86,6 +88,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	if (tid == 0)
 		for (int c = 0; c < min(nchunks, AT_STAGES); ++c) issue(c);
 	pdl_wait();                                          // q and the newest cache rows come from earlier kernels
+	GPTQ_TRACE_STAMP(p.trace, 0);
 
 	// this lane's 16 query dims (sub*8 .. +7 and 64 + sub*8 .. +7), pre-scaled
 	float qf[16];
@@ -103,12 +106,13 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		}
 	}
 	const int fresh_lo = len - AT_FRESH;
+	GPTQ_TRACE_STAMP(p.trace, 1);
 
 	float m = -INFINITY, l = 0.f, acc[16];
 #pragma unroll
 	for (int i = 0; i < 16; ++i) acc[i] = 0.f;
 
-	constexpr int KPG = AT_CHUNK / 16;       // keys per 8-lane group and chunk
+	constexpr int KPG = AT_CHUNK / AT_GROUPS;       // keys per 8-lane group and chunk
 	bool failed = false;
 #pragma unroll 1
 	for (int c = 0; c < nchunks; ++c) {
@@ -123,7 +127,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		uint4 kr[KPG][2], vr[KPG][2];
 #pragma unroll
 		for (int u = 0; u < KPG; ++u) {
-			const int kk = g16 + 16 * u, key = key0 + kk;
+			const int kk = g16 + AT_GROUPS * u, key = key0 + kk;
 			if (kk < n) {
 				const bool fresh = key >= fresh_lo;
 				const __half *kp = fresh ? kbase + (size_t)key * AT_D : reinterpret_cast<const __half *>(sK) + kk * AT_D;
@@ -136,7 +140,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		}
 #pragma unroll
 		for (int u = 0; u < KPG; ++u) {
-			const bool valid = g16 + 16 * u < n;          // uniform within an 8-lane group
+			const bool valid = g16 + AT_GROUPS * u < n;          // uniform within an 8-lane group
 			float s = 0.f;
 			if (valid) {
 				const __half2 *h0 = reinterpret_cast<const __half2 *>(&kr[u][0]), *h1 = reinterpret_cast<const __half2 *>(&kr[u][1]);
@@ -176,7 +180,9 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	}
 	if (failed && tid == 0 && p.ws_ticket) atomicExch(p.ws_ticket + AT_STATUS_SLOT, 1);      // a bulk copy never completed
 
-	// ---- merge the 16 groups of the CTA (fixed order) -------------------------------------------
+	GPTQ_TRACE_STAMP(p.trace, 2);
+	// ---- merge the key groups of the CTA (fixed order) --------------------------------------------
+	__syncthreads();                                     // every warp is done with the staged rows: the region becomes s_acc
 	if (sub == 0) {
 		s_m[g16] = m;
 		s_l[g16] = l;
@@ -189,23 +195,25 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	__syncthreads();
 	float M = -INFINITY;
 #pragma unroll
-	for (int g = 0; g < 16; ++g) M = fmaxf(M, s_m[g]);
-	float L = 0.f, o = 0.f;            // thread tid owns output dim tid
+	for (int g = 0; g < AT_GROUPS; ++g) M = fmaxf(M, s_m[g]);
+	float L = 0.f, o = 0.f;            // thread tid < 128 owns output dim tid
+	const int dim = tid & (AT_D - 1);
 #pragma unroll 4
-	for (int g = 0; g < 16; ++g) {
+	for (int g = 0; g < AT_GROUPS; ++g) {
 		const float w = (s_m[g] == -INFINITY) ? 0.f : __expf(s_m[g] - M);
 		L = fmaf(s_l[g], w, L);
-		o = fmaf(s_acc[g][tid], w, o);
+		o = fmaf(s_acc[g][dim], w, o);
 	}
+	const bool writer = tid < AT_D;
 
 	const int bh = b * p.heads + head;
 	if (p.splits == 1) {
-		p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(o / L);
+		if (writer) p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(o / L);
 		GPTQ_TRACE_END(p.trace);
 		return;
 	}
 	float *wp = p.ws_partial + ((size_t)bh * p.splits + split) * 130;
-	__stcg(wp + 2 + tid, o);
+	if (writer) __stcg(wp + 2 + tid, o);
 	if (tid == 0) {
 		__stcg(wp, M);
 		__stcg(wp + 1, L);
@@ -223,20 +231,45 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		GPTQ_TRACE_END(p.trace);
 		return;
 	}
+	GPTQ_TRACE_STAMP(p.trace, 4);
 	__threadfence();
 	const float *wb = p.ws_partial + (size_t)bh * p.splits * 130;
-	float Mg = -INFINITY;
-#pragma unroll 4
-	for (int s = 0; s < p.splits; ++s) Mg = fmaxf(Mg, __ldcg(wb + s * 130));
-	float Lg = 0.f, og = 0.f;
-#pragma unroll 2
-	for (int s = 0; s < p.splits; ++s) {
-		const float ms = __ldcg(wb + s * 130);
-		const float w = (ms == -INFINITY) ? 0.f : __expf(ms - Mg);
-		Lg = fmaf(__ldcg(wb + s * 130 + 1), w, Lg);
-		og = fmaf(__ldcg(wb + s * 130 + 2 + tid), w, og);
+	if (writer) {
+		// all partials of a batch of splits are requested at once, then folded into the running
+		// (max, sum, output) in split order
+		float Mg = -INFINITY, Lg = 0.f, og = 0.f;
+		constexpr int MB = 12;
+#pragma unroll 1
+		for (int s0 = 0; s0 < p.splits; s0 += MB) {
+			float ms[MB], ls[MB], os[MB];
+#pragma unroll
+			for (int j = 0; j < MB; ++j) {
+				if (s0 + j < p.splits) {
+					const float *src = wb + (size_t)(s0 + j) * 130;
+					ms[j] = __ldcg(src);
+					ls[j] = __ldcg(src + 1);
+					os[j] = __ldcg(src + 2 + tid);
+				}
+			}
+			float bm = Mg;
+#pragma unroll
+			for (int j = 0; j < MB; ++j)
+				if (s0 + j < p.splits) bm = fmaxf(bm, ms[j]);
+			const float keep = (Mg == -INFINITY) ? 0.f : __expf(Mg - bm);
+			Lg *= keep;
+			og *= keep;
+#pragma unroll
+			for (int j = 0; j < MB; ++j) {
+				if (s0 + j < p.splits) {
+					const float w = (ms[j] == -INFINITY) ? 0.f : __expf(ms[j] - bm);
+					Lg = fmaf(ls[j], w, Lg);
+					og = fmaf(os[j], w, og);
+				}
+			}
+			Mg = bm;
+		}
+		p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(og / Lg);
 	}
-	p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(og / Lg);
 	GPTQ_TRACE_END(p.trace);
 }
 
