@@ -218,10 +218,14 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		__stcg(wp, M);
 		__stcg(wp + 1, L);
 	}
-	__threadfence();
+	// The ticket is an acquire-release read-modify-write at GPU scope after a CTA barrier: the partial
+	// sums that this CTA's threads stored before the barrier are released with it, and the partials of
+	// the CTAs that took a ticket earlier are acquired by it (and, through the next barrier, by every
+	// thread of this CTA).  No separate fences.
 	__syncthreads();
 	if (tid == 0) {
-		const int t = atomicAdd(p.ws_ticket + bh, 1);
+		int t;
+		asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(t) : "l"(p.ws_ticket + bh) : "memory");
 		const int last = (t == p.splits - 1);
 		if (last) p.ws_ticket[bh] = 0;
 		s_last = last;
@@ -232,7 +236,6 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		return;
 	}
 	GPTQ_TRACE_STAMP(p.trace, 4);
-	__threadfence();
 	const float *wb = p.ws_partial + (size_t)bh * p.splits * 130;
 	if (writer) {
 		// all partials of a batch of splits are requested at once, then folded into the running
