@@ -757,10 +757,12 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 		}
 		if (!ok) atomicExch(p.ws_ticket + SK_STATUS_SLOT, 6);      // a split never delivered its partial sums
 	} else if (p.splitk > 1) {
-		__threadfence();
+		// the ticket is an acquire-release atomic at GPU scope after the CTA barrier: it releases the partial
+		// sums this CTA stored and acquires those of the CTAs that arrived earlier (no separate fences)
 		__syncthreads();
 		if (tid == 0) {
-			const int t = atomicAdd(p.ws_ticket + tile, 1);
+			int t;
+			asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(t) : "l"(p.ws_ticket + tile) : "memory");
 			const int last = (t == p.splitk - 1);
 			if (last) p.ws_ticket[tile] = 0;        // leave the counter ready for the next launch
 			s_last = last;
@@ -771,7 +773,6 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			GPTQ_TRACE_END(p.trace);
 			return;
 		}
-		__threadfence();
 		const float *wt = p.ws_partial + (size_t)tile * p.splitk * nelem;
 		if (M8) {
 #pragma unroll 1
