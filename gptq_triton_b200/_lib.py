@@ -51,14 +51,13 @@ _SIGNATURES = {
 	'gptq_rmsnorm': (c_int, [_P, c_int64, _P, _P, c_int64, c_int, c_int, ctypes.c_float, _P]),
 	'gptq_qmatmul_noalloc': (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P]),
 	'gptq_noalloc_scratch_bytes': (c_size_t, [c_int, c_int, c_int, c_int]),
+	'gptq_noalloc_status': (c_int, [c_int]),
 }
 # Entry points outside the header's stable surface (tuning hooks); bound when present.
 _OPTIONAL = {
 	'gptq_debug_force_splitk': (None, [c_int]),
-	'gptq_debug_force_kw': (None, [c_int]),
 	'gptq_debug_set_pdl': (None, [c_int]),
 	'gptq_debug_allow_narrow': (None, [c_int]),
-	'gptq_debug_allow_words': (None, [c_int]),
 	'gptq_debug_tc_force': (None, [c_int]),
 }
 

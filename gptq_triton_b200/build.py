@@ -35,7 +35,7 @@ def up_to_date() -> bool:
 	if not LIB.exists():
 		return False
 	t = LIB.stat().st_mtime
-	deps = list(CSRC.glob('*.cu')) + list(CSRC.glob('*.cuh')) + list((PKG.parent / 'include').glob('*.h'))
+	deps = list(CSRC.glob('*.cu')) + list(CSRC.glob('*.cuh')) + list(CSRC.glob('*.inl')) + list((PKG.parent / 'include').glob('*.h'))
 	return all(d.stat().st_mtime <= t for d in deps)
 
 

@@ -16,22 +16,7 @@ namespace gptq {
 thread_local int g_last_cuda_error = 0;
 
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
-static int g_force_kw = 2;
-static int g_attn_splits = 0;     // tuning hook: 0 = heuristic
-static int g_use_tc = 1;          // tensor-core kernel for M > 16
 static int g_pdl = 1;             // programmatic dependent launch for the decode-step kernels (+3 % on the decode step)
-#ifdef GPTQ_TRACE
-static TraceSlot *g_trace = nullptr;      // [4096] slots in device memory, handed in by the debug script
-static int g_trace_n = 0;
-static TraceSlot *trace_slot(int kind) {
-	if (!g_trace || g_trace_n >= 4096) return nullptr;
-	(void)kind;
-	return g_trace + g_trace_n++;
-}
-#endif
-#ifdef GPTQ_SK_TIMING
-static long long *g_dbg = nullptr;
-#endif
 
 static int sm_count() {
 	static int cached[64] = {0};
@@ -225,7 +210,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 	}
 	if (g_force_splitk > 0) {
 		best_sk = std::min(g_force_splitk, p.total_chunks);
-		best_kw = p.spg < 4 ? 2 : g_force_kw;
+		best_kw = 2;
 		best_stage = 4;
 		int cps, eff, a, b, c;
 		const size_t cap = best_kw == 2 ? (size_t)113 * 1024 : (size_t)SK_SMEM_LIMIT - 2048;
@@ -244,7 +229,6 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 
 // Narrow geometry (one 32-column strip and the whole of K per CTA, no split-K): worth it when
 // N / 32 CTAs fill most of the chip in one wave and the x rows of the whole K fit in shared memory.
-static int g_allow_words = 1;       // ticket-free split-K exchange (gptq_debug_allow_words)
 static int g_allow_narrow = 0;      // opt-in (gptq_debug_allow_narrow): measured slower than the tiled split-K form
 static bool plan_narrow(SkinnyParams &p, dim3 &grid, size_t &smem) {
 	if (!g_allow_narrow || g_force_splitk > 0) return false;
@@ -319,7 +303,7 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 	const size_t need = skinny_ws_bytes(p.M, p.N, NSTREAM);
 	if (workspace == nullptr || ws_bytes < need) return GPTQ_ERR_WORKSPACE;
 	// ticket-free split-K exchange: M <= 8, one wave of co-resident CTAs (the polling CTA is the last one dispatched)
-	if (gather_off == (size_t)-1 && !narrow && p.M <= 8 && p.splitk > 1 && g_allow_words &&
+	if (gather_off == (size_t)-1 && !narrow && p.M <= 8 && p.splitk > 1 &&
 		(int)(grid.x * grid.y) <= sm_count() * (kw == 2 ? 2 : 1) && ws_bytes >= words_offset(need) + words_bytes(p.M, need))
 		p.ws_words = reinterpret_cast<unsigned long long *>(reinterpret_cast<unsigned char *>(workspace) + words_offset(need));
 	if (p.perm) {
@@ -333,14 +317,6 @@ static int launch_skinny(SkinnyParams &p, const int32_t *qw0, const int32_t *qw1
 		p.ldx = p.K;
 		p.perm = nullptr;
 	}
-#ifdef GPTQ_TRACE
-	p.trace = trace_slot(EPI);
-#endif
-#ifdef GPTQ_SK_TIMING
-	p.dbg = g_dbg;
-	p.raw0 = qw0;
-	p.raw1 = qw1 ? qw1 : qw0;
-#endif
 	p.ws_ticket = reinterpret_cast<int *>(workspace);
 	p.ws_partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + SK_TICKET_BYTES);
 	alignas(64) CUtensorMap tm0, tm1;
@@ -441,35 +417,8 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 
 // Tuning / test hook: force the split-K factor of the decode kernel (0 restores the heuristic).
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
-void gptq_debug_force_kw(int kw) { g_force_kw = (kw == 4) ? 4 : 2; }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 void gptq_debug_allow_narrow(int on) { g_allow_narrow = on ? 1 : 0; }
-void gptq_debug_allow_words(int on) { g_allow_words = on ? 1 : 0; }
-void gptq_debug_use_tc(int on) { g_use_tc = on ? 1 : 0; }
-void gptq_debug_attn_splits(int n) { g_attn_splits = n; }
-// Host-only: the launch plan of the decode kernel for a shape.  out[0..7] = split-K, K-warps, ring stages,
-// dynamic shared memory bytes, x-slice bytes, strip groups, chunks per split, 0.
-int gptq_debug_plan(int M, int K, int N, int groupsize, int nstream, int *out) {
-	if (groupsize == -1) groupsize = K;
-	if (M <= 0 || M > 16 || !skinny_shape_ok(K, N, groupsize, nullptr)) return GPTQ_ERR_UNSUPPORTED;
-	SkinnyParams p = {};
-	p.M = M; p.K = K; p.N = N; p.groupsize = groupsize;
-	dim3 grid;
-	size_t smem;
-	int kw;
-	plan_skinny(p, nstream, kw, grid, smem);
-	out[0] = p.splitk; out[1] = kw; out[2] = p.nstage; out[3] = (int)smem; out[4] = p.xs_bytes; out[5] = p.strip_groups;
-	out[6] = p.chunks_per_split; out[7] = 0;
-	return GPTQ_OK;
-}
-#ifdef GPTQ_TRACE
-// buf: 4096 slots of 4 x u64, begin preset to ~0 and end to 0 by the caller; returns the slots handed out so far
-int gptq_debug_trace(void *buf) { g_trace = reinterpret_cast<TraceSlot *>(buf); const int n = g_trace_n; g_trace_n = 0; return n; }
-#endif
-#ifdef GPTQ_SK_TIMING
-void gptq_debug_set_timing(long long *buf) { g_dbg = buf; }
-#endif
-
 size_t gptq_workspace_bytes(int M, int K, int N) {
 	if (M <= 0 || N <= 0) return SK_TICKET_BYTES;
 	const size_t base = skinny_ws_bytes(M, N, 2);
@@ -519,7 +468,7 @@ static int qmatmul_impl(const void *x, const int32_t *qweight, const int32_t *qz
 		}
 		return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, workspace, workspace_bytes, st);
 	}
-	if (fast && !perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
+	if (fast && !perm && tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};
 		a.x = (const __half *)x; a.ldx = ldx; a.qw0 = qweight; a.qz0 = qzeros; a.sc0 = (const __half *)scales;
 		a.perm = perm; a.M = M; a.K = K; a.N = N; a.groupsize = groupsize;
@@ -542,7 +491,7 @@ int gptq_qmatmul(const void *x, const int32_t *qweight, const int32_t *qzeros, c
 }
 
 // ---- tensor parallelism: row-parallel projection with the all-reduce in its epilogue ----------------------
-size_t gptq_ar_partial_bytes(int N) { return N <= 0 ? 0 : (size_t)8 * ((N + SK_BN - 1) / SK_BN) * 16 * SK_BN * sizeof(unsigned long long); }
+size_t gptq_ar_partial_bytes(int N) { return N <= 0 ? 0 : (size_t)2 * 8 * ((N + SK_BN - 1) / SK_BN) * 16 * SK_BN * sizeof(unsigned long long); }
 size_t gptq_ar_flag_bytes(int N) { return N <= 0 ? 0 : (((size_t)((N + SK_BN - 1) / SK_BN) * sizeof(unsigned)) + 255) & ~(size_t)255; }
 
 int gptq_qmatmul_ar(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const int32_t *g_idx,
@@ -580,7 +529,6 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 	if ((size_t)batch * heads * 4 > (size_t)AT_TICKET_BYTES - 8) return GPTQ_ERR_UNSUPPORTED;
 	// two CTAs (96 KB of staged cache rows each) fit an SM: one wave of at most 2 * SMs CTAs
 	int splits = std::max(1, 2 * sm_count() / (batch * heads));
-	if (g_attn_splits > 0) splits = g_attn_splits;
 	splits = std::max(1, std::min(splits, std::min(AT_MAX_SPLITS, (len_hint + 63) / 64)));
 	if (splits > 1 && (!workspace || workspace_bytes < gptq_attn_workspace_bytes(batch, heads))) return GPTQ_ERR_WORKSPACE;
 	AttnParams p = {};
@@ -591,9 +539,6 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 	p.scale = scale; p.heads = heads; p.splits = splits;
 	p.ws_ticket = reinterpret_cast<int *>(workspace);
 	p.ws_partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + AT_TICKET_BYTES);
-#ifdef GPTQ_TRACE
-	p.trace = trace_slot(3);
-#endif
 	{
 		static bool ready[64] = {false};
 		int dev = 0;
@@ -644,7 +589,8 @@ int gptq_qmatmul_noalloc(const void *x, const int32_t *qweight, const int32_t *q
 	cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 	// the arrival counters must start at zero; partial sums need no clearing (every slot that is
 	// read is written first by this launch)
-	cudaError_t e = cudaMemsetAsync(scratch, 0, SK_TICKET_BYTES, st);
+	// (the last word of the counter area is the status word: it is kept, gptq_noalloc_status reads it)
+	cudaError_t e = cudaMemsetAsync(scratch, 0, SK_TICKET_BYTES - 4, st);
 	if (e != cudaSuccess) return cuda_status(e);
 	SkinnyParams p = {};
 	p.x = (const __half *)x; p.ldx = ldx;
@@ -663,6 +609,17 @@ int gptq_qmatmul_noalloc(const void *x, const int32_t *qweight, const int32_t *q
 	plan_skinny(plan, 1, kw, grid, smem);
 	const size_t off = gather_offset(noalloc_need(plan));
 	return launch_skinny<1, EPI_PLAIN>(p, qweight, nullptr, scratch, std::max(skinny_ws_bytes(M, N, 1), off + gather_bytes(M, K)), st, off);
+}
+
+int gptq_noalloc_status(int clear) {
+	void *scratch = nullptr;
+	if (noalloc_scratch_ptr(&scratch) != GPTQ_OK) return GPTQ_ERR_CUDA;
+	int *word = reinterpret_cast<int *>(scratch) + SK_STATUS_SLOT;
+	int status = 0;
+	if (cudaDeviceSynchronize() != cudaSuccess) return GPTQ_ERR_CUDA;
+	if (cudaMemcpy(&status, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return GPTQ_ERR_CUDA;
+	if (clear && status != 0 && cudaMemset(word, 0, sizeof(int)) != cudaSuccess) return GPTQ_ERR_CUDA;
+	return status;
 }
 
 static int gateup_impl(const void *x, const int32_t *gate_qweight, const int32_t *gate_qzeros, const void *gate_scales,
@@ -691,7 +648,7 @@ static int gateup_impl(const void *x, const int32_t *gate_qweight, const int32_t
 		return launch_skinny<2, EPI_SILU>(p, gate_qweight, up_qweight, workspace, workspace_bytes, st);
 	}
 	if (rms_weight) return GPTQ_ERR_UNSUPPORTED;
-	if (fast && !perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
+	if (fast && !perm && tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};
 		a.x = (const __half *)x; a.ldx = ldx;
 		a.qw0 = gate_qweight; a.qz0 = gate_qzeros; a.sc0 = (const __half *)gate_scales;
@@ -743,7 +700,8 @@ static int qkv_rope_impl(const void *x, const int32_t *qweight, const int32_t *q
 	if (ldx % 8 != 0) return GPTQ_ERR_ALIGN;
 	if (!aligned16(x) || !aligned16(qweight) || !aligned16(qzeros) || !aligned16(scales)) return GPTQ_ERR_ALIGN;
 	if (g_idx) return GPTQ_ERR_UNSUPPORTED;       // act-order must be prepared with gptq_act_order_rows (perm)
-	if (!skinny_shape_ok(K, N, groupsize, nullptr) || (perm && !aligned16(perm))) return GPTQ_ERR_UNSUPPORTED;
+	if (perm && !aligned16(perm)) return GPTQ_ERR_UNSUPPORTED;
+	if (M <= 16 && !skinny_shape_ok(K, N, groupsize, nullptr)) return GPTQ_ERR_UNSUPPORTED;
 	if (int rc = check_rms(rms_weight, sumsq_in, sumsq_tiles, rms_eps, M, g_idx, perm)) return rc;
 	if (M == 0) return GPTQ_OK;
 	cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -760,7 +718,7 @@ static int qkv_rope_impl(const void *x, const int32_t *qweight, const int32_t *q
 		p.kv_sp = kv_stride_pos; p.tokens_per_batch = tokens_per_batch; p.hidden = hidden; p.max_pos = max_pos;
 		return launch_skinny<1, EPI_ROPE>(p, qweight, nullptr, workspace, workspace_bytes, st);
 	}
-	if (!perm && g_use_tc && tc_shape_ok(M, K, N, groupsize)) {
+	if (!perm && tc_shape_ok(M, K, N, groupsize)) {
 		TcArgs a = {};
 		a.x = (const __half *)x; a.ldx = ldx; a.qw0 = qweight; a.qz0 = qzeros; a.sc0 = (const __half *)scales;
 		a.perm = perm; a.M = M; a.K = K; a.N = N; a.groupsize = groupsize;

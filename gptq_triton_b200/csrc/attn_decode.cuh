@@ -41,9 +41,6 @@ struct AttnParams {
 	int heads, splits;
 	float *ws_partial;        // [b*heads][splits][130]
 	int *ws_ticket;           // [b*heads]
-#ifdef GPTQ_TRACE
-	TraceSlot *trace;
-#endif
 };
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -58,7 +55,6 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int grp = lane >> 3, sub = lane & 7;           // 4 key groups per warp, 8 lanes per key
 	const int g16 = warp * 4 + grp;                      // key group 0..31
-	GPTQ_TRACE_BEGIN(p.trace);
 	pdl_trigger();
 	// positions beyond the cache are never read: the length is clamped to the rows a head owns
 	const int len = max(1, min(p.pos[b] + 1, (int)(p.kv_stride_h / AT_D)));
@@ -88,7 +84,6 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	if (tid == 0)
 		for (int c = 0; c < min(nchunks, AT_STAGES); ++c) issue(c);
 	pdl_wait();                                          // q and the newest cache rows come from earlier kernels
-	GPTQ_TRACE_STAMP(p.trace, 0);
 
 	// this lane's 16 query dims (sub*8 .. +7 and 64 + sub*8 .. +7), pre-scaled
 	float qf[16];
@@ -106,7 +101,6 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		}
 	}
 	const int fresh_lo = len - AT_FRESH;
-	GPTQ_TRACE_STAMP(p.trace, 1);
 
 	float m = -INFINITY, l = 0.f, acc[16];
 #pragma unroll
@@ -180,7 +174,6 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	}
 	if (failed && tid == 0 && p.ws_ticket) atomicExch(p.ws_ticket + AT_STATUS_SLOT, 1);      // a bulk copy never completed
 
-	GPTQ_TRACE_STAMP(p.trace, 2);
 	// ---- merge the key groups of the CTA (fixed order) --------------------------------------------
 	__syncthreads();                                     // every warp is done with the staged rows: the region becomes s_acc
 	if (sub == 0) {
@@ -209,7 +202,6 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	const int bh = b * p.heads + head;
 	if (p.splits == 1) {
 		if (writer) p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(o / L);
-		GPTQ_TRACE_END(p.trace);
 		return;
 	}
 	float *wp = p.ws_partial + ((size_t)bh * p.splits + split) * 130;
@@ -232,10 +224,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 	}
 	__syncthreads();
 	if (!s_last) {
-		GPTQ_TRACE_END(p.trace);
 		return;
 	}
-	GPTQ_TRACE_STAMP(p.trace, 4);
 	const float *wb = p.ws_partial + (size_t)bh * p.splits * 130;
 	if (writer) {
 		// all partials of a batch of splits are requested at once, then folded into the running
@@ -273,7 +263,6 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const AttnParam
 		}
 		p.out[(size_t)b * p.out_stride_b + head * AT_D + tid] = __float2half_rn(og / Lg);
 	}
-	GPTQ_TRACE_END(p.trace);
 }
 
 // ---- RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, fp32 inside, one fp16 rounding ----------------

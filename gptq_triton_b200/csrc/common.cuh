@@ -155,34 +155,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int 
 		: "memory");
 }
 
-// Debug builds (-DGPTQ_TRACE): every launch gets a slot; each CTA folds its own begin / end
-// times (ns) into the slot's earliest begin and latest end.
-#ifdef GPTQ_TRACE
-struct TraceSlot { unsigned long long begin, end, stamp[6]; };      // stamp[i]: latest time any CTA reached phase i
-__device__ __forceinline__ void trace_begin(TraceSlot *t) {
-	if (t && threadIdx.x == 0) atomicMin(&t->begin, global_timer_ns());
-}
-__device__ __forceinline__ void trace_end(TraceSlot *t) {
-	if (t && threadIdx.x == 0) atomicMax(&t->end, global_timer_ns());
-}
-__device__ __forceinline__ void trace_stamp(TraceSlot *t, int i) {
-	if (t && threadIdx.x == 0) atomicMax(&t->stamp[i], global_timer_ns());
-}
-#define GPTQ_TRACE_BEGIN(t) trace_begin(t)
-#define GPTQ_TRACE_END(t) trace_end(t)
-#define GPTQ_TRACE_STAMP(t, i) trace_stamp(t, i)
-#else
-#define GPTQ_TRACE_BEGIN(t) \
-	do {                    \
-	} while (0)
-#define GPTQ_TRACE_END(t) \
-	do {                  \
-	} while (0)
-#define GPTQ_TRACE_STAMP(t, i) \
-	do {                       \
-	} while (0)
-#endif
-
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap) {
 	asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }

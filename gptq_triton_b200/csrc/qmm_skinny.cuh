@@ -90,7 +90,7 @@ struct SkinnyParams {
 	// fence and no separate signal is needed), then polls its OWN receive buffer until the words of every
 	// peer carry this launch's sequence number, and adds the tiles in rank order: the same bits on every rank.
 	int ar_world, ar_rank;
-	unsigned long long *ar_buf[8];     // receive buffer of every rank: [source rank][tile][16 rows][128] words
+	unsigned long long *ar_buf[8];     // receive buffer of every rank: [parity of the sequence number][source rank < 8][tile][16 rows][128] words
 	unsigned *ar_seq;                  // this rank's sequence number per tile (same on every rank: same launches)
 	// EPI_ROPE
 	const __half *cos_t, *sin_t;
@@ -98,29 +98,7 @@ struct SkinnyParams {
 	__half *q_out, *k_out, *v_out;
 	long long q_stride_m, kv_sb, kv_st, kv_sh, kv_sp;
 	int tokens_per_batch, hidden, max_pos;
-#ifdef GPTQ_TRACE
-	TraceSlot *trace;
-#endif
-#ifdef GPTQ_SK_TIMING
-	long long *dbg;        // [cta][8] phase timestamps (debug builds only)
-	const int32_t *raw0, *raw1;
-#endif
 };
-
-#ifdef GPTQ_SK_TIMING
-#define SK_STAMP(i)                                                                                         \
-	do {                                                                                                    \
-		if (p.dbg && threadIdx.x == 0) {                                                                    \
-			long long t_;                                                                                   \
-			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                          \
-			p.dbg[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = t_;                            \
-		}                                                                                                   \
-	} while (0)
-#else
-#define SK_STAMP(i) \
-	do {            \
-	} while (0)
-#endif
 
 // SPG_T: steps per group known at compile time (1 or 2), or 0 when a group spans whole chunks.
 // x is always read in order: for act-order weights the host gathers x[:, perm] once per call with
@@ -147,8 +125,6 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int wn = NARROW ? 0 : (warp & 3), kw = NARROW ? warp : (warp >> 2), gid = lane >> 2, tig = lane & 3;
 	const int tile = blockIdx.x, split = blockIdx.y;
-	SK_STAMP(0);
-	GPTQ_TRACE_BEGIN(p.trace);
 	const int n0 = tile * BN, n0w = n0 + wn * 32;
 	const bool warp_active = n0w < p.N;
 
@@ -190,18 +166,7 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			if (lane == 0) {
 				const uint32_t bar = bar_w + 8 * pr_stage;
 				mbar_arrive_expect_tx(bar, SK_CHUNK_BYTES);
-#ifdef GPTQ_SK_BULK1D
-				{
-					const unsigned char *src = reinterpret_cast<const unsigned char *>((NSTREAM == 2 && pr_stream) ? p.raw1 : p.raw0) +
-											   ((size_t)(tile * NWN + wn) * p.total_chunks + pr_chunk) * SK_CHUNK_BYTES;
-					asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-									 ring_w + pr_stage * SK_CHUNK_BYTES),
-								 "l"(src), "r"(SK_CHUNK_BYTES), "r"(bar)
-								 : "memory");
-				}
-#else
 				tma_load_2d(ring_w + pr_stage * SK_CHUNK_BYTES, (NSTREAM == 2 && pr_stream) ? &tm1 : &tm0, n0w, pr_chunk * 16, bar);
-#endif
 			}
 			++pr_j;
 			if (++pr_stage == p.nstage) pr_stage = 0;
@@ -338,7 +303,6 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			if (it == 0) {
 #pragma unroll 1
 				for (int s = 0; s < p.nstage; ++s) produce();    // weight prefetch: nstage chunks per warp
-				SK_STAMP(1);
 				pdl_wait();
 				if (!early && x_passes > 0) x_load(xr, xub, v0, wq);
 				if (rms) {
@@ -406,7 +370,6 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 		}
 	}
 	__syncthreads();
-	SK_STAMP(2);
 
 	// ---- main loop ---------------------------------------------------------------------
 	// acc[stream][batch block][column 0..3 of this lane][batch row 2*tig + {0,1}]
@@ -419,9 +382,6 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			for (int c = 0; c < 4; ++c) acc[s][b][c][0] = acc[s][b][c][1] = 0.f;
 
 	bool failed = false;
-#ifdef GPTQ_SK_TIMING
-	long long wait_cycles = 0, math_cycles = 0, tail_cycles = 0;
-#endif
 	if (nw > 0) {
 		const bool have_row0 = gid < p.M, have_row1 = gid + 8 < p.M;
 		// In step l of a chunk this lane works on packed row 2*tig + (l&1) + 8*(l>>1); the ring
@@ -479,10 +439,6 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 				uint4 xb0 = make_uint4(0u, 0u, 0u, 0u), xb1 = make_uint4(0u, 0u, 0u, 0u);
 				if (have_row0) xb0 = *reinterpret_cast<const uint4 *>(x0);
 				if (!M8 && have_row1) xb1 = *reinterpret_cast<const uint4 *>(x1);
-#ifdef GPTQ_SK_NOMATH
-				g[0][0][0] += __uint_as_float((q.x ^ q.y ^ q.z ^ q.w ^ xb0.x ^ xb1.x) & 0x3fffffu);
-				return;
-#endif
 				const uint32_t qv[4] = {q.x, q.y, q.z, q.w};
 				uint32_t a04[4], a15[4], a26[4], a37[4];
 #pragma unroll
@@ -510,13 +466,7 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			auto begin = [&]() -> bool {
 				if (!first) produce();
 				first = false;
-#ifdef GPTQ_SK_TIMING
-				const long long tw0 = clock64();
-#endif
 				const bool ok = mbar_wait_bounded(bar_w + 8 * stage, parity);
-#ifdef GPTQ_SK_TIMING
-				wait_cycles += clock64() - tw0;
-#endif
 				return ok;
 			};
 			auto end = [&]() {
@@ -619,13 +569,9 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			if (failed) break;
 		}
 	}
-#ifdef GPTQ_SK_TIMING
-	if (p.dbg && tid == 0) p.dbg[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + 7] = wait_cycles | (math_cycles << 20) | (tail_cycles << 40);
-#endif
 	if (failed && lane == 0) atomicExch(p.ws_ticket + SK_STATUS_SLOT, 1);          // a TMA load never completed
 	if (tid == 0 && (smem_u32(smem) & 1023u) != 0) atomicExch(p.ws_ticket + SK_STATUS_SLOT, 2);   // swizzle needs 1 KB alignment
 	__syncthreads();            // every warp is done with its ring: the region becomes `red`
-	SK_STAMP(3);
 
 	// ---- reduce the KW warp-rows ---------------------------------------------------------
 	// red[kw][stream][row][128]; this lane holds columns wn*32 + 4*gid + 0..3 of rows 2*tig + {0,1} (+8)
@@ -719,10 +665,8 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 	}
 	if (M8 && p.splitk > 1 && p.ws_words) {
 		if (split != p.splitk - 1) {                         // partial sums are on their way: done
-			GPTQ_TRACE_END(p.trace);
 			return;
 		}
-		SK_STAMP(4);
 		unsigned long long *wt = p.ws_words + (size_t)tile * p.splitk * nelem;
 		const unsigned long long t0 = global_timer_ns();
 		bool ok = true;
@@ -768,9 +712,7 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			s_last = last;
 		}
 		__syncthreads();
-		SK_STAMP(4);
 		if (!s_last) {
-			GPTQ_TRACE_END(p.trace);
 			return;
 		}
 		const float *wt = p.ws_partial + (size_t)tile * p.splitk * nelem;
@@ -818,7 +760,6 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 	const int epi_n = (EPI == EPI_ROPE) ? p.M * 64 : p.M * BN;
 	const int e_lo = 0, e_hi = epi_n;
 	const float *fin = red;
-	SK_STAMP(5);
 	// ---- epilogue from shared memory ---------------------------------------------------------
 	if (EPI == EPI_PLAIN || EPI == EPI_SILU) {
 		__shared__ float s_ss[64];                           // [row][quarter of the tile]
@@ -829,7 +770,12 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			if (tid == 0) s_seq = p.ar_seq[tile] + 1u;           // written by the previous launch on this buffer, long complete
 			__syncthreads();
 			const unsigned seq = s_seq;
-			const size_t slot = ((size_t)p.ar_rank * gridDim.x + tile) * (16 * BN);      // where this rank's words go in a peer's buffer
+			// The receive area is double-buffered by the parity of the sequence number: a rank that runs ahead
+			// into call n + 1 on the same buffers writes the other half, so a peer that is still reading the
+			// words of call n never sees them overwritten (call n + 2 cannot start before that peer has pushed
+			// its own words of call n + 1, i.e. after it has finished reading call n).
+			const size_t half = (size_t)(seq & 1u) * ((size_t)8 * gridDim.x * (16 * BN));
+			const size_t slot = half + ((size_t)p.ar_rank * gridDim.x + tile) * (16 * BN);      // where this rank's words go in a peer's buffer
 #pragma unroll 1
 			for (int e = e_lo + tid; e < e_hi; e += NT) {
 				const int n = n0 + (e & (BN - 1));
@@ -855,7 +801,7 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 						v += red[e];
 						continue;
 					}
-					const unsigned long long *src = p.ar_buf[p.ar_rank] + ((size_t)r * gridDim.x + tile) * (16 * BN) + e;
+					const unsigned long long *src = p.ar_buf[p.ar_rank] + half + ((size_t)r * gridDim.x + tile) * (16 * BN) + e;
 					unsigned long long w;
 #pragma unroll 1
 					for (;;) {
@@ -915,6 +861,7 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			if (pos < 0 || pos >= p.max_pos) {          // never index the tables / the cache out of range
 				atomicExch(p.ws_ticket + SK_STATUS_SLOT, 4);
 				pos = 0;
+				if (section != 0) continue;             // K / V of such a row are dropped, not written over cache row 0
 			}
 			float o1 = a, o2 = b;
 			if (section < 2) {
@@ -934,8 +881,6 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			dst[d + 64] = __float2half_rn(o2);
 		}
 	}
-	SK_STAMP(6);
-	GPTQ_TRACE_END(p.trace);
 }
 
 // ---- act-order gather: out[m][k] = x[m][perm[k]], 8 elements per thread -------------------

@@ -96,9 +96,6 @@ struct TcParams {
 	TcArgs a;
 	int epi;
 	int *status;
-#ifdef GPTQ_TC_TIMING
-	long long *dbg;
-#endif
 };
 
 }   // namespace
@@ -116,16 +113,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 namespace gptq {
 
 EncodeTiledFn tensor_map_encoder();      // defined in api.cu
-int g_tc_wide = 1, g_tc_tall = 1;      // tuning hooks: allow 256-column / 256-row tiles
-extern "C" void gptq_debug_tc_wide(int on) { g_tc_wide = on ? 1 : 0; }
-extern "C" void gptq_debug_tc_tall(int on) { g_tc_tall = on ? 1 : 0; }
 int g_tc_force = 0;                    // tests: 0 = choose by cost, 1 = 128 x 128, 2 = 128 x 256, 3 = 256 x 256 (256 x 128 for two streams), 4 = 256 x 128
 constexpr double TC_SPEED_256x128 = 1.6;
 extern "C" void gptq_debug_tc_force(int cfg) { g_tc_force = cfg; }
-#ifdef GPTQ_TC_TIMING
-long long *g_tc_dbg = nullptr;
-extern "C" void gptq_debug_set_tc_timing(long long *b) { g_tc_dbg = b; }
-#endif
 
 bool tc_shape_ok(int M, int K, int N, int groupsize) {
 	return M > 16 && N % TC_BN == 0 && K % TC_BK == 0 && groupsize % TC_BK == 0 && K % groupsize == 0;
@@ -202,9 +192,6 @@ int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaSt
 	p.a = a;
 	p.epi = epi;
 	p.status = reinterpret_cast<int *>(workspace) + (16384 / 4 - 1);
-#ifdef GPTQ_TC_TIMING
-	p.dbg = g_tc_dbg;
-#endif
 	// Tile choice: estimated time = waves * (rows * columns of a tile) / relative speed of the configuration
 	// (measured per busy SM: 128 x 128 tiles 1.0, 128 x 256 tiles 1.7, 256-row tiles 2.5).
 	int dev = 0, sms = 148;
@@ -216,12 +203,12 @@ int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaSt
 		return (double)waves * bm * bn / speed;
 	};
 	if (epi == TC_EPI_SILU) {
-		const bool tall = g_tc_force ? (g_tc_force >= 3) : (g_tc_tall && cost(256, 128, 1.5) < cost(128, 128, 1.0));
+		const bool tall = g_tc_force ? (g_tc_force >= 3) : (cost(256, 128, 1.5) < cost(128, 128, 1.0));
 		return tall ? tc_launch_inst<2, TC_EPI_SILU, 128, 2>(tmx, p, stream) : tc_launch_inst<2, TC_EPI_SILU, 128, 1>(tmx, p, stream);
 	}
 	// configurations: 0 = 128 x 128, 1 = 128 x 256, 2 = 256 x 256, 3 = 256 x 128
-	const double c[4] = {cost(128, 128, 1.0), g_tc_wide ? cost(128, 256, 1.7) : 1e30, g_tc_tall ? cost(256, 256, 2.5) : 1e30,
-						 g_tc_tall ? cost(256, 128, TC_SPEED_256x128) : 1e30};
+	const double c[4] = {cost(128, 128, 1.0), cost(128, 256, 1.7), cost(256, 256, 2.5),
+						 cost(256, 128, TC_SPEED_256x128)};
 	int pick = 0;
 	for (int i = 1; i < 4; ++i)
 		if (c[i] < c[pick]) pick = i;

@@ -97,17 +97,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 			for (int kb = 0; kb < nkb && !*s_abort; ++kb) {
 				const int s = kb % S;
 				const uint32_t ph = (kb / S) & 1;
-#ifdef GPTQ_TC_TIMING
-				const long long t0 = clock64();
-#endif
 				if (!mbar_wait_bounded(bar_full_a + 8 * s, ph, TC_SPIN)) { fail(); break; }
-#ifdef GPTQ_TC_TIMING
-				const long long t1 = clock64();
-#endif
 				if (!mbar_wait_bounded(bar_full_b + 8 * s, ph, TC_SPIN)) { fail(); break; }
-#ifdef GPTQ_TC_TIMING
-				if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) { atomicAdd((unsigned long long *)p.dbg + 0, (unsigned long long)(t1 - t0)); atomicAdd((unsigned long long *)p.dbg + 1, (unsigned long long)(clock64() - t1)); }
-#endif
 				tc_fence_after();
 #pragma unroll
 				for (int h = 0; h < MH; ++h) {
@@ -121,13 +112,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 									 (kb > 0 || k > 0) ? 1u : 0u);
 					}
 				}
-#ifdef GPTQ_TC_TIMING
-				const long long t5 = clock64();
-#endif
 				umma_commit(bar_empty + 8 * s);          // stage free once these MMAs have read it
-#ifdef GPTQ_TC_TIMING
-				if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) { p.dbg[6] += t5 - t1; p.dbg[7] += clock64() - t5; }
-#endif
 			}
 			umma_commit(bar_acc);                        // accumulators complete
 		}
@@ -177,13 +162,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 			}
 			{
 				const int ws = kb % PS;
-#ifdef GPTQ_TC_TIMING
-				const long long t0 = clock64();
-#endif
 				if (*s_abort || !mbar_wait_bounded(bar_full_w + 8 * ws, (kb / PS) & 1, TC_SPIN)) { ok = false; break; }
-#ifdef GPTQ_TC_TIMING
-				if (p.dbg && tid == 64 && blockIdx.x == 0 && blockIdx.y == 0) p.dbg[2] += clock64() - t0;
-#endif
 #pragma unroll
 				for (int u = 0; u < NU; ++u) {
 					const uint32_t *wp = reinterpret_cast<const uint32_t *>(sW + (ws * NSTREAM + u / CPT) * PW_BYTES) + wt + 128 * (u % CPT);
@@ -194,14 +173,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				if (lane == 0) mbar_arrive(bar_empty_w + 8 * ws);
 			}
 			const int s = kb % S;
-#ifdef GPTQ_TC_TIMING
-			const long long t2 = clock64();
-#endif
 			if (*s_abort || !mbar_wait_bounded(bar_empty + 8 * s, ((kb / S) & 1) ^ 1, TC_SPIN)) { ok = false; break; }
-#ifdef GPTQ_TC_TIMING
-			const long long t3 = clock64();
-			if (p.dbg && tid == 64 && blockIdx.x == 0 && blockIdx.y == 0) p.dbg[3] += t3 - t2;
-#endif
 #pragma unroll
 			for (int u = 0; u < NU; ++u) {
 				// row (wt + 128j) of the B tile: 8-row groups of 1024 bytes, 16 groups per 128 rows
@@ -221,14 +193,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 					*reinterpret_cast<uint4 *>(bst + (((r0 + r) ^ (wt & 7)) << 4)) = o;
 				}
 			}
-#ifdef GPTQ_TC_TIMING
-			const long long t4 = clock64();
-#endif
 			fence_proxy_async();                               // generic-proxy stores -> visible to the tensor core
 			mbar_arrive(bar_full_b + 8 * s);
-#ifdef GPTQ_TC_TIMING
-			if (p.dbg && tid == 64 && blockIdx.x == 0 && blockIdx.y == 0) { p.dbg[4] += t4 - t3; p.dbg[5] += clock64() - t4; }
-#endif
 		}
 		if (!ok) fail();
 
@@ -248,9 +214,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				const int ncol = n0 + head_local * 128;
 				const int section = ncol / a.hidden, head = (ncol - section * a.hidden) >> 7;
 				int pos = live ? a.pos[row] : 0;
+				bool pos_ok = true;
 				if (pos < 0 || pos >= a.max_pos) {      // never index the tables / the cache out of range
 					atomicExch(p.status, 4);
 					pos = 0;
+					pos_ok = false;
 				}
 				__half *dst = nullptr;
 				if (live) {
@@ -269,7 +237,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 					tmem_ld32(t_head + hc * 32, lo);
 					tmem_ld32(t_head + 64 + hc * 32, hi);
 					tmem_ld_wait();
-					if (live) {
+					if (live && (pos_ok || section == 0)) {      // K / V of an out-of-range position are dropped, not written over cache row 0
 						const __half *ct = a.cos_t + (size_t)pos * 128, *stb = a.sin_t + (size_t)pos * 128;
 #pragma unroll
 						for (int j = 0; j < 32; j += 2) {

@@ -172,14 +172,16 @@ class QuantLlamaAttention(nn.Module):
 			self._tables = rope_tables(self.head_dim, n, self.rope_theta, device=device)
 		return self._tables
 
-	def project_qkv(self, hidden_states, position_ids, kv_cache=None, rms_weight=None, rms_eps=1e-6, sumsq_in=None):
+	def project_qkv(self, hidden_states, position_ids, kv_cache=None, rms_weight=None, rms_eps=1e-6, sumsq_in=None, need_positions: int = 0):
+		"""`need_positions`: rows the rotary tables must have when there is no static cache (past + new tokens);
+		like the reference's rotary cache (fused_attention.py:101) the tables grow beyond max_position_embeddings."""
 		qw, g_idx, perm = self.qkv_proj.kernel_operands()
 		if g_idx is not None:
 			raise NotImplementedError('fused QKV needs act-order groups of equal size')
 		bsz, q_len, _ = hidden_states.shape
 		if position_ids is None:
 			position_ids = torch.arange(q_len, device=hidden_states.device).unsqueeze(0).expand(bsz, q_len)
-		need = 0 if kv_cache is None else kv_cache[0].shape[2]      # a static cache fixes the position range
+		need = max(need_positions, q_len) if kv_cache is None else kv_cache[0].shape[2]      # a static cache fixes the position range
 		cos, sin = self.tables(hidden_states.device, need)
 		return qkv_rope(self.qkv_proj.groupsize, hidden_states, qw, self.qkv_proj.scales, self.qkv_proj.qzeros, cos, sin,
 						position_ids, self.num_heads, self.head_dim, perm=perm, kv_cache=kv_cache, rms_weight=rms_weight, rms_eps=rms_eps,
@@ -193,10 +195,10 @@ class QuantLlamaAttention(nn.Module):
 		(fused_attention.py:79-153): returns (attn_output, attn_weights or None, (K, V) or None)."""
 		bsz, q_len, _ = hidden_states.size()
 		hidden_states = hidden_states.contiguous()
+		past = 0 if past_key_value is None else past_key_value[0].shape[-2]
 		if position_ids is None:
-			past = 0 if past_key_value is None else past_key_value[0].shape[-2]
 			position_ids = torch.arange(past, past + q_len, device=hidden_states.device).unsqueeze(0).expand(bsz, q_len)
-		query_states, key_states, value_states = self.project_qkv(hidden_states, position_ids)
+		query_states, key_states, value_states = self.project_qkv(hidden_states, position_ids, need_positions=past + q_len)
 		if past_key_value is not None:
 			key_states = torch.cat([past_key_value[0], key_states], dim=2)
 			value_states = torch.cat([past_key_value[1], value_states], dim=2)

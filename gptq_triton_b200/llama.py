@@ -219,6 +219,7 @@ class DecodeEngine:
 		self.len_hint = max_seq
 		self.graph = None
 		self.launches_per_step = None
+		self.next_pos = 0          # host-side copy of the position the next step() writes (the cache has max_seq rows)
 
 	# -- one layer on hidden states h [b, t, hidden]; K/V go to the cache at `pos` --------------
 	# ss_in: per-tile sums of squares of h left by the projection that produced it (decode steps
@@ -288,6 +289,7 @@ class DecodeEngine:
 		self.logits = logits
 		self.tok.copy_(logits.argmax(-1))
 		self.pos.fill_(t)
+		self.next_pos = t
 		self.len_hint = t + 1
 		self.mask.fill_(float('-inf'))
 		self.mask[..., :t + 1] = 0
@@ -309,6 +311,9 @@ class DecodeEngine:
 	@torch.no_grad()
 	def step(self) -> torch.Tensor:
 		"""Feeds self.tok at self.pos, returns the next token [b, 1] (device tensor)."""
+		if self.next_pos >= self.max_seq:
+			raise RuntimeError(f'DecodeEngine: the static KV cache holds {self.max_seq} positions and is full; build the engine with a larger max_seq')
+		self.next_pos += 1
 		if not self.use_graph:
 			self._step_body()
 			return self.tok
@@ -340,7 +345,24 @@ class DecodeEngine:
 	@torch.no_grad()
 	def generate(self, input_ids: torch.Tensor, steps: int) -> torch.Tensor:
 		"""Greedy generation: returns [b, steps] token ids (the first comes from the prefill)."""
+		from . import _lib
 		out = [self.prefill(input_ids)]
 		for _ in range(steps - 1):
 			out.append(self.step().clone())
-		return torch.cat(out, dim=1)
+		toks = torch.cat(out, dim=1)
+		# the kernels' bounded waits report through a status word instead of hanging: a non-zero word means
+		# that some result of this run cannot be trusted
+		status = _lib.kernel_status(self.device)
+		if status != 0:
+			raise _lib.GptqB200Error(f'a decode kernel reported status {status} (see _lib.kernel_status)')
+		return toks
+
+	def close(self):
+		"""Releases the tensor-parallel exchange buffers (mapped by the peers: call it on every rank, after the
+		last step has completed everywhere) and the captured graph."""
+		self.graph = None
+		for name in ('ar_o', 'ar_down'):
+			ex = getattr(self, name, None)
+			if ex is not None:
+				ex.close()
+				setattr(self, name, None)

@@ -42,6 +42,16 @@ def autotune_warmup(model):
 	return None
 
 
+def _load_checkpoint_state(model, state, strict: bool):
+	"""Checkpoints written under the transformers versions the reference names (README.md:66) carry
+	`...self_attn.rotary_emb.inv_freq`, a persistent buffer of the HF attention module of that time; the
+	reference loads them into the HF model as they are (__init__.py:60-63).  The decoder here builds its
+	rotary tables from the config, so those keys are dropped; every other key is loaded as given (strictly
+	for safetensors, non-strictly for model.pt, as the reference does)."""
+	state = {k: v for k, v in state.items() if not k.endswith('.rotary_emb.inv_freq')}
+	model.load_state_dict(state, strict=strict)
+
+
 def load_quant(checkpoint: str, warmup_autotune: bool = True, device: Optional[str] = 'cuda', fuse_mlp: Optional[bool] = None):
 	"""Load a quantised model from a checkpoint directory.
 	fuse_mlp: None fuses for every groupsize (the fused kernel here is not slower for grouped
@@ -53,9 +63,9 @@ def load_quant(checkpoint: str, warmup_autotune: bool = True, device: Optional[s
 	model = _empty_model(config, wbits, groupsize)
 	if (ck / 'model.safetensors').exists():
 		from safetensors.torch import load_file as safe_load
-		model.load_state_dict(safe_load(str(ck / 'model.safetensors')))
+		_load_checkpoint_state(model, safe_load(str(ck / 'model.safetensors')), strict=True)
 	elif (ck / 'model.pt').exists():
-		model.load_state_dict(torch.load(ck / 'model.pt'), strict=False)
+		_load_checkpoint_state(model, torch.load(ck / 'model.pt'), strict=False)
 	else:
 		raise FileNotFoundError(f"Could not find model checkpoint at {checkpoint}; please ensure that the path is correct and contains a `model.pt` or `model.safetensors` file.")
 	for _, m in model.named_modules():

@@ -202,10 +202,12 @@ int gptq_qkv_rope_rms(const void *x, const int32_t *qweight, const int32_t *qzer
  * counterpart in the reference, which has no multi-GPU code.  Decode sizes only (M <= 16,
  * N % 128 == 0); larger M uses gptq_qmatmul + an NCCL all-reduce.
  *   partials[r]   receive buffer of rank r as mapped into THIS process (own buffer for r == rank),
- *                 gptq_ar_partial_bytes(N) bytes, zeroed once.
+ *                 gptq_ar_partial_bytes(N) bytes (two halves of [8 source ranks][tiles][16][128] words), zeroed once.
  *   flags[rank]   this rank's per-tile sequence numbers, gptq_ar_flag_bytes(N) bytes, zeroed once
  *                 (the other entries of flags are not used).
- * One pair per projection that alternates in a layer (o_proj and down_proj must not share one).
+ * The receive area is double-buffered by the parity of the call's sequence number, so back-to-back
+ * calls on one pair are safe (a rank cannot get two calls ahead of a peer: it needs that peer's
+ * words of the call in between).  Calls that may overlap on the GPU need separate pairs.
  * Every rank calls with the same arguments in the same order.  Each rank pushes its tile in fp32
  * (bias included: pass it on one rank only) into its peers' receive buffers as 8-byte words
  * {value, sequence number}, polls its own buffer (at most two seconds, then status word 5) until
@@ -258,8 +260,18 @@ int gptq_qmatmul_noalloc(const void *x, const int32_t *qweight, const int32_t *q
                          gptq_stream_t stream);
 
 /* Scratch bytes gptq_qmatmul_noalloc would use for this shape on the current device (0 when the
- * shape is not served by it).  Host-only arithmetic. */
+ * shape is not served by it).  Launches nothing and touches no device memory; it does query the
+ * current device's multiprocessor count (the split-K plan depends on it), so call it with the
+ * device current on which the matmul will run. */
 size_t gptq_noalloc_scratch_bytes(int M, int K, int N, int groupsize);
+
+/* Status word of the allocation-free entry point on the current device: 0 = healthy; 1 = a weight
+ * tile never arrived within the kernel's bounded wait; 2 = shared memory misaligned; 6 = a split-K
+ * partial sum never arrived (results of that call are wrong).  The word lives in the built-in
+ * array, survives later calls and is sticky until read with clear != 0.  The call synchronises the
+ * device (cudaDeviceSynchronize + a 4-byte copy): use it after a batch of calls, not in a serving
+ * loop, and not during stream capture.  Negative: a GPTQ_ERR_* code.  No counterpart in the reference. */
+int gptq_noalloc_status(int clear);
 
 #ifdef __cplusplus
 }

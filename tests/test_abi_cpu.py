@@ -75,7 +75,7 @@ def test_extension_entry_points_validate_on_the_host(lib):
 	assert lib.gptq_gateup_silu_rms(*gu, None, None, 0, 1e-6) == -1      # norm weight required
 	assert lib.gptq_gateup_silu_rms(*gu, fake, None, 8, 1e-6) == -1      # ... and the sums of squares
 	assert lib.gptq_gateup_silu_rms(*gu, fake, fake, 300, 1e-6) == -6    # more partial sums than the kernel folds
-	assert lib.gptq_ar_partial_bytes(4096) == 8 * 32 * 16 * 128 * 8
+	assert lib.gptq_ar_partial_bytes(4096) == 2 * 8 * 32 * 16 * 128 * 8      # two halves (parity of the sequence number)
 	assert lib.gptq_ar_flag_bytes(4096) % 256 == 0 and lib.gptq_ar_flag_bytes(4096) >= 32 * 4
 	assert lib.gptq_peer_alloc(0, None) == -1 and lib.gptq_peer_export(None, None) == -1 and lib.gptq_peer_open(None, None) == -1
 	assert lib.gptq_peer_free(None) == 0 and lib.gptq_peer_close(None) == 0

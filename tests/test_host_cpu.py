@@ -85,6 +85,48 @@ def test_module_surgery_and_checkpoint_round_trip(tmp_path):
 		G.load_quant(str(tmp_path), warmup_autotune=False, device=None)
 
 
+@pytest.mark.parametrize('safetensors', [True, False])
+def test_checkpoint_with_rotary_inv_freq_keys_loads(tmp_path, safetensors):
+	"""Checkpoints written under the transformers versions the reference names carry
+	`self_attn.rotary_emb.inv_freq` per layer; they must load, in both file formats, and any OTHER
+	unexpected key of a safetensors file must still be refused."""
+	model = loader._empty_model(SMALL, 4, 128)
+	gen = torch.Generator().manual_seed(2)
+	for n, m in model.named_modules():
+		if isinstance(m, G.QuantLinear):
+			qw, qz, sc = quantize.quantize_linear_weight(torch.randn((m.outfeatures, m.infeatures), generator=gen) * 0.02, 128)
+			m.qweight.copy_(qw); m.qzeros.copy_(qz); m.scales.copy_(sc)
+	for prm in model.parameters():
+		prm.data.normal_(0, 0.02, generator=gen)
+	loader.save_quant(model, tmp_path, 128, safetensors=safetensors)
+	head_dim = SMALL.hidden_size // SMALL.num_attention_heads
+	extra = {f'model.layers.{i}.self_attn.rotary_emb.inv_freq': 1.0 / (10000.0 ** (torch.arange(0, head_dim, 2).float() / head_dim))
+			 for i in range(SMALL.num_hidden_layers)}
+	if safetensors:
+		from safetensors.torch import load_file, save_file
+		sd = load_file(str(tmp_path / 'model.safetensors'))
+		save_file({**sd, **extra}, str(tmp_path / 'model.safetensors'))
+	else:
+		sd = torch.load(tmp_path / 'model.pt')
+		torch.save({**sd, **extra}, tmp_path / 'model.pt')
+	loaded = G.load_quant(str(tmp_path), warmup_autotune=False, device=None)
+	assert torch.equal(loaded.model.layers[1].self_attn.o_proj.qweight, model.model.layers[1].self_attn.o_proj.qweight)
+	if safetensors:
+		save_file({**sd, **extra, 'model.layers.0.bogus.weight': torch.zeros(1)}, str(tmp_path / 'model.safetensors'))
+		with pytest.raises(RuntimeError):
+			G.load_quant(str(tmp_path), warmup_autotune=False, device=None)
+
+
+def test_decode_engine_refuses_to_step_past_its_cache():
+	"""Host-side guard: step() raises before a position beyond the static cache could reach a kernel
+	(checked without a GPU by calling the guard on a bare object)."""
+	from gptq_triton_b200.llama import DecodeEngine
+	e = DecodeEngine.__new__(DecodeEngine)
+	e.next_pos, e.max_seq = 8, 8
+	with pytest.raises(RuntimeError, match='is full'):
+		e.step()
+
+
 def test_make_fused_mlp_returns_module():
 	model = loader._empty_model(SMALL, 4, 128)
 	mlp = model.model.layers[0].mlp

@@ -61,6 +61,34 @@ def test_noalloc_matches_workspace_entry_point(M, K, N, gs, extra):
 	assert torch.equal(outs[0], outs[1])
 
 
+def test_noalloc_act_order_gather_and_status_word():
+	"""Act-order weights (rows sorted by group at load, `perm` passed): the gathered x lives in the built-in
+	array behind the partial sums.  Afterwards the sticky status word of the array must read healthy."""
+	from gptq_triton_b200 import build, _lib, synth
+	from gptq_triton_b200.quant_linear import _act_order_perm, act_order_rows
+	from oracle import gptq_oracle as O
+	build.build()
+	L = _lib.lib()
+	dev = torch.device('cuda', 0)
+	M, K, N, gs = 3, 2048, 512, 128
+	t = synth.quant_tensors(K, N, gs, seed=21, act_order=True)
+	x = synth.activations((M, K), seed=22).to(dev)
+	g_idx = t['g_idx'].to(dev)
+	perm = _act_order_perm(g_idx, gs)
+	assert perm is not None
+	qw = act_order_rows(t['qweight'].to(dev), perm)
+	qz, sc = t['qzeros'].to(dev), t['scales'].to(dev)
+	stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+	r32 = O.qmatmul_r32(x.cpu(), t['qweight'], t['qzeros'], t['scales'], gs, g_idx=t['g_idx'])
+	for _ in range(2):
+		y = torch.full((M, N), float('nan'), dtype=torch.float16, device=dev)
+		rc = L.gptq_qmatmul_noalloc(_ptr(x), _ptr(qw), _ptr(qz), _ptr(sc), _ptr(perm), None, None, 0, _ptr(y), M, K, N, gs, K, N, stream)
+		assert rc == 0, L.gptq_error_string(rc)
+		torch.cuda.synchronize()
+		assert O.max_rel_err(y, r32) <= TOL
+	assert L.gptq_noalloc_status(0) == 0
+
+
 def test_noalloc_rejects_what_does_not_fit():
 	from gptq_triton_b200 import build, _lib
 	build.build()
