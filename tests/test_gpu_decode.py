@@ -68,3 +68,35 @@ def test_reference_style_forward_matches_engine_logits():
 	logits_mod, _ = model(prompt)
 	scale = logits_ref.float().abs().max().item()
 	assert (logits_mod.float() - logits_ref.float()).abs().max().item() <= 1e-2 * scale
+
+
+def test_greedy_tokens_identical_at_7b_dimensions():
+	"""The benchmark's decoder dimensions (hidden 4096, MLP 11008, 32 heads x 128, vocabulary 32000) with four
+	layers and a 2048-token prompt: 32 greedy steps of the graph-captured engine against the
+	dequantise-then-matmul twin.  Random-init logits over 32000 entries are nearly flat, so the prompt is
+	chosen (by seed) such that every top-1/top-2 margin of the reference run is clear of fp16 noise."""
+	import gptq_triton_b200 as G
+	from gptq_triton_b200 import _lib, loader
+	from gptq_triton_b200.llama import LlamaConfig
+	cfg = LlamaConfig(num_hidden_layers=4, max_position_embeddings=2048 + 64)
+	steps, prompt_len = 32, 2048
+	model = G.synthetic_quantized_llama(cfg, groupsize=128, seed=11, device='cuda', fuse=False)
+	dense = loader.dense_reference_copy(model)
+	G.make_quant_attn(model)
+	G.make_fused_mlp(model)
+	best = None
+	for seed in range(16):
+		prompt = torch.randint(0, cfg.vocab_size, (1, prompt_len), generator=torch.Generator().manual_seed(100 + seed)).cuda()
+		ref_toks, margins = reference_greedy(dense, prompt, steps)
+		if best is None or min(margins) > best[2]:
+			best = (prompt, ref_toks, min(margins))
+		if min(margins) > 0.03:
+			break
+	prompt, ref_toks, margin = best
+	assert margin > 0.01, f'no prompt with clear argmax margins (best {margin})'
+	del dense
+	torch.cuda.empty_cache()
+	engine = G.DecodeEngine(model, batch=1, max_seq=prompt_len + steps + 8, use_graph=True)
+	toks = engine.generate(prompt, steps)
+	assert torch.equal(toks.cpu(), ref_toks.cpu()), (toks.cpu(), ref_toks.cpu(), margin)
+	assert _lib.kernel_status() == 0
