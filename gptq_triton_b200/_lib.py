@@ -52,6 +52,14 @@ _SIGNATURES = {
 	'gptq_qmatmul_noalloc': (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P]),
 	'gptq_noalloc_scratch_bytes': (c_size_t, [c_int, c_int, c_int, c_int]),
 	'gptq_noalloc_status': (c_int, [c_int]),
+	'gptq_chain_supported': (c_int, [c_int, c_int, c_int, c_int, c_int]),
+	'gptq_chain_desc_bytes': (c_size_t, [c_int]),
+	'gptq_chain_scratch_bytes': (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+	'gptq_chain_build': (c_int, [_P, c_int, c_int, c_int, _P]),
+	'gptq_decode_chain': (c_int, [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int64, c_int64, ctypes.c_float,
+							  _P, _P, _P, c_size_t, _P]),
+	'gptq_lm_head_workspace_bytes': (c_size_t, [c_int]),
+	'gptq_lm_head_argmax': (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, ctypes.c_float, _P, _P, _P, _P, c_size_t, _P]),
 }
 # Entry points outside the header's stable surface (tuning hooks); bound when present.
 _OPTIONAL = {
@@ -136,17 +144,29 @@ def workspace(device: torch.device, M: int, K: int, N: int, min_bytes: int = 0) 
 
 
 _retired = []
+_status_buffers = []      # scratch areas of other kernels whose status word sits at the same offset (bytes 16380..16383)
+
+
+def register_status_buffer(buf: torch.Tensor):
+	"""Includes the status word of `buf` (a kernel's scratch area, first 16 KiB = control words) in kernel_status()."""
+	import weakref
+	_status_buffers.append(weakref.ref(buf))
 
 
 def kernel_status(device=None) -> int:
 	"""OR of the status words that the decode kernels keep in their workspaces (0 = healthy;
 	1 = a TMA / bulk load never completed within the bounded wait; 2 = shared memory misaligned;
 	3 = a wait inside the tensor-core kernel ran out; 4 = position outside the rotary table / cache;
-	5 = a peer never arrived in the fused tensor-parallel all-reduce; 6 = a split-K partial sum never arrived)."""
+	5 = a peer never arrived in the fused tensor-parallel all-reduce; 6 = a split-K partial sum never arrived;
+	7 = a grid barrier of the persistent decode-step kernel timed out)."""
 	st = 0
 	for (dev, _), ws in _workspaces.items():
 		if device is None or dev == (device.index if isinstance(device, torch.device) else device):
 			st |= int(ws[16384 - 4:16384].view(torch.int32).item())
+	for ref in _status_buffers:
+		buf = ref()
+		if buf is not None and (device is None or buf.device.index == (device.index if isinstance(device, torch.device) else device)):
+			st |= int(buf[16384 - 4:16384].view(torch.int32).item())
 	return st
 
 
@@ -154,3 +174,7 @@ def clear_kernel_status():
 	"""Resets the status words (after the cause of a non-zero status has been dealt with)."""
 	for ws in _workspaces.values():
 		ws[16384 - 4:16384].zero_()
+	for ref in _status_buffers:
+		buf = ref()
+		if buf is not None:
+			buf[:16384].zero_()          # also the barrier counters, which a failed run leaves behind

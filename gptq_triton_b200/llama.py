@@ -220,6 +220,88 @@ class DecodeEngine:
 		self.graph = None
 		self.launches_per_step = None
 		self.next_pos = 0          # host-side copy of the position the next step() writes (the cache has max_seq rows)
+		# One persistent kernel per decode step (gptq_decode_chain) + the lm_head / arg-max kernel, where the model
+		# allows it (one GPU, batch <= 8, no act-order, no bias, one group size); opt-in with GPTQ_B200_CHAIN=1 (default: the
+		# kernel-per-projection path).
+		self.chain = None
+		if os.environ.get('GPTQ_B200_CHAIN', '0') != '0':
+			self.chain = self._chain_setup()
+
+	def _chain_setup(self):
+		"""Descriptors and scratch of the persistent decode-step kernel, or None when the model is not served by it."""
+		import ctypes
+		from . import _lib
+		cfg, model, dev = self.cfg, self.model, self.device
+		if self.tp_world != 1 or not (1 <= self.batch <= 8):
+			return None
+		layers = model.model.layers
+		heads = cfg.num_attention_heads
+		gs = None
+		rows = []
+		for i, layer in enumerate(layers):
+			attn, mlp = layer.self_attn, layer.mlp
+			if not isinstance(mlp, QuantLlamaMLP) or attn.head_dim != 128 or attn.num_heads != heads:
+				return None
+			qkv_w, qkv_g, qkv_p = attn.qkv_proj.kernel_operands()
+			o_w, o_g, o_p = attn.o_proj.kernel_operands()
+			d_w, d_g, d_p = mlp.down_proj.kernel_operands()
+			if not mlp._ao_ready:
+				mlp._prepare()
+			if any(v is not None for v in (qkv_g, qkv_p, o_g, o_p, d_g, d_p, mlp._perm, mlp._gidx)):
+				return None          # act-order layers keep the kernel-per-projection path
+			if any(m.bias is not None for m in (attn.qkv_proj, attn.o_proj, mlp.down_proj)):
+				return None
+			sizes = {attn.qkv_proj.groupsize, attn.o_proj.groupsize, mlp.groupsize, mlp.down_proj.groupsize}
+			if len(sizes) != 1 or (gs is not None and gs not in sizes):
+				return None
+			gs = sizes.pop()
+			if mlp.gate_proj_qweight.shape[1] != cfg.intermediate_size or qkv_w.shape[1] != 3 * cfg.hidden_size:
+				return None
+			rows.append(((qkv_w, o_w, mlp.gate_proj_qweight, mlp.up_proj_qweight, d_w),
+						 (attn.qkv_proj.qzeros, attn.o_proj.qzeros, mlp.gate_proj_qzeros, mlp.up_proj_qzeros, mlp.down_proj.qzeros),
+						 (attn.qkv_proj.scales, attn.o_proj.scales, mlp.gate_proj_scales, mlp.up_proj_scales, mlp.down_proj.scales),
+						 layer.input_layernorm.weight, layer.post_attention_layernorm.weight, self.kcache[i], self.vcache[i]))
+		L = _lib.lib()
+		if gs is None or not L.gptq_chain_supported(self.batch, cfg.hidden_size, cfg.intermediate_size, heads, gs):
+			return None
+		if cfg.hidden_size % 256 != 0 or self.batch * cfg.hidden_size * 2 > 96 * 1024:
+			return None
+
+		class Layer(ctypes.Structure):
+			_fields_ = [('qweight', ctypes.c_void_p * 5), ('qzeros', ctypes.c_void_p * 5), ('scales', ctypes.c_void_p * 5),
+						('ln1', ctypes.c_void_p), ('ln2', ctypes.c_void_p), ('kcache', ctypes.c_void_p), ('vcache', ctypes.c_void_p)]
+		arr = (Layer * len(rows))()
+		for dst, (qw, qz, sc, ln1, ln2, kc, vc) in zip(arr, rows):
+			for j in range(5):
+				dst.qweight[j], dst.qzeros[j], dst.scales[j] = qw[j].data_ptr(), qz[j].data_ptr(), sc[j].data_ptr()
+			dst.ln1, dst.ln2, dst.kcache, dst.vcache = ln1.data_ptr(), ln2.data_ptr(), kc.data_ptr(), vc.data_ptr()
+		desc = torch.zeros(L.gptq_chain_desc_bytes(len(rows)), dtype=torch.uint8, device=dev)
+		with torch.cuda.device(dev):
+			_lib.check(L.gptq_chain_build(arr, len(rows), cfg.hidden_size, cfg.intermediate_size, _lib.ptr(desc)), 'gptq_chain_build')
+		scratch = torch.zeros(L.gptq_chain_scratch_bytes(self.batch, cfg.hidden_size, cfg.intermediate_size, heads, gs), dtype=torch.uint8, device=dev)
+		_lib.register_status_buffer(scratch)
+		cos, sin = layers[0].self_attn.tables(dev, self.max_seq)
+		return dict(desc=desc, scratch=scratch, groupsize=gs, cos=cos, sin=sin, keep=rows,
+					h_out=torch.zeros((self.batch, cfg.hidden_size), dtype=torch.float16, device=dev),
+					ss_out=torch.zeros((self.batch, cfg.hidden_size // 32), dtype=torch.float32, device=dev),
+					logits=torch.zeros((self.batch, 1, cfg.vocab_size), dtype=torch.float16, device=dev),
+					lm_ws=torch.zeros(L.gptq_lm_head_workspace_bytes(self.batch), dtype=torch.uint8, device=dev))
+
+	def _chain_step_body(self):
+		from . import _lib
+		c, cfg, L = self.chain, self.cfg, _lib.lib()
+		H, S, D = cfg.num_attention_heads, self.max_seq, 128
+		st = _lib.stream_ptr(self.device)
+		eps = float(self.model.model.norm.variance_epsilon)
+		rc = L.gptq_decode_chain(_lib.ptr(c['desc']), cfg.num_hidden_layers, self.batch, cfg.hidden_size, cfg.intermediate_size, H, c['groupsize'],
+								 _lib.ptr(self.model.model.embed_tokens.weight), _lib.ptr(self.tok), _lib.ptr(self.pos), _lib.ptr(c['cos']), _lib.ptr(c['sin']),
+								 S, H * S * D, S * D, eps, _lib.ptr(c['h_out']), _lib.ptr(c['ss_out']), _lib.ptr(c['scratch']), c['scratch'].numel(), st)
+		_lib.check(rc, 'gptq_decode_chain')
+		rc = L.gptq_lm_head_argmax(_lib.ptr(c['h_out']), _lib.ptr(c['ss_out']), _lib.ptr(self.model.model.norm.weight), _lib.ptr(self.model.lm_head.weight),
+								   self.batch, cfg.hidden_size, cfg.vocab_size, eps, _lib.ptr(c['logits']), _lib.ptr(self.tok), _lib.ptr(self.pos),
+								   _lib.ptr(c['lm_ws']), c['lm_ws'].numel(), st)
+		_lib.check(rc, 'gptq_lm_head_argmax')
+		self.logits = c['logits']
 
 	# -- one layer on hidden states h [b, t, hidden]; K/V go to the cache at `pos` --------------
 	# ss_in: per-tile sums of squares of h left by the projection that produced it (decode steps
@@ -296,6 +378,8 @@ class DecodeEngine:
 		return self.tok.clone()
 
 	def _step_body(self):
+		if self.chain is not None:
+			return self._chain_step_body()
 		h = self.model.model.embed_tokens(self.tok)
 		ss = None
 		for i in range(len(self.model.model.layers)):

@@ -273,6 +273,62 @@ size_t gptq_noalloc_scratch_bytes(int M, int K, int N, int groupsize);
  * loop, and not during stream capture.  Negative: a GPTQ_ERR_* code.  No counterpart in the reference. */
 int gptq_noalloc_status(int clear);
 
+/*
+ * A whole decode step of a quantised LLaMA decoder in ONE persistent kernel (batch rows M <= 8, one GPU):
+ * per layer RMSNorm, fused QKV projection + rotary embedding + in-place KV-cache append, attention of the
+ * new token over the cache, o_proj + residual, RMSNorm, fused gate/up SiLU*mul, down_proj + residual.
+ * Replaces, for decode steps, the per-module forward chain of the reference
+ * (src/gptq_triton/fused_attention.py:79-153, fused_mlp.py:78-79 and the HF decoder layer around them):
+ * the grid stays resident across all layers, phases are separated by grid-wide barriers with bounded
+ * waits, and every warp streams its weight tiles and cache rows through one ring that keeps running
+ * across the phase boundaries.
+ *
+ * Set-up (once per model): fill one gptq_chain_layer per decoder layer (device pointers; the five weights
+ * are the fused QKV [hidden, 3*hidden], o_proj [hidden, hidden], gate and up [hidden, inter] and down
+ * [inter, hidden], all without act-order and without bias, one groupsize % 128 == 0 for all of them;
+ * KV caches [M, heads, max_pos, 128] fp16, 256-byte aligned) and call gptq_chain_build, which encodes the
+ * tensor maps and copies the descriptors into desc_dev (gptq_chain_desc_bytes(n_layers) bytes of device
+ * memory, 128-byte aligned; synchronous host-to-device copy).
+ * Per step: gptq_decode_chain.  tok[M] (int64) are the tokens fed, pos[M] (int32) their positions (= keys
+ * already cached; the new K / V row is written at pos).  h_out [M, hidden] fp16 receives the final hidden
+ * state BEFORE the last RMSNorm and sumsq_out [M, hidden / 32] its sums of squares per 32 columns, which is
+ * what gptq_lm_head_argmax takes.  scratch: gptq_chain_scratch_bytes(...) bytes, 256-byte aligned, zeroed
+ * once; the last 4 bytes of its first 16 KiB are the status word (1: a load never arrived, 4: position
+ * outside [0, max_pos), 7: a grid barrier timed out); after a non-zero status zero the first 16 KiB again.
+ * The launch is cooperative (all CTAs co-resident, else it fails with GPTQ_ERR_CUDA).
+ * gptq_chain_supported: 1 when the shape is served (M <= 8, head_dim 128, hidden % 256 == 0, inter % 128 == 0,
+ * groupsize % 128 == 0 dividing hidden and inter).
+ */
+typedef struct gptq_chain_layer {
+    const int32_t *qweight[5];      /* fused qkv, o_proj, gate, up, down */
+    const int32_t *qzeros[5];
+    const void *scales[5];
+    const void *ln1, *ln2;          /* RMSNorm weights before attention / before the MLP, fp16 [hidden] */
+    void *kcache, *vcache;
+} gptq_chain_layer;
+int gptq_chain_supported(int M, int hidden, int inter, int heads, int groupsize);
+size_t gptq_chain_desc_bytes(int n_layers);
+size_t gptq_chain_scratch_bytes(int M, int hidden, int inter, int heads, int groupsize);
+int gptq_chain_build(const gptq_chain_layer *layers /* host */, int n_layers, int hidden, int inter, void *desc_dev);
+int gptq_decode_chain(const void *desc_dev, int n_layers, int M, int hidden, int inter, int heads,
+                      int groupsize, const void *embed, const int64_t *tok, const int32_t *pos,
+                      const void *cos, const void *sin, int max_pos, int64_t kv_stride_b,
+                      int64_t kv_stride_h, float rms_eps, void *h_out, float *sumsq_out,
+                      void *scratch, size_t scratch_bytes, gptq_stream_t stream);
+
+/*
+ * Final RMSNorm + fp16 lm_head + greedy sampling in one kernel (the tail of a decode step; the reference
+ * leaves this to HF's LlamaForCausalLM and generate(), generate.py:41-50).  h [M, K] fp16 is the hidden
+ * state before the norm, sumsq [M, K / 32] its sums of squares per 32 columns, W [V, K] fp16 the lm_head
+ * weight.  Writes logits [M, V] fp16, tok_out[M] = arg-max (lowest index on ties) and adds 1 to
+ * pos_inout[M].  M <= 8, K % 256 == 0.  workspace: gptq_lm_head_workspace_bytes(M) bytes, 256-byte
+ * aligned, zeroed once.
+ */
+size_t gptq_lm_head_workspace_bytes(int M);
+int gptq_lm_head_argmax(const void *h, const float *sumsq, const void *norm_weight, const void *W, int M,
+                        int K, int V, float rms_eps, void *logits, int64_t *tok_out, int32_t *pos_inout,
+                        void *workspace, size_t workspace_bytes, gptq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
