@@ -49,6 +49,7 @@ _SIGNATURES = {
 	'gptq_attn_workspace_bytes': (c_size_t, [c_int, c_int]),
 	'gptq_attn_decode': (c_int, [_P, c_int64, _P, _P, c_int64, c_int64, _P, _P, c_int64, c_int, c_int, c_int, c_int, ctypes.c_float, _P, c_size_t, _P]),
 	'gptq_rmsnorm': (c_int, [_P, c_int64, _P, _P, c_int64, c_int, c_int, ctypes.c_float, _P]),
+	'gptq_embed_rmsnorm': (c_int, [_P, c_int64, c_int64, _P, _P, _P, c_int64, _P, c_int64, c_int, c_int, ctypes.c_float, _P]),
 	'gptq_qmatmul_noalloc': (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int, c_int64, c_int64, _P]),
 	'gptq_noalloc_scratch_bytes': (c_size_t, [c_int, c_int, c_int, c_int]),
 	'gptq_noalloc_status': (c_int, [c_int]),

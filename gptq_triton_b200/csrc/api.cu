@@ -558,7 +558,18 @@ int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_
 	if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || ldx % 8 || ldy % 8) return GPTQ_ERR_ALIGN;
 	if (M == 0) return GPTQ_OK;
 	return launch_ex(rmsnorm_kernel, dim3(M, 1, 1), dim3(RN_THREADS, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), (const __half *)x, (long long)ldx,
-					 (const __half *)weight, (__half *)y, (long long)ldy, K, eps);
+					 (const __half *)weight, (__half *)y, (long long)ldy, K, eps, (const long long *)nullptr, (__half *)nullptr, 0ll);
+}
+
+int gptq_embed_rmsnorm(const void *table, int64_t ldt, int64_t n_rows, const int64_t *tok, const void *weight, void *h_out, int64_t ldh, void *y,
+					   int64_t ldy, int M, int K, float eps, gptq_stream_t stream) {
+	if (!table || !tok || !weight || !h_out || !y || M < 0 || K <= 0 || n_rows <= 0) return GPTQ_ERR_INVALID;
+	if (K % 8 != 0) return GPTQ_ERR_SHAPE;
+	if (!aligned16(table) || !aligned16(weight) || !aligned16(h_out) || !aligned16(y) || ldt % 8 || ldh % 8 || ldy % 8) return GPTQ_ERR_ALIGN;
+	if (M == 0) return GPTQ_OK;
+	(void)n_rows;          // the ids are on the device; the caller guarantees 0 <= tok[m] < n_rows
+	return launch_ex(rmsnorm_kernel, dim3(M, 1, 1), dim3(RN_THREADS, 1, 1), 0, reinterpret_cast<cudaStream_t>(stream), (const __half *)table, (long long)ldt,
+					 (const __half *)weight, (__half *)y, (long long)ldy, K, eps, (const long long *)tok, (__half *)h_out, (long long)ldh);
 }
 
 size_t gptq_noalloc_scratch_bytes(int M, int K, int N, int groupsize) {

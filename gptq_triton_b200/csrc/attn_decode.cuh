@@ -294,10 +294,12 @@ __device__ __forceinline__ uint4 rn_scale(const uint4 &v, const uint4 &g, float 
 	return o;
 }
 
+// With `rows` the input row m is x[rows[m]] (an embedding lookup: x is the table, the token ids come from an
+// earlier kernel) and the row itself is also copied to `copy` (the residual stream of the first layer).
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const __half *__restrict__ x, long long ldx, const __half *__restrict__ w,
-															 __half *__restrict__ y, long long ldy, int K, float eps) {
+															 __half *__restrict__ y, long long ldy, int K, float eps,
+															 const long long *__restrict__ rows, __half *__restrict__ copy, long long ldc) {
 	const int row = blockIdx.x, tid = threadIdx.x;
-	const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * ldx);
 	const uint4 *wr = reinterpret_cast<const uint4 *>(w);
 	uint4 *yr = reinterpret_cast<uint4 *>(y + (size_t)row * ldy);
 	const int nu = K >> 3;
@@ -305,7 +307,14 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_kernel(const __half *__res
 	uint4 g0 = make_uint4(0u, 0u, 0u, 0u), v0 = make_uint4(0u, 0u, 0u, 0u);
 	if (tid < nu) g0 = __ldg(wr + tid);                 // the weight does not depend on earlier kernels
 	pdl_wait();
+	const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)(rows ? rows[row] : (long long)row) * ldx);
 	if (tid < nu) v0 = xr[tid];
+	if (copy) {
+		uint4 *cr = reinterpret_cast<uint4 *>(copy + (size_t)row * ldc);
+		if (tid < nu) cr[tid] = v0;
+#pragma unroll 1
+		for (int u = tid + RN_THREADS; u < nu; u += RN_THREADS) cr[u] = xr[u];
+	}
 	float ss = rn_sumsq(v0);
 #pragma unroll 1
 	for (int u = tid + RN_THREADS; u < nu; u += RN_THREADS) ss += rn_sumsq(xr[u]);

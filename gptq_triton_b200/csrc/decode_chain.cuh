@@ -1024,65 +1024,59 @@ __global__ void __launch_bounds__(LM_THREADS, 2) lm_head_kernel(const LmHeadPara
 		reinterpret_cast<uint4 *>(xs + (size_t)r * p.K)[u] = pack8(hf);
 	}
 	__syncthreads();
-	float best[CH_MAX_M];
-	int besti[CH_MAX_M];
-#pragma unroll
-	for (int r = 0; r < CH_MAX_M; ++r) {
-		best[r] = -INFINITY;
-		besti[r] = 0x7fffffff;
+	// per-lane partial dot products of the current vocabulary row with every batch row, and the warp's best so far
+	__shared__ float s_acc[CH_MAX_M][LM_THREADS];
+	if (lane < CH_MAX_M) {
+		s_bv[warp][lane] = -INFINITY;
+		s_bi[warp][lane] = 0x7fffffff;
 	}
+	__syncwarp();
 	const int gw = blockIdx.x * NW + warp, nwarps = gridDim.x * NW;
 	const int upl = units / 32;               // 16-byte units per lane and row (K % 256 == 0)
 #pragma unroll 1
 	for (int v = gw; v < p.V; v += nwarps) {
 		const uint4 *wr = reinterpret_cast<const uint4 *>(p.W + (size_t)v * p.K);
-		float acc[CH_MAX_M];
-#pragma unroll
-		for (int r = 0; r < CH_MAX_M; ++r) acc[r] = 0.f;
+#pragma unroll 1
+		for (int r = 0; r < p.M; ++r) s_acc[r][tid] = 0.f;
 #pragma unroll 1
 		for (int u0 = 0; u0 < upl; u0 += 8) {
-			uint4 w[8];
+			uint4 w[8];                           // 8 loads in flight per lane: half a row of 4096 weights per warp
 #pragma unroll
 			for (int j = 0; j < 8; ++j)
 				if (u0 + j < upl) w[j] = ld_nc_v4(wr + (u0 + j) * 32 + lane);
+#pragma unroll 1
+			for (int r = 0; r < p.M; ++r) {
+				const uint4 *xr = reinterpret_cast<const uint4 *>(xs + (size_t)r * p.K) + u0 * 32 + lane;
+				float a = 0.f;
 #pragma unroll
-			for (int j = 0; j < 8; ++j) {
-				if (u0 + j < upl) {
-					float wf[8];
-					unpack8(w[j], wf);
+				for (int j = 0; j < 8; ++j) {
+					if (u0 + j < upl) {
+						const uint4 xv = xr[j * 32];
+						const __half2 *wh = reinterpret_cast<const __half2 *>(&w[j]), *xh = reinterpret_cast<const __half2 *>(&xv);
 #pragma unroll
-					for (int r = 0; r < CH_MAX_M; ++r) {
-						if (r < p.M) {
-							float xf[8];
-							unpack8(reinterpret_cast<const uint4 *>(xs + (size_t)r * p.K)[(u0 + j) * 32 + lane], xf);
-#pragma unroll
-							for (int e = 0; e < 8; ++e) acc[r] = fmaf(wf[e], xf[e], acc[r]);
+						for (int e = 0; e < 4; ++e) {
+							const float2 wf = __half22float2(wh[e]), xf = __half22float2(xh[e]);
+							a = fmaf(wf.x, xf.x, fmaf(wf.y, xf.y, a));
 						}
 					}
 				}
+				s_acc[r][tid] += a;
 			}
 		}
+#pragma unroll 1
+		for (int r = 0; r < p.M; ++r) {
+			float a = s_acc[r][tid];
 #pragma unroll
-		for (int r = 0; r < CH_MAX_M; ++r) {
-			if (r < p.M) {
-				float a = acc[r];
-#pragma unroll
-				for (int d = 16; d > 0; d >>= 1) a += __shfl_xor_sync(0xffffffffu, a, d);
+			for (int d = 16; d > 0; d >>= 1) a += __shfl_xor_sync(0xffffffffu, a, d);
+			if (lane == 0) {
 				const __half hv = __float2half_rn(a);
-				if (lane == 0) p.logits[(size_t)r * p.V + v] = hv;
-				const float f = __half2float(hv);            // the arg-max is taken over the fp16 logits, first index wins ties
-				if (f > best[r] || (f == best[r] && v < besti[r])) {
-					best[r] = f;
-					besti[r] = v;
+				p.logits[(size_t)r * p.V + v] = hv;
+				const float f = __half2float(hv);            // the arg-max is taken over the fp16 logits, lowest index wins ties
+				if (f > s_bv[warp][r] || (f == s_bv[warp][r] && v < s_bi[warp][r])) {
+					s_bv[warp][r] = f;
+					s_bi[warp][r] = v;
 				}
 			}
-		}
-	}
-	if (lane == 0) {
-#pragma unroll
-		for (int r = 0; r < CH_MAX_M; ++r) {
-			s_bv[warp][r] = best[r];
-			s_bi[warp][r] = besti[r];
 		}
 	}
 	__syncthreads();

@@ -98,8 +98,11 @@ class LlamaAttention(nn.Module):
 		q = self.q_proj(hidden_states).view(b, t, self.num_heads, self.head_dim).transpose(1, 2)
 		k = self.k_proj(hidden_states).view(b, t, self.num_heads, self.head_dim).transpose(1, 2)
 		v = self.v_proj(hidden_states).view(b, t, self.num_heads, self.head_dim).transpose(1, 2)
-		if self._tables is None or self._tables[0].device != q.device:
-			self._tables = rope_tables(self.head_dim, self.config.max_position_embeddings, self.config.rope_theta, device=q.device, dtype=q.dtype)
+		# the tables cover every position in use: the cached ones plus the new tokens (they grow past
+		# max_position_embeddings, as the rotary cache of the HF module does)
+		need = (0 if past_key_value is None else past_key_value[0].shape[2]) + t
+		if self._tables is None or self._tables[0].device != q.device or self._tables[0].shape[0] < need:
+			self._tables = rope_tables(self.head_dim, max(need, self.config.max_position_embeddings), self.config.rope_theta, device=q.device, dtype=q.dtype)
 		cos, sin = self._tables
 		c, s = cos[position_ids].unsqueeze(1), sin[position_ids].unsqueeze(1)
 		rot = lambda x: torch.cat([-x[..., x.shape[-1] // 2:], x[..., :x.shape[-1] // 2]], dim=-1)
@@ -306,7 +309,8 @@ class DecodeEngine:
 	# -- one layer on hidden states h [b, t, hidden]; K/V go to the cache at `pos` --------------
 	# ss_in: per-tile sums of squares of h left by the projection that produced it (decode steps
 	# with the norms folded into the kernels); returns (h, ss of the new h or None).
-	def _layer(self, i, h, pos, attn_mask, kv_len, ss_in=None):
+	def _layer(self, i, h, pos, attn_mask, kv_len, ss_in=None, x_normed=None):
+		"""x_normed: input_layernorm(h), when the caller has computed it already (first layer of a decode step)."""
 		layer = self.model.model.layers[i]
 		attn: QuantLlamaAttention = layer.self_attn
 		decode = h.shape[1] == 1
@@ -316,7 +320,9 @@ class DecodeEngine:
 		# hidden state (and its sums of squares); with NCCL the norms stay separate kernels
 		fused_ar = decode and self.ar_o is not None and b <= 16
 		fold = self.fuse_norm and decode and (self.tp_world == 1 or fused_ar) and b <= 16 and self.cfg.hidden_size % 128 == 0 and self.cfg.hidden_size // 32 <= 256
-		if fold:
+		if x_normed is not None:
+			q, _, _ = attn.project_qkv(x_normed, pos, kv_cache=(self.kcache[i], self.vcache[i]))
+		elif fold:
 			q, _, _ = attn.project_qkv(h.contiguous(), pos, kv_cache=(self.kcache[i], self.vcache[i]), rms_weight=ln1.weight,
 									   rms_eps=ln1.variance_epsilon, sumsq_in=ss_in)      # ss_in None (first layer): RMSNorm kernel
 		else:
@@ -377,14 +383,57 @@ class DecodeEngine:
 		self.mask[..., :t + 1] = 0
 		return self.tok.clone()
 
+	def _own_ends(self):
+		"""Buffers for the first and last kernel of a decode step when both ends run as own kernels: embedding
+		lookup + first RMSNorm in one kernel, final RMSNorm + lm_head + arg-max + position increment in one kernel
+		(batch <= 8, hidden a multiple of 256); None otherwise."""
+		if getattr(self, '_ends', False) is not False:
+			return self._ends
+		from . import _lib
+		cfg, dev = self.cfg, self.device
+		ok = 1 <= self.batch <= 8 and cfg.hidden_size % 256 == 0 and self.batch * cfg.hidden_size * 2 <= 96 * 1024 \
+			and self.model.lm_head.bias is None and self.model.lm_head.weight.dtype == torch.float16
+		self._ends = None
+		if ok:
+			L = _lib.lib()
+			self._ends = dict(h0=torch.empty((self.batch, 1, cfg.hidden_size), dtype=torch.float16, device=dev),
+							  x0=torch.empty((self.batch, 1, cfg.hidden_size), dtype=torch.float16, device=dev),
+							  logits=torch.zeros((self.batch, 1, cfg.vocab_size), dtype=torch.float16, device=dev),
+							  lm_ws=torch.zeros(L.gptq_lm_head_workspace_bytes(self.batch), dtype=torch.uint8, device=dev))
+		return self._ends
+
 	def _step_body(self):
 		if self.chain is not None:
 			return self._chain_step_body()
-		h = self.model.model.embed_tokens(self.tok)
+		from . import _lib
+		m, cfg = self.model.model, self.cfg
+		ends = self._own_ends()
 		ss = None
-		for i in range(len(self.model.model.layers)):
+		if ends is not None:
+			# embedding row of the token and the first layer's input norm in one kernel
+			ln = m.layers[0].input_layernorm
+			rc = _lib.lib().gptq_embed_rmsnorm(_lib.ptr(m.embed_tokens.weight), cfg.hidden_size, cfg.vocab_size, _lib.ptr(self.tok), _lib.ptr(ln.weight),
+											   _lib.ptr(ends['h0']), cfg.hidden_size, _lib.ptr(ends['x0']), cfg.hidden_size, self.batch, cfg.hidden_size,
+											   float(ln.variance_epsilon), _lib.stream_ptr(self.device))
+			_lib.check(rc, 'gptq_embed_rmsnorm')
+			h = ends['h0']
+			h, ss = self._layer(0, h, self.pos, self.mask, self.max_seq, None, x_normed=ends['x0'])
+			rest = range(1, len(m.layers))
+		else:
+			h = m.embed_tokens(self.tok)
+			rest = range(len(m.layers))
+		for i in rest:
 			h, ss = self._layer(i, h, self.pos, self.mask, self.max_seq, ss)
-		h = rmsnorm_kernel(h, self.model.model.norm.weight, self.model.model.norm.variance_epsilon)
+		eps = float(m.norm.variance_epsilon)
+		if ends is not None and ss is not None:
+			# final norm (from the sums of squares the last down_proj left), lm_head, arg-max, next token and position
+			rc = _lib.lib().gptq_lm_head_argmax(_lib.ptr(h), _lib.ptr(ss), _lib.ptr(m.norm.weight), _lib.ptr(self.model.lm_head.weight), self.batch,
+												cfg.hidden_size, cfg.vocab_size, eps, _lib.ptr(ends['logits']), _lib.ptr(self.tok), _lib.ptr(self.pos),
+												_lib.ptr(ends['lm_ws']), ends['lm_ws'].numel(), _lib.stream_ptr(self.device))
+			_lib.check(rc, 'gptq_lm_head_argmax')
+			self.logits = ends['logits']
+			return
+		h = rmsnorm_kernel(h, m.norm.weight, eps)
 		logits = self.model.lm_head(h)
 		self.logits = logits
 		nxt = logits.argmax(-1)

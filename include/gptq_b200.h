@@ -159,6 +159,14 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_t ldy,
                  int M, int K, float eps, gptq_stream_t stream);
 
+/* Embedding lookup + RMSNorm for the first decoder layer of a decode step: h_out[m] = table[tok[m]] (the
+ * residual stream) and y[m] = rmsnorm(h_out[m]) * weight in one kernel; tok[M] are int64 token ids on the device
+ * (0 <= tok[m] < n_rows is the caller's guarantee).  Replaces the embedding module + input_layernorm calls of
+ * the HF decoder the reference runs (src/gptq_triton/__init__.py:47). */
+int gptq_embed_rmsnorm(const void *table, int64_t ldt, int64_t n_rows, const int64_t *tok, const void *weight,
+                       void *h_out, int64_t ldh, void *y, int64_t ldy, int M, int K, float eps,
+                       gptq_stream_t stream);
+
 /*
  * RMSNorm folded into the decode kernels (M <= 16).  No counterpart in the reference, whose
  * decoder layer runs the HF LlamaRMSNorm module between its fused ops.  A decode step otherwise
