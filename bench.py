@@ -318,6 +318,57 @@ def prefill_record(G, model, cfg, dev, peak_tflops):
 	return out
 
 
+def measure_config4(G, tp, dev, rank, world, barrier, dist, steps=16, warmup=4):
+	"""Benchmark configuration 4: LLaMA-65B architecture, 4-bit g128, batch 16, 2048-token prompts, greedy decode,
+	tensor parallel over the ranks of this run.  Device-timed like the main measurement (barrier, CUDA events, max over
+	ranks).  Reports tokens/s over all sequences, the bytes one rank streams per step and the fraction of that rank's
+	HBM roofline."""
+	import torch
+	from gptq_triton_b200 import _lib
+	from gptq_triton_b200.llama import LlamaConfig
+	cfg = LlamaConfig.llama_65b()
+	batch = 16
+	model = G.synthetic_quantized_llama(cfg, groupsize=GROUPSIZE, seed=4321, device=dev, fuse=False)
+	if world > 1:
+		tp.shard_llama(model, rank, world)
+	G.make_quant_attn(model)
+	G.make_fused_mlp(model)
+	torch.cuda.empty_cache()
+	engine = G.DecodeEngine(model, batch=batch, max_seq=PROMPT + warmup + steps + 16, use_graph=True)
+	prompt = torch.randint(0, cfg.vocab_size, (batch, PROMPT), generator=torch.Generator().manual_seed(77)).to(dev)
+	engine.prefill(prompt)
+	for _ in range(warmup):
+		engine.step()
+	barrier()
+	e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+	e0.record()
+	for _ in range(steps):
+		engine.step()
+	e1.record()
+	barrier()
+	t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+	if dist is not None:
+		dist.all_reduce(t, op=dist.ReduceOp.MAX)
+	ms = float(t.item())
+	wbytes = 0
+	for n, b_ in model.named_buffers():
+		if n.endswith(('qweight', 'qzeros', 'scales')):
+			wbytes += b_.numel() * b_.element_size()
+	wbytes += model.lm_head.weight.numel() * 2
+	heads_local = model.model.layers[0].self_attn.num_heads
+	ctx = PROMPT + warmup + steps / 2.0
+	kv = 2.0 * cfg.num_hidden_layers * batch * heads_local * ctx * 128 * 2
+	peak, which = measured_peaks()
+	ach = (wbytes + kv) / (ms / steps) / 1e6
+	rec = {'workload': 'llama65b-arch 4-bit g128 greedy decode, batch 16, 2048-token prompts, tp%d' % world, 'value': batch * steps / (ms / 1e3), 'unit': UNIT,
+		   'ms_per_step': ms / steps, 'steps': steps, 'warmup': warmup, 'weight_bytes_per_rank': wbytes, 'kv_bytes_per_rank_per_step': kv,
+		   'achieved_gbs_per_rank': ach, 'hbm_peak_gbs': peak, 'frac_of_rank_roofline': ach / peak, 'peak_source': which,
+		   'fused_all_reduce': engine.ar_o is not None, 'kernel_status': _lib.kernel_status(dev)}
+	barrier()
+	engine.close()
+	return rec
+
+
 def gpu_arm(args):
 	import torch
 	import torch.distributed as dist
@@ -505,29 +556,49 @@ def gpu_arm(args):
 		cpu = cpu_baseline_record(9)
 		cpu['config0'] = cpu_config0()
 
+	# ---- benchmark configuration 4 as a sub-record: 65B architecture, batch 16, tensor parallel (N >= 2 by default) ----
+	config4 = None
+	want4 = (args.config4 == 'on') or (args.config4 == 'auto' and world > 1)
+	if want4 and not big and not args.layers:
+		launches_7b = None
+		chain_used = engine.chain is not None
+		fused_ar = engine.ar_o is not None
+		folded_7b = engine.fuse_norm and batch <= 16 and (world == 1 or engine.ar_o is not None)
+		barrier()
+		engine.close()
+		del engine, model
+		torch.cuda.empty_cache()
+		config4 = measure_config4(G, tp, dev, rank, world, barrier, dist if world > 1 else None)
+		engine = None
+	else:
+		chain_used = engine.chain is not None
+		fused_ar = engine.ar_o is not None
+		folded_7b = engine.fuse_norm and batch <= 16 and (world == 1 or engine.ar_o is not None)
+
 	rc = 0
 	if rank == 0:
 		# own kernels per rank and step: 4 quantised matmuls + attention per layer, embedding + first norm in one kernel,
 		# final norm + lm_head + arg-max in one kernel; RMSNorm is otherwise folded into the matmul kernels.  The persistent
 		# kernel path: one chain kernel + lm_head.
-		if engine.chain is not None:
+		if chain_used:
 			launches_per_step = 2
 		else:
-			folded = engine.fuse_norm and batch <= 16 and (world == 1 or engine.ar_o is not None)
-			launches_per_step = (5 * cfg.num_hidden_layers + 2) if folded else (7 * cfg.num_hidden_layers + 1)
+			launches_per_step = (5 * cfg.num_hidden_layers + 2) if folded_7b else (7 * cfg.num_hidden_layers + 1)
 		line = {
 			'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
 			'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16',
 			'data': 'synthetic',
 			'config': {'workload': WORKLOAD if not big else 'llama65b-arch 4-bit g128 greedy decode, batch 16, 2048-token prompts', 'layers': cfg.num_hidden_layers, 'hidden': cfg.hidden_size, 'groupsize': GROUPSIZE,
-					   'parallelism': (('tp%d: QKV and gate/up by columns, o_proj and down by rows, ' % world) + ('all-reduce fused into those kernels over peer memory' if engine.ar_o is not None else 'one NCCL all-reduce after each')) if world > 1 else 'single GPU',
-					   'step': 'persistent chain kernel' if engine.chain is not None else 'one kernel per projection, CUDA graph',
+					   'parallelism': (('tp%d: QKV and gate/up by columns, o_proj and down by rows, ' % world) + ('all-reduce fused into those kernels over peer memory' if fused_ar else 'one NCCL all-reduce after each')) if world > 1 else 'single GPU',
+					   'step': 'persistent chain kernel' if chain_used else 'one kernel per projection, CUDA graph',
 					   'l2': 'inputs larger than L2: 3.6 GB of weights + KV cache are streamed every step'},
 			'e2e': {'value': e2e_tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 8 * batch, 'd2h_bytes_per_step': 8 * batch},
 			'gpu_launches': launches_per_step * args.steps,
-			'roofline': roof, 'prefill': prefill, 'parity': parity, 'cpu_baseline': cpu, 'clocks': clocks, 'kernel_status': status,
+			'roofline': roof, 'prefill': prefill, 'parity': parity, 'config4': config4, 'cpu_baseline': cpu, 'clocks': clocks, 'kernel_status': status,
 		}
 		print(json.dumps(line), flush=True)
+		if config4 is not None and config4.get('kernel_status'):
+			status = status or config4['kernel_status']
 		if status != 0:
 			sys.stderr.write('bench.py: a kernel reported status %d (see gptq_triton_b200._lib.kernel_status)\n' % status)
 			rc = 3
@@ -560,6 +631,47 @@ def kernel_case(args):
 			G.qmatmul(GROUPSIZE, x, *w)
 		torch.cuda.synchronize()
 		print(json.dumps({'kernel_case': 'prefill', 'M': int(x.shape[0]), 'launches': 3}))
+		return
+	if args.kernel_case == 'lmhead':
+		# final RMSNorm + fp16 lm_head + arg-max: 32000 x 4096 weights (262 MB, larger than L2), timed with CUDA events
+		from gptq_triton_b200 import _lib
+		L = _lib.lib()
+		V, K = 32000, 4096
+		h = (torch.randn((M, K), device=dev) * 2).half()
+		wn = torch.ones((K,), device=dev, dtype=torch.float16)
+		W = (torch.randn((V, K), device=dev) * 0.02).half()
+		ss = h.float().pow(2).view(M, K // 32, 32).sum(-1).contiguous()
+		logits = torch.zeros((M, V), dtype=torch.float16, device=dev)
+		tok = torch.zeros((M,), dtype=torch.int64, device=dev)
+		pos = torch.zeros((M,), dtype=torch.int32, device=dev)
+		ws = torch.zeros(L.gptq_lm_head_workspace_bytes(M), dtype=torch.uint8, device=dev)
+		def run():
+			rc = L.gptq_lm_head_argmax(_lib.ptr(h), _lib.ptr(ss), _lib.ptr(wn), _lib.ptr(W), M, K, V, 1e-6, _lib.ptr(logits), _lib.ptr(tok), _lib.ptr(pos),
+									   _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+			assert rc == 0
+		for _ in range(3):
+			run()
+		torch.cuda.synchronize()
+		e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+		e0.record()
+		for _ in range(10):
+			run()
+		e1.record()
+		torch.cuda.synchronize()
+		us = e0.elapsed_time(e1) * 100
+		x = (h.float() * torch.rsqrt(h.float().pow(2).mean(-1, keepdim=True) + 1e-6)).half()
+		t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+		for _ in range(3):
+			(x @ W.t()).argmax(-1)
+		t0.record()
+		for _ in range(10):
+			(x @ W.t()).argmax(-1)
+		t1.record()
+		torch.cuda.synchronize()
+		peak, which = measured_peaks()
+		alg = V * K * 2 + M * K * 2 + M * V * 2
+		print(json.dumps({'kernel_case': 'lmhead', 'M': M, 'us': us, 'gbs': alg / us / 1e3, 'frac': alg / us / 1e3 / peak, 'peak_source': which,
+						  'cublas_plus_argmax_us': t0.elapsed_time(t1) * 100, 'launches': 13}))
 		return
 	if args.kernel_case == 'attn':
 		# single-query attention over 8 rotating caches (8 x 36 MB > L2) at 2100 tokens of context
@@ -601,9 +713,10 @@ def main():
 	ap.add_argument('--no-cpu-baseline', action='store_true')
 	ap.add_argument('--no-parity', action='store_true', help='skip the greedy-decoding parity check before the timed region')
 	ap.add_argument('--no-prefill', action='store_true', help='skip the prefill-kernel record')
+	ap.add_argument('--config4', default='auto', choices=['auto', 'on', 'off'], help='also measure the 65B-architecture batch-16 configuration as a sub-record (auto: with 2 or more GPUs)')
 	ap.add_argument('--workload', default='llama7b', choices=['llama7b', 'llama65b-b16'], help='llama65b-b16: 65B architecture, batch 16 (tensor-parallel runs)')
 	ap.add_argument('--no-graph', action='store_true', help='do not capture the decode step in a CUDA graph')
-	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down', 'prefill', 'attn'], help='profiling aid: run a few launches of one kernel and exit')
+	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down', 'prefill', 'attn', 'lmhead'], help='profiling aid: run a few launches of one kernel and exit')
 	ap.add_argument('--m', type=int, default=1, help='batch rows for --kernel-case')
 	args = ap.parse_args()
 	if args.kernel_case:

@@ -203,7 +203,11 @@ class DecodeEngine:
 		# tensor parallelism, decode steps: the all-reduce after o_proj / down_proj is fused into those kernels
 		# over peer memory (one exchange buffer per projection); GPTQ_B200_TP_FUSED=0 keeps NCCL
 		self.ar_o = self.ar_down = None
-		if self.tp_world > 1 and batch <= 16 and cfg.hidden_size % 128 == 0 and os.environ.get('GPTQ_B200_TP_FUSED', '1') != '0':
+		# (row shards of act-order layers look their groups up per row and run on the general kernel, which has no
+		# fused exchange: those models use NCCL)
+		plain_rows = all(l.self_attn.o_proj.kernel_operands()[1] is None and
+						 (not isinstance(l.mlp, QuantLlamaMLP) or l.mlp.down_proj.kernel_operands()[1] is None) for l in model.model.layers)
+		if self.tp_world > 1 and batch <= 16 and cfg.hidden_size % 128 == 0 and plain_rows and os.environ.get('GPTQ_B200_TP_FUSED', '1') != '0':
 			from .tp import PeerExchange
 			try:          # collective: fails on every rank or on none
 				self.ar_o = PeerExchange(cfg.hidden_size, self.tp_rank, self.tp_world, tp_group)

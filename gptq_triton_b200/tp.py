@@ -41,11 +41,22 @@ def shard_columns(q: QuantLinear, lo: int, hi: int) -> QuantLinear:
 
 def shard_rows(q: QuantLinear, lo: int, hi: int, keep_bias: bool) -> QuantLinear:
 	"""Input rows [lo, hi) of a QuantLinear.  Without act-order the cut must fall on group
-	boundaries; the shard then owns the groups lo/groupsize .. hi/groupsize.  The bias is kept
-	on one rank only (the partial sums are added up afterwards)."""
-	assert q.g_idx is None, 'row shards of act-order layers are not supported'
+	boundaries; the shard then owns the groups lo/groupsize .. hi/groupsize.  With act-order (g_idx) any
+	cut on a multiple of 8 rows is valid: the rows of a shard may belong to any group, so the shard keeps
+	the FULL scale / zero tables (they are small) and its slice of g_idx.  The bias is kept on one rank
+	only (the partial sums are added up afterwards)."""
 	gs = q.groupsize
 	assert lo % 8 == 0 and hi % 8 == 0 and 0 <= lo < hi <= q.infeatures
+	if q.g_idx is not None:
+		has_bias = q.bias is not None and keep_bias
+		out = QuantLinear(q.bits, gs, hi - lo, q.outfeatures, has_bias)
+		out.qweight = q.qweight[lo // 8:hi // 8].contiguous()
+		out.qzeros = q.qzeros.clone()          # [G, N / 8] of the whole layer, indexed through g_idx
+		out.scales = q.scales.clone()
+		if has_bias:
+			out.bias = q.bias.clone()
+		out.set_g_idx(q.g_idx[lo:hi].contiguous())
+		return out
 	assert (lo % gs == 0 and hi % gs == 0) or gs >= q.infeatures, 'row shards must be cut on group boundaries'
 	has_bias = q.bias is not None and keep_bias
 	if gs >= q.infeatures:

@@ -619,3 +619,21 @@ def test_decode_narrow_geometry(G, M, K, gs):
 	assert torch.allclose(ss2, y2.float().pow(2).view(M, N // 32, 32).sum(-1), rtol=1e-5, atol=1e-6)
 	torch.cuda.synchronize()
 	assert _lib.kernel_status() == 0
+
+
+def test_row_parallel_shards_of_an_act_order_layer_on_the_gpu(G):
+	"""Tensor-parallel row shards of an act-order layer (full scale / zero tables + a slice of g_idx each), run one
+	after the other on this GPU: decode and prefill sizes, the partial sums add up to the oracle's full product."""
+	from gptq_triton_b200 import tp
+	K, N, gs, world = 1024, 256, 128, 2
+	t = synth(K, N, gs, seed=77, act_order=True)
+	full = G.QuantLinear(4, gs, K, N, False)
+	full.qweight, full.qzeros, full.scales = t['qweight'], t['qzeros'], t['scales']
+	full.set_g_idx(t['g_idx'])
+	cuts = [0, 520, 1024]
+	shards = [tp.shard_rows(full, cuts[r], cuts[r + 1], keep_bias=False).cuda() for r in range(world)]
+	for M in (1, 16, 40):
+		x = acts((M, K), seed=M)
+		ref = O.qmatmul_r32(x, t['qweight'], t['qzeros'], t['scales'], gs, g_idx=t['g_idx'])
+		y = sum(shards[r](x[:, cuts[r]:cuts[r + 1]].contiguous().cuda()).float() for r in range(world))
+		assert O.max_rel_err(y, ref) <= 2 * TOL

@@ -62,6 +62,28 @@ def test_row_and_column_shards_reproduce_the_full_product(gs):
 			raise AssertionError
 
 
+def test_row_shards_of_an_act_order_layer():
+	"""g_idx = a random permutation of the group assignment: a row shard keeps the full scale / zero tables and its
+	slice of g_idx; the partial products of the shards add up to the full product (any cut on 8 rows is valid)."""
+	K, N, gs, world = 512, 128, 128, 4
+	full = _quant_linear(K, N, gs, seed=5, bias=True)
+	g = torch.Generator().manual_seed(6)
+	g_idx = (torch.arange(K) // gs)[torch.randperm(K, generator=g)].to(torch.int32)
+	full.set_g_idx(g_idx)
+	x = (torch.randn((3, K), generator=g)).half()
+	ref = O.qmatmul_r32(x, full.qweight, full.qzeros, full.scales, gs, g_idx=g_idx, bias=full.bias)
+	cuts = [0, 72, 200, 384, 512]          # multiples of 8, not of the group size
+	rows = [tp.shard_rows(full, cuts[r], cuts[r + 1], keep_bias=(r == 0)) for r in range(world)]
+	assert all(torch.equal(r_.qzeros, full.qzeros) and torch.equal(r_.scales, full.scales) for r_ in rows)
+	assert torch.equal(torch.cat([r_.g_idx for r_ in rows]), g_idx)
+	part = sum(O.qmatmul_r32(x[:, cuts[r]:cuts[r + 1]], rows[r].qweight, rows[r].qzeros, rows[r].scales, gs, g_idx=rows[r].g_idx, bias=rows[r].bias)
+			   for r in range(world))
+	assert torch.allclose(part, ref, atol=1e-4)
+	# column shards carry the whole g_idx
+	col = tp.shard_columns(full, 0, 64)
+	assert torch.equal(col.g_idx, g_idx)
+
+
 def test_shard_llama_shapes():
 	cfg = LlamaConfig(hidden_size=512, intermediate_size=1408, num_hidden_layers=1, num_attention_heads=4, vocab_size=64, max_position_embeddings=64)
 	for world in (2, 4):
