@@ -68,6 +68,8 @@ _OPTIONAL = {
 	'gptq_debug_set_pdl': (None, [c_int]),
 	'gptq_debug_allow_narrow': (None, [c_int]),
 	'gptq_debug_tc_force': (None, [c_int]),
+	'gptq_debug_tc_splitk': (None, [c_int]),
+	'gptq_debug_chain_stages': (None, [c_int]),
 }
 
 

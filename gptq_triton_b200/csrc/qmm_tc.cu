@@ -19,6 +19,8 @@
 //
 // Every mbarrier wait is bounded; a wait that runs out sets a status word and the kernel
 // unwinds (TMEM is still released).
+#include <algorithm>
+
 #include <cuda.h>
 
 #include "qmm_tc.cuh"
@@ -96,6 +98,8 @@ struct TcParams {
 	TcArgs a;
 	int epi;
 	int *status;
+	int kb_per_split;            // K-blocks of 64 per CTA along grid.z (all of them without split-K)
+	float *partial;              // split-K: [split][M][N] fp32 partial sums in the workspace, else nullptr
 };
 
 }   // namespace
@@ -121,7 +125,16 @@ bool tc_shape_ok(int M, int K, int N, int groupsize) {
 	return M > 16 && N % TC_BN == 0 && K % TC_BK == 0 && groupsize % TC_BK == 0 && K % groupsize == 0;
 }
 
-size_t tc_ws_bytes(int, int) { return 16384; }       // only the status word at its end is used
+// Workspace: the status word at the end of the first 16 KB; behind it room for the fp32 partial sums of a split-K
+// launch (up to TC_MAX_SPLITK splits of M x N, at most TC_SPLIT_BYTES: larger problems fill the chip without it).
+constexpr int TC_MAX_SPLITK = 4;
+constexpr size_t TC_SPLIT_BYTES = (size_t)96 << 20;
+size_t tc_ws_bytes(int M, int N) {
+	const size_t part = (size_t)TC_MAX_SPLITK * (size_t)std::max(M, 0) * (size_t)std::max(N, 0) * 4;
+	return 16384 + (M > 16 && part <= TC_SPLIT_BYTES ? part : 0);
+}
+int g_tc_splitk = 0;                   // tests: 0 = choose by cost, n = force n splits where the epilogue allows
+extern "C" void gptq_debug_tc_splitk(int n) { g_tc_splitk = n; }
 
 static int x_tensor_map(const __half *x, int M, int K, long long ldx, CUtensorMap *out) {
 	EncodeTiledFn enc = tensor_map_encoder();
@@ -177,9 +190,17 @@ static int tc_launch_inst(const CUtensorMap &tmx, const TcParams &p, cudaStream_
 		if (e != cudaSuccess) return cuda_status(e);
 		ready[dev] = true;
 	}
-	dim3 grid(p.a.N / BN, (p.a.M + TC_BM * MH - 1) / (TC_BM * MH), 1);
+	const int nkb = p.a.K / TC_BK;
+	const int splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
+	dim3 grid(p.a.N / BN, (p.a.M + TC_BM * MH - 1) / (TC_BM * MH), splits);
 	k<<<grid, TC_THREADS, smem, stream>>>(tmx, tmw0, tmw1, p);
-	return cuda_status(cudaGetLastError());
+	if (int rc = cuda_status(cudaGetLastError())) return rc;
+	if (p.partial) {
+		const size_t units = (size_t)p.a.M * (p.a.N / 8);
+		tc_splitk_finish<<<(unsigned)((units + 255) / 256), 256, 0, stream>>>(p.partial, splits, p.a.M, p.a.N, p.a.bias, p.a.residual, p.a.ldr, p.a.y, p.a.ldy);
+		return cuda_status(cudaGetLastError());
+	}
+	return GPTQ_OK;
 }
 
 int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaStream_t stream) {
@@ -192,6 +213,8 @@ int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaSt
 	p.a = a;
 	p.epi = epi;
 	p.status = reinterpret_cast<int *>(workspace) + (16384 / 4 - 1);
+	p.kb_per_split = a.K / TC_BK;
+	p.partial = nullptr;
 	// Tile choice: estimated time = waves * (rows * columns of a tile) / relative speed of the configuration
 	// (measured per busy SM: 128 x 128 tiles 1.0, 128 x 256 tiles 1.7, 256-row tiles 2.5).
 	int dev = 0, sms = 148;
@@ -207,12 +230,51 @@ int tc_launch(const TcArgs &a, int epi, void *workspace, size_t ws_bytes, cudaSt
 		return tall ? tc_launch_inst<2, TC_EPI_SILU, 128, 2>(tmx, p, stream) : tc_launch_inst<2, TC_EPI_SILU, 128, 1>(tmx, p, stream);
 	}
 	// configurations: 0 = 128 x 128, 1 = 128 x 256, 2 = 256 x 256, 3 = 256 x 128
-	const double c[4] = {cost(128, 128, 1.0), cost(128, 256, 1.7), cost(256, 256, 2.5),
-						 cost(256, 128, TC_SPEED_256x128)};
 	int pick = 0;
-	for (int i = 1; i < 4; ++i)
-		if (c[i] < c[pick]) pick = i;
-	if (g_tc_force) pick = ((g_tc_force == 2 || g_tc_force == 3) && a.N % 256 != 0) ? 0 : g_tc_force - 1;
+	if (epi == TC_EPI_PLAIN) {
+		// Plain epilogue: tile configuration AND split-K by estimated time.  Measured on B200 (M = 512 and 1024,
+		// N = 4096, K = 4096 and 11008): a CTA needs t_kb microseconds per K-block of 64 whatever the number of CTAs
+		// (0.66 for 128 x 128 tiles, 0.73 for 128 x 256, 0.91 for 256 x 256, 0.82 for 256 x 128) plus about 2.5 us
+		// to start and drain; split-K costs about 6 us (second launch, strided fp32 stores) plus the partial sums
+		// written and read back at about 4 TB/s.  Short prompts with a long K gain most (M = 512, 11008 -> 4096:
+		// 102 -> 62 us); M = 512, 4096 -> 4096 gains 10 %.
+		const int bms[4] = {128, 128, 256, 256}, bns[4] = {128, 256, 256, 128};
+		const double t_kbs[4] = {0.66, 0.73, 0.91, 0.82};
+		const int nkb = a.K / TC_BK;
+		const bool room = ws_bytes >= 16384 + (size_t)TC_MAX_SPLITK * a.M * a.N * 4 && (size_t)TC_MAX_SPLITK * a.M * a.N * 4 <= TC_SPLIT_BYTES;
+		double best = 1e30;
+		int best_sk = 1;
+		for (int i = 0; i < 4; ++i) {
+			if (a.N % bns[i] != 0) continue;
+			if (g_tc_force && i != (((g_tc_force == 2 || g_tc_force == 3) && a.N % 256 != 0) ? 0 : g_tc_force - 1)) continue;
+			const double t_kb = t_kbs[i];
+			const long long tiles = (long long)(a.N / bns[i]) * ((a.M + bms[i] - 1) / bms[i]);
+			for (int sk = 1; sk <= TC_MAX_SPLITK; sk *= 2) {
+				if (sk > 1 && (!room || nkb < sk)) break;
+				if (g_tc_splitk > 0) {
+					if (sk != g_tc_splitk) continue;                 // forced by a test
+				} else if (sk > 1 && nkb / sk < 8) {
+					break;                                           // too few K-blocks per split to amortise the start / drain
+				}
+				const int kbps = (nkb + sk - 1) / sk;
+				const long long waves = (tiles * ((nkb + kbps - 1) / kbps) + sms - 1) / sms;
+				double t = (double)waves * (kbps * t_kb + 2.5);
+				if (sk > 1) t += 6.0 + (double)sk * a.M * a.N * 8.0 / 4.0e6;
+				if (t < best) {
+					best = t;
+					pick = i;
+					best_sk = sk;
+				}
+			}
+		}
+		p.kb_per_split = (nkb + best_sk - 1) / best_sk;
+		p.partial = best_sk > 1 ? reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + 16384) : nullptr;
+	} else {
+		const double c[4] = {cost(128, 128, 1.0), cost(128, 256, 1.7), cost(256, 256, 2.5), cost(256, 128, TC_SPEED_256x128)};
+		for (int i = 1; i < 4; ++i)
+			if (c[i] < c[pick]) pick = i;
+		if (g_tc_force) pick = ((g_tc_force == 2 || g_tc_force == 3) && a.N % 256 != 0) ? 0 : g_tc_force - 1;
+	}
 	switch (epi) {
 		case TC_EPI_PLAIN:
 			return pick == 3 ? tc_launch_inst<1, TC_EPI_PLAIN, 128, 2>(tmx, p, stream)

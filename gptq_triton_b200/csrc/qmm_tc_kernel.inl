@@ -26,7 +26,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (TC_BM * MH);
-	const int nkb = a.K / TC_BK;
+	// split-K (plain epilogue only): blockIdx.z takes the K-blocks [kb0, kb0 + nkb) and leaves fp32 partial sums
+	const int kb0 = blockIdx.z * p.kb_per_split;
+	const int nkb = min(p.kb_per_split, a.K / TC_BK - kb0);
 
 	unsigned char *sA = smem;                                              // [S][MH][16 KB]
 	unsigned char *sB = smem + S * A_STAGE;                                // [NSTREAM][S][B_TILE]
@@ -76,8 +78,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 					const int s = kw % PS;
 					if (!mbar_wait_bounded(bar_empty_w + 8 * s, ((kw / PS) & 1) ^ 1, TC_SPIN)) return false;
 					mbar_arrive_expect_tx(bar_full_w + 8 * s, NSTREAM * PW_BYTES);
-					tma_load_2d(smem_u32(sW + (s * NSTREAM) * PW_BYTES), &tmw0, n0, kw * 8, bar_full_w + 8 * s);
-					if (NSTREAM == 2) tma_load_2d(smem_u32(sW + (s * NSTREAM + 1) * PW_BYTES), &tmw1, n0, kw * 8, bar_full_w + 8 * s);
+					tma_load_2d(smem_u32(sW + (s * NSTREAM) * PW_BYTES), &tmw0, n0, (kb0 + kw) * 8, bar_full_w + 8 * s);
+					if (NSTREAM == 2) tma_load_2d(smem_u32(sW + (s * NSTREAM + 1) * PW_BYTES), &tmw1, n0, (kb0 + kw) * 8, bar_full_w + 8 * s);
 				}
 				return true;
 			};
@@ -88,7 +90,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				mbar_arrive_expect_tx(bar_full_a + 8 * s, A_STAGE);
 #pragma unroll
 				for (int h = 0; h < MH; ++h)          // rows beyond M are filled with zeros by the copy
-					tma_load_2d(smem_u32(sA + s * A_STAGE + h * TC_TILE_BYTES), &tmx, kb * TC_BK, m0 + h * TC_BM, bar_full_a + 8 * s);
+					tma_load_2d(smem_u32(sA + s * A_STAGE + h * TC_TILE_BYTES), &tmx, (kb0 + kb) * TC_BK, m0 + h * TC_BM, bar_full_a + 8 * s);
 			}
 		}
 	} else if (warp == 1) {
@@ -141,11 +143,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				sraw[u] = __half_as_ushort(__ldg(sc + (size_t)g * a.N + n));
 			}
 		};
-		if (grp < NG) fetch_group(min((grp * TC_BK) / a.groupsize, ngroups - 1));
+		if (grp < NG) fetch_group(min(((kb0 + grp) * TC_BK) / a.groupsize, ngroups - 1));
 		int g_cur = -1;
 		bool ok = true;
 		for (int kb = (grp < NG ? grp : nkb); kb < nkb; kb += NG) {
-			const int g = (kb * TC_BK) / a.groupsize;
+			const int g = ((kb0 + kb) * TC_BK) / a.groupsize;
 			if (g != g_cur) {
 				g_cur = g;
 #pragma unroll
@@ -157,7 +159,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 				}
 			}
 			{
-				const int g_next = ((kb + NG) * TC_BK) / a.groupsize;     // group of this thread's next K-block
+				const int g_next = ((kb0 + kb + NG) * TC_BK) / a.groupsize;     // group of this thread's next K-block
 				if (g_next < ngroups) fetch_group(g_next);                 // always: the registers then hold that group's data
 			}
 			{
@@ -266,7 +268,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 					tmem_ld32(t_row + c * 32, v);
 					if (EPI == TC_EPI_SILU) tmem_ld32(t_row + BN + c * 32, u);
 					tmem_ld_wait();
-					if (live) {
+					if (EPI == TC_EPI_PLAIN && p.partial != nullptr) {
+						// split-K: this split's fp32 sums; bias, residual and the fp16 rounding follow in tc_splitk_finish
+						if (live) {
+							float4 *dst = reinterpret_cast<float4 *>(p.partial + ((size_t)blockIdx.z * a.M + row) * a.N + n0 + c * 32);
+#pragma unroll
+							for (int j = 0; j < 8; ++j) __stcg(dst + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+						}
+					} else if (live) {
 						const int nc = n0 + c * 32;
 #pragma unroll
 						for (int j = 0; j < 32; j += 8) {
@@ -317,6 +326,47 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_kernel(const __grid_constant
 		__syncwarp();
 		tmem_dealloc(tmem_base, TMEM_COLS);
 	}
+}
+
+// Split-K tail of the plain epilogue: y = fp16(sum over splits of the partial sums (in split order) + bias + residual).
+__global__ void __launch_bounds__(256) tc_splitk_finish(const float *__restrict__ partial, int splitk, int M, int N, const __half *__restrict__ bias,
+														const __half *__restrict__ residual, long long ldr, __half *__restrict__ y, long long ldy) {
+	const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;           // unit of 8 columns
+	const int upr = N >> 3;
+	if (i >= (size_t)M * upr) return;
+	const int row = (int)(i / upr), n = (int)(i % upr) * 8;
+	float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+	for (int s = 0; s < splitk; ++s) {
+		const float4 *src = reinterpret_cast<const float4 *>(partial + ((size_t)s * M + row) * N + n);
+		const float4 a = __ldcg(src), b = __ldcg(src + 1);
+		o[0] += a.x; o[1] += a.y; o[2] += a.z; o[3] += a.w;
+		o[4] += b.x; o[5] += b.y; o[6] += b.z; o[7] += b.w;
+	}
+	if (bias) {
+		const uint4 bv = *reinterpret_cast<const uint4 *>(bias + n);
+		const __half2 *bh = reinterpret_cast<const __half2 *>(&bv);
+#pragma unroll
+		for (int e = 0; e < 4; ++e) {
+			const float2 f = __half22float2(bh[e]);
+			o[2 * e] += f.x;
+			o[2 * e + 1] += f.y;
+		}
+	}
+	if (residual) {
+		const uint4 rv = *reinterpret_cast<const uint4 *>(residual + (size_t)row * ldr + n);
+		const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+		for (int e = 0; e < 4; ++e) {
+			const float2 f = __half22float2(rh[e]);
+			o[2 * e] += f.x;
+			o[2 * e + 1] += f.y;
+		}
+	}
+	uint4 ov;
+	__half2 *oh = reinterpret_cast<__half2 *>(&ov);
+#pragma unroll
+	for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(o[2 * e], o[2 * e + 1]);
+	*reinterpret_cast<uint4 *>(y + (size_t)row * ldy + n) = ov;
 }
 
 }   // namespace gptq

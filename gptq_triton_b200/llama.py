@@ -429,7 +429,7 @@ class DecodeEngine:
 		for i in rest:
 			h, ss = self._layer(i, h, self.pos, self.mask, self.max_seq, ss)
 		eps = float(m.norm.variance_epsilon)
-		if ends is not None and ss is not None:
+		if ends is not None and ss is not None and self.batch <= 2:          # (at larger batches the dense matmul of the library is faster than the row-at-a-time kernel)
 			# final norm (from the sums of squares the last down_proj left), lm_head, arg-max, next token and position
 			rc = _lib.lib().gptq_lm_head_argmax(_lib.ptr(h), _lib.ptr(ss), _lib.ptr(m.norm.weight), _lib.ptr(self.model.lm_head.weight), self.batch,
 												cfg.hidden_size, cfg.vocab_size, eps, _lib.ptr(ends['logits']), _lib.ptr(self.tok), _lib.ptr(self.pos),

@@ -637,3 +637,25 @@ def test_row_parallel_shards_of_an_act_order_layer_on_the_gpu(G):
 		ref = O.qmatmul_r32(x, t['qweight'], t['qzeros'], t['scales'], gs, g_idx=t['g_idx'])
 		y = sum(shards[r](x[:, cuts[r]:cuts[r + 1]].contiguous().cuda()).float() for r in range(world))
 		assert O.max_rel_err(y, ref) <= 2 * TOL
+
+
+@pytest.mark.parametrize('sk', [2, 4])
+@pytest.mark.parametrize('cfg', [1, 2, 3, 4])
+def test_prefill_split_k(G, cfg, sk):
+	"""Split-K of the tensor-core kernel (plain epilogue): every tile configuration with 2 and 4 splits, uneven last
+	split (K = 1216 = 19 blocks of 64), bias and residual applied by the finishing kernel."""
+	from gptq_triton_b200 import _lib
+	M, K, N, gs = 300, 1216, 512, 64
+	t = synth(K, N, gs, seed=cfg * 10 + sk, bias=True)
+	x, res = acts((M, K), seed=3), acts((M, N), seed=4)
+	ref = O.qmatmul_r32(x, t['qweight'], t['qzeros'], t['scales'], gs, bias=t['bias'], residual=res)
+	try:
+		_lib.lib().gptq_debug_tc_force(cfg)
+		_lib.lib().gptq_debug_tc_splitk(sk)
+		y = G.qmatmul(gs, x.cuda(), t['qweight'].cuda(), t['scales'].cuda(), t['qzeros'].cuda(), bias=t['bias'].cuda(), residual=res.cuda())
+		torch.cuda.synchronize()
+	finally:
+		_lib.lib().gptq_debug_tc_force(0)
+		_lib.lib().gptq_debug_tc_splitk(0)
+	assert O.max_rel_err(y, ref) <= TOL
+	assert _lib.kernel_status() == 0
