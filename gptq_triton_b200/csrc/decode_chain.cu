@@ -275,7 +275,7 @@ int gptq_lm_head_argmax(const void *h, const float *sumsq, const void *norm_weig
 	if (K % 256 != 0) return GPTQ_ERR_SHAPE;
 	if (!aligned16(h) || !aligned16(norm_weight) || !aligned16(W) || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return GPTQ_ERR_ALIGN;
 	if (workspace_bytes < gptq_lm_head_workspace_bytes(M)) return GPTQ_ERR_WORKSPACE;
-	const size_t smem = (size_t)M * K * 2;
+	const size_t smem = (size_t)CH_MAX_M * ((size_t)K * 2 + LM_XPAD);          // all 8 rows of x (absent ones zero)
 	if (smem > 96 * 1024) return GPTQ_ERR_UNSUPPORTED;
 	static bool ready[64] = {false};
 	int dev = 0;
@@ -285,7 +285,7 @@ int gptq_lm_head_argmax(const void *h, const float *sumsq, const void *norm_weig
 		if (e != cudaSuccess) return cuda_status(e);
 		ready[dev] = true;
 	}
-	const int grid = std::min(2 * sm_count_now(), (V + LM_THREADS / 32 - 1) / (LM_THREADS / 32));
+	const int grid = std::max(1, std::min(2 * sm_count_now(), ((V + 15) / 16 + LM_THREADS / 32 - 1) / (LM_THREADS / 32)));      // a warp per 16 vocabulary rows
 	unsigned char *wb = reinterpret_cast<unsigned char *>(workspace);
 	LmHeadParams p = {};
 	p.h = reinterpret_cast<const __half *>(h);

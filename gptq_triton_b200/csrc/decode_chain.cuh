@@ -972,10 +972,15 @@ __global__ void __launch_bounds__(CH_THREADS, 2) decode_chain_kernel(const __gri
 }
 
 // ---- lm_head: logits = rmsnorm(h) x W^T (fp16 weights [V, K]), greedy token, position + 1 -------------------
-// Each warp takes vocabulary rows in turn (16 bytes per lane and load, all loads of a row in flight); x is the
-// normalised hidden state in shared memory.  The arg-max is reduced per warp and CTA, the last CTA to arrive
-// (ticket) reduces the per-CTA candidates in CTA order, writes the tokens and advances the positions.
+// HBM-bound: every weight is read once, 16 bytes per lane and load.  A warp takes 16 vocabulary rows at a time and
+// multiplies them with all (up to 8) batch rows on the tensor cores: the weight rows are the A operand of
+// mma.sync.m16n8k16 straight from global memory, the normalised hidden states (shared memory) the B operand.  The
+// dot product does not care about the order of k, so the lane (gid, tig) simply takes the 8 consecutive k of rows
+// gid and gid + 8 that its 16-byte loads deliver (k = 32 * step + 8 * tig + 0..7) and the same 8 k of batch row gid:
+// two MMAs per pair of loads, no shuffles, no conversion.  The arg-max is reduced per warp and CTA; the last CTA to
+// arrive (ticket) reduces the per-CTA candidates in CTA order, writes the tokens and advances the positions.
 constexpr int LM_THREADS = 256;
+constexpr int LM_XPAD = 64;               // bytes added to a row of x in shared memory: conflict-free 16-byte reads
 
 struct LmHeadParams {
 	const __half *h;              // [M, K] final hidden state (before the norm)
@@ -994,13 +999,13 @@ struct LmHeadParams {
 
 __global__ void __launch_bounds__(LM_THREADS, 2) lm_head_kernel(const LmHeadParams p) {
 	extern __shared__ __align__(16) unsigned char lm_smem[];
-	__half *xs = reinterpret_cast<__half *>(lm_smem);                       // [M][K]
-	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
 	constexpr int NW = LM_THREADS / 32;
 	__shared__ float s_inv[CH_MAX_M];
 	__shared__ float s_bv[NW][CH_MAX_M];
 	__shared__ int s_bi[NW][CH_MAX_M];
 	__shared__ int s_last;
+	const int xs_stride = p.K * 2 + LM_XPAD;                 // bytes; x: [8 rows][K] fp16, rows >= M are zero
 	const int tiles32 = p.K >> 5;
 	for (int r = warp; r < p.M; r += NW) {
 		float t = 0.f;
@@ -1011,73 +1016,85 @@ __global__ void __launch_bounds__(LM_THREADS, 2) lm_head_kernel(const LmHeadPara
 	}
 	__syncthreads();
 	const int units = p.K >> 3;
-	for (int i = tid; i < p.M * units; i += LM_THREADS) {
+	for (int i = tid; i < CH_MAX_M * units; i += LM_THREADS) {
 		const int r = i / units, u = i - r * units;
-		const uint4 hv = __ldcg(reinterpret_cast<const uint4 *>(p.h + (size_t)r * p.K) + u);
-		const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(p.norm_w) + u);
-		float hf[8], wf[8];
-		unpack8(hv, hf);
-		unpack8(wv, wf);
-		const float inv = s_inv[r];
+		uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+		if (r < p.M) {
+			const uint4 hv = __ldcg(reinterpret_cast<const uint4 *>(p.h + (size_t)r * p.K) + u);
+			const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(p.norm_w) + u);
+			float hf[8], wf[8];
+			unpack8(hv, hf);
+			unpack8(wv, wf);
+			const float inv = s_inv[r];
 #pragma unroll
-		for (int e = 0; e < 8; ++e) hf[e] = hf[e] * inv * wf[e];          // x * inv * w, one rounding
-		reinterpret_cast<uint4 *>(xs + (size_t)r * p.K)[u] = pack8(hf);
+			for (int e = 0; e < 8; ++e) hf[e] = hf[e] * inv * wf[e];          // x * inv * w, one rounding
+			xv = pack8(hf);
+		}
+		*reinterpret_cast<uint4 *>(lm_smem + (size_t)r * xs_stride + u * 16) = xv;
 	}
 	__syncthreads();
-	// per-lane partial dot products of the current vocabulary row with every batch row, and the warp's best so far
-	__shared__ float s_acc[CH_MAX_M][LM_THREADS];
-	if (lane < CH_MAX_M) {
-		s_bv[warp][lane] = -INFINITY;
-		s_bi[warp][lane] = 0x7fffffff;
-	}
-	__syncwarp();
+	// this lane's running best of batch columns 2*tig and 2*tig + 1 (the same on all lanes of equal tig)
+	float best0 = -INFINITY, best1 = -INFINITY;
+	int besti0 = 0x7fffffff, besti1 = 0x7fffffff;
+	auto better = [](float f, int i, float bf, int bi) { return f > bf || (f == bf && i < bi); };
 	const int gw = blockIdx.x * NW + warp, nwarps = gridDim.x * NW;
-	const int upl = units / 32;               // 16-byte units per lane and row (K % 256 == 0)
+	const int ntiles = (p.V + 15) >> 4;
+	const unsigned char *xrow = lm_smem + (size_t)gid * xs_stride + tig * 16;
+	constexpr int U = 8;                                     // steps of 32 k per batch of loads: 16 loads of 16 bytes in flight per lane
 #pragma unroll 1
-	for (int v = gw; v < p.V; v += nwarps) {
-		const uint4 *wr = reinterpret_cast<const uint4 *>(p.W + (size_t)v * p.K);
+	for (int tile = gw; tile < ntiles; tile += nwarps) {
+		const int ra = tile * 16 + gid, rb = ra + 8;
+		const uint4 *pa = reinterpret_cast<const uint4 *>(p.W + (size_t)min(ra, p.V - 1) * p.K) + tig;
+		const uint4 *pb = reinterpret_cast<const uint4 *>(p.W + (size_t)min(rb, p.V - 1) * p.K) + tig;
+		float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-		for (int r = 0; r < p.M; ++r) s_acc[r][tid] = 0.f;
-#pragma unroll 1
-		for (int u0 = 0; u0 < upl; u0 += 8) {
-			uint4 w[8];                           // 8 loads in flight per lane: half a row of 4096 weights per warp
+		for (int k0 = 0; k0 < p.K; k0 += 32 * U) {             // K % 256 == 0
+			uint4 wa[U], wb[U];
 #pragma unroll
-			for (int j = 0; j < 8; ++j)
-				if (u0 + j < upl) w[j] = ld_nc_v4(wr + (u0 + j) * 32 + lane);
-#pragma unroll 1
-			for (int r = 0; r < p.M; ++r) {
-				const uint4 *xr = reinterpret_cast<const uint4 *>(xs + (size_t)r * p.K) + u0 * 32 + lane;
-				float a = 0.f;
+			for (int u = 0; u < U; ++u) {
+				wa[u] = ld_nc_v4(pa + (k0 >> 3) + 4 * u);
+				wb[u] = ld_nc_v4(pb + (k0 >> 3) + 4 * u);
+			}
 #pragma unroll
-				for (int j = 0; j < 8; ++j) {
-					if (u0 + j < upl) {
-						const uint4 xv = xr[j * 32];
-						const __half2 *wh = reinterpret_cast<const __half2 *>(&w[j]), *xh = reinterpret_cast<const __half2 *>(&xv);
-#pragma unroll
-						for (int e = 0; e < 4; ++e) {
-							const float2 wf = __half22float2(wh[e]), xf = __half22float2(xh[e]);
-							a = fmaf(wf.x, xf.x, fmaf(wf.y, xf.y, a));
-						}
-					}
-				}
-				s_acc[r][tid] += a;
+			for (int u = 0; u < U; ++u) {
+				const uint4 xv = *reinterpret_cast<const uint4 *>(xrow + (k0 + 32 * u) * 2);
+				mma16816(d, wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
+				mma16816(d, wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
 			}
 		}
-#pragma unroll 1
-		for (int r = 0; r < p.M; ++r) {
-			float a = s_acc[r][tid];
-#pragma unroll
-			for (int d = 16; d > 0; d >>= 1) a += __shfl_xor_sync(0xffffffffu, a, d);
-			if (lane == 0) {
-				const __half hv = __float2half_rn(a);
-				p.logits[(size_t)r * p.V + v] = hv;
-				const float f = __half2float(hv);            // the arg-max is taken over the fp16 logits, lowest index wins ties
-				if (f > s_bv[warp][r] || (f == s_bv[warp][r] && v < s_bi[warp][r])) {
-					s_bv[warp][r] = f;
-					s_bi[warp][r] = v;
-				}
-			}
+		// d[0], d[1]: row ra, batch columns 2*tig, 2*tig + 1; d[2], d[3]: row rb
+		const int c0 = 2 * tig, c1 = c0 + 1;
+		const __half h0 = __float2half_rn(d[0]), h1 = __float2half_rn(d[1]), h2 = __float2half_rn(d[2]), h3 = __float2half_rn(d[3]);
+		if (ra < p.V) {
+			if (c0 < p.M) p.logits[(size_t)c0 * p.V + ra] = h0;
+			if (c1 < p.M) p.logits[(size_t)c1 * p.V + ra] = h1;
 		}
+		if (rb < p.V) {
+			if (c0 < p.M) p.logits[(size_t)c0 * p.V + rb] = h2;
+			if (c1 < p.M) p.logits[(size_t)c1 * p.V + rb] = h3;
+		}
+		// the arg-max is taken over the fp16 logits, lowest index wins ties
+		float f0 = (ra < p.V) ? __half2float(h0) : -INFINITY, f1 = (ra < p.V) ? __half2float(h1) : -INFINITY;
+		int i0 = ra, i1 = ra;
+		if (rb < p.V) {
+			if (better(__half2float(h2), rb, f0, i0)) { f0 = __half2float(h2); i0 = rb; }
+			if (better(__half2float(h3), rb, f1, i1)) { f1 = __half2float(h3); i1 = rb; }
+		}
+#pragma unroll
+		for (int s = 4; s < 32; s <<= 1) {               // over the 8 row pairs of the tile (lanes of equal tig)
+			const float of0 = __shfl_xor_sync(0xffffffffu, f0, s), of1 = __shfl_xor_sync(0xffffffffu, f1, s);
+			const int oi0 = __shfl_xor_sync(0xffffffffu, i0, s), oi1 = __shfl_xor_sync(0xffffffffu, i1, s);
+			if (better(of0, oi0, f0, i0)) { f0 = of0; i0 = oi0; }
+			if (better(of1, oi1, f1, i1)) { f1 = of1; i1 = oi1; }
+		}
+		if (better(f0, i0, best0, besti0)) { best0 = f0; besti0 = i0; }
+		if (better(f1, i1, best1, besti1)) { best1 = f1; besti1 = i1; }
+	}
+	if (gid == 0) {
+		s_bv[warp][2 * tig] = best0;
+		s_bi[warp][2 * tig] = besti0;
+		s_bv[warp][2 * tig + 1] = best1;
+		s_bi[warp][2 * tig + 1] = besti1;
 	}
 	__syncthreads();
 	if (tid < p.M) {

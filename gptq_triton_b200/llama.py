@@ -271,7 +271,7 @@ class DecodeEngine:
 		L = _lib.lib()
 		if gs is None or not L.gptq_chain_supported(self.batch, cfg.hidden_size, cfg.intermediate_size, heads, gs):
 			return None
-		if cfg.hidden_size % 256 != 0 or self.batch * cfg.hidden_size * 2 > 96 * 1024:
+		if cfg.hidden_size % 256 != 0 or 8 * (cfg.hidden_size * 2 + 64) > 96 * 1024:
 			return None
 
 		class Layer(ctypes.Structure):
@@ -395,7 +395,7 @@ class DecodeEngine:
 			return self._ends
 		from . import _lib
 		cfg, dev = self.cfg, self.device
-		ok = 1 <= self.batch <= 8 and cfg.hidden_size % 256 == 0 and self.batch * cfg.hidden_size * 2 <= 96 * 1024 \
+		ok = 1 <= self.batch <= 8 and cfg.hidden_size % 256 == 0 and 8 * (cfg.hidden_size * 2 + 64) <= 96 * 1024 \
 			and self.model.lm_head.bias is None and self.model.lm_head.weight.dtype == torch.float16
 		self._ends = None
 		if ok:
@@ -429,7 +429,7 @@ class DecodeEngine:
 		for i in rest:
 			h, ss = self._layer(i, h, self.pos, self.mask, self.max_seq, ss)
 		eps = float(m.norm.variance_epsilon)
-		if ends is not None and ss is not None and self.batch <= 2:          # (at larger batches the dense matmul of the library is faster than the row-at-a-time kernel)
+		if ends is not None and ss is not None:
 			# final norm (from the sums of squares the last down_proj left), lm_head, arg-max, next token and position
 			rc = _lib.lib().gptq_lm_head_argmax(_lib.ptr(h), _lib.ptr(ss), _lib.ptr(m.norm.weight), _lib.ptr(self.model.lm_head.weight), self.batch,
 												cfg.hidden_size, cfg.vocab_size, eps, _lib.ptr(ends['logits']), _lib.ptr(self.tok), _lib.ptr(self.pos),
