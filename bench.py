@@ -632,6 +632,31 @@ def kernel_case(args):
 		torch.cuda.synchronize()
 		print(json.dumps({'kernel_case': 'prefill', 'M': int(x.shape[0]), 'launches': 3}))
 		return
+	if args.kernel_case == 'chain':
+		# the persistent decode-step kernel on four layers of the 7B architecture after a 2048-token prompt (about 1 GB on
+		# the device): a few steps, nothing else; also prints the step time of both engines
+		from gptq_triton_b200.llama import LlamaConfig
+		cfg = LlamaConfig(num_hidden_layers=4, max_position_embeddings=4096)
+		model = G.synthetic_quantized_llama(cfg, groupsize=GROUPSIZE, seed=1, device=dev)
+		prompt = torch.randint(0, cfg.vocab_size, (1, PROMPT), generator=torch.Generator().manual_seed(3)).to(dev)
+		out = {'kernel_case': 'chain', 'layers': 4}
+		for name, flag in (('chain', '1'), ('kernel_per_projection', '0')):
+			os.environ['GPTQ_B200_CHAIN'] = flag
+			e = G.DecodeEngine(model, batch=1, max_seq=PROMPT + 64, use_graph=(flag == '0'))
+			assert (e.chain is not None) == (flag == '1')
+			e.prefill(prompt)
+			for _ in range(5):
+				e.step()
+			torch.cuda.synchronize()
+			e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+			e0.record()
+			for _ in range(20):
+				e.step()
+			e1.record()
+			torch.cuda.synchronize()
+			out[name + '_ms_per_step'] = e0.elapsed_time(e1) / 20
+		print(json.dumps(out))
+		return
 	if args.kernel_case == 'lmhead':
 		# final RMSNorm + fp16 lm_head + arg-max: 32000 x 4096 weights (262 MB, larger than L2), timed with CUDA events
 		from gptq_triton_b200 import _lib
@@ -716,7 +741,7 @@ def main():
 	ap.add_argument('--config4', default='auto', choices=['auto', 'on', 'off'], help='also measure the 65B-architecture batch-16 configuration as a sub-record (auto: with 2 or more GPUs)')
 	ap.add_argument('--workload', default='llama7b', choices=['llama7b', 'llama65b-b16'], help='llama65b-b16: 65B architecture, batch 16 (tensor-parallel runs)')
 	ap.add_argument('--no-graph', action='store_true', help='do not capture the decode step in a CUDA graph')
-	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down', 'prefill', 'attn', 'lmhead'], help='profiling aid: run a few launches of one kernel and exit')
+	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down', 'prefill', 'attn', 'lmhead', 'chain'], help='profiling aid: run a few launches of one kernel and exit')
 	ap.add_argument('--m', type=int, default=1, help='batch rows for --kernel-case')
 	args = ap.parse_args()
 	if args.kernel_case:
