@@ -65,6 +65,7 @@ _SIGNATURES = {
 # Entry points outside the header's stable surface (tuning hooks); bound when present.
 _OPTIONAL = {
 	'gptq_debug_force_splitk': (None, [c_int]),
+	'gptq_debug_max_stages': (None, [c_int]),
 	'gptq_debug_set_pdl': (None, [c_int]),
 	'gptq_debug_allow_narrow': (None, [c_int]),
 	'gptq_debug_tc_force': (None, [c_int]),
@@ -95,6 +96,8 @@ def lib() -> ctypes.CDLL:
 				fn = getattr(l, name)
 				fn.restype = res
 				fn.argtypes = args
+		if os.environ.get('GPTQ_B200_STAGES') and hasattr(l, 'gptq_debug_max_stages'):
+			l.gptq_debug_max_stages(int(os.environ['GPTQ_B200_STAGES']))      # ring depth of the decode kernel (A/B measurements)
 		if os.environ.get('GPTQ_B200_PDL', '1') == '0' and hasattr(l, 'gptq_debug_set_pdl'):
 			l.gptq_debug_set_pdl(0)      # opt out of programmatic dependent launch (A/B measurements)
 		_lib = l

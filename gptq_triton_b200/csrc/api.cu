@@ -16,6 +16,7 @@ namespace gptq {
 thread_local int g_last_cuda_error = 0;
 
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
+static int g_max_stages = 4;     // tuning hook: upper bound of the ring depth of the decode kernel
 static int g_pdl = 1;             // programmatic dependent launch for the decode-step kernels (+3 % on the decode step)
 
 static int sm_count() {
@@ -186,7 +187,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 		const int slots = sms * per_sm;
 		for (int sk = 1; sk <= std::min(p.total_chunks, SK_MAX_SPLITK); ++sk) {
 			int cps, eff, a, b, c;
-			int nstage = 4;
+			int nstage = g_max_stages;
 			while (nstage > 2 && layout(sk, kwarps, nstage, cps, eff, a, b, c) > cap) --nstage;
 			if (layout(sk, kwarps, nstage, cps, eff, a, b, c) > cap) continue;
 			if (eff != sk) continue;
@@ -197,7 +198,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 			double score = (double)ctas / ((double)waves * slots);
 			score -= 0.35 * (waves - 1);
 			score -= 0.004 * eff;
-			score -= 0.02 * (4 - nstage);
+			score -= 0.02 * std::max(0, 4 - nstage);
 			if (cps < kwarps) score -= 0.25;
 			if (kwarps == 4) score -= 0.03;
 			if (score > best_score) {
@@ -417,6 +418,7 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 
 // Tuning / test hook: force the split-K factor of the decode kernel (0 restores the heuristic).
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
+void gptq_debug_max_stages(int n) { g_max_stages = std::max(2, std::min(n, 8)); }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 void gptq_debug_allow_narrow(int on) { g_allow_narrow = on ? 1 : 0; }
 size_t gptq_workspace_bytes(int M, int K, int N) {
