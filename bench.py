@@ -699,16 +699,31 @@ def kernel_case(args):
 						  'cublas_plus_argmax_us': t0.elapsed_time(t1) * 100, 'launches': 13}))
 		return
 	if args.kernel_case == 'attn':
-		# single-query attention over 8 rotating caches (8 x 36 MB > L2) at 2100 tokens of context
+		# single-query attention over rotating caches (together larger than L2) at 2100 tokens of context:
+		# --m sequences x --heads heads (1 x 32: the 7B decode step; 16 x 8 / 16 x 16 / 16 x 32: configuration 4 per rank at tp8 / 4 / 2)
 		from gptq_triton_b200.fused_attention import attn_decode
-		H, S, D = 32, 2200, 128
-		caches = [(torch.randn((1, H, S, D), device=dev).half(), torch.randn((1, H, S, D), device=dev).half()) for _ in range(8)]
-		q = torch.randn((1, 1, H, D), device=dev).half().transpose(1, 2)
-		pos = torch.full((1, 1), 2100, dtype=torch.int32, device=dev)
-		for i in range(8):
+		B, H, S, D = M, args.heads, 2200, 128
+		per = 2 * B * H * S * D * 2
+		ncache = max(2, min(8, (300 << 20) // per + 1))
+		caches = [(torch.randn((B, H, S, D), device=dev).half(), torch.randn((B, H, S, D), device=dev).half()) for _ in range(ncache)]
+		q = torch.randn((B, 1, H, D), device=dev).half().transpose(1, 2)
+		pos = torch.full((B, 1), 2100, dtype=torch.int32, device=dev)
+		for i in range(ncache):
 			attn_decode(q, caches[i][0], caches[i][1], pos, 2101)
 		torch.cuda.synchronize()
-		print(json.dumps({'kernel_case': 'attn', 'launches': 8}))
+		e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+		reps = 4
+		e0.record()
+		for _ in range(reps):
+			for i in range(ncache):
+				attn_decode(q, caches[i][0], caches[i][1], pos, 2101)
+		e1.record()
+		torch.cuda.synchronize()
+		us = e0.elapsed_time(e1) * 1e3 / (reps * ncache)
+		alg = 2 * B * H * 2101 * D * 2
+		peak, which = measured_peaks()
+		print(json.dumps({'kernel_case': 'attn', 'batch': B, 'heads': H, 'ctx': 2101, 'us': us, 'gbs': alg / us / 1e3, 'frac': alg / us / 1e3 / peak,
+						  'peak_source': which, 'launches': ncache * (reps + 1)}))
 		return
 	if args.kernel_case == 'gateup':
 		K, N = 4096, 11008
@@ -743,6 +758,7 @@ def main():
 	ap.add_argument('--no-graph', action='store_true', help='do not capture the decode step in a CUDA graph')
 	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down', 'prefill', 'attn', 'lmhead', 'chain'], help='profiling aid: run a few launches of one kernel and exit')
 	ap.add_argument('--m', type=int, default=1, help='batch rows for --kernel-case')
+	ap.add_argument('--heads', type=int, default=32, help='heads for --kernel-case attn')
 	args = ap.parse_args()
 	if args.kernel_case:
 		kernel_case(args)

@@ -133,3 +133,17 @@ def test_make_fused_mlp_returns_module():
 	fused = G.make_fused_mlp(mlp)
 	assert isinstance(fused, G.QuantLlamaMLP) and fused.infeatures == 256 and fused.outfeatures == 256
 	assert G.make_fused_mlp(torch.nn.Linear(4, 4)).__class__ is torch.nn.Linear
+
+
+def test_bench_reference_arm_prints_one_json_line():
+	"""`bench.py --impl reference` (the CPU port of the reference path) runs without a GPU and prints the contract's
+	JSON line with its own cpu_baseline and e2e records."""
+	import subprocess, sys
+	from pathlib import Path
+	root = Path(__file__).resolve().parent.parent
+	r = subprocess.run([sys.executable, str(root / 'bench.py'), '--impl', 'reference', '--steps', '1', '--warmup', '0'], capture_output=True, text=True, timeout=600)
+	assert r.returncode == 0, r.stderr[-2000:]
+	line = json.loads(r.stdout.strip().splitlines()[-1])
+	assert line['impl'] == 'reference' and line['unit'] == 'tokens/s' and line['value'] > 0
+	assert line['cpu_baseline']['kind'] == 'port' and line['cpu_baseline']['cores'] >= 1 and line['cpu_baseline']['factor'] == 32
+	assert line['e2e'] == {'value': line['value'], 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}
