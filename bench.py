@@ -562,6 +562,7 @@ def gpu_arm(args):
 	if want4 and not big and not args.layers:
 		launches_7b = None
 		chain_used = engine.chain is not None
+		qa_used = engine.used_qkv_attn
 		fused_ar = engine.ar_o is not None
 		folded_7b = engine.fuse_norm and batch <= 16 and (world == 1 or engine.ar_o is not None)
 		barrier()
@@ -572,25 +573,27 @@ def gpu_arm(args):
 		engine = None
 	else:
 		chain_used = engine.chain is not None
+		qa_used = engine.used_qkv_attn
 		fused_ar = engine.ar_o is not None
 		folded_7b = engine.fuse_norm and batch <= 16 and (world == 1 or engine.ar_o is not None)
 
 	rc = 0
 	if rank == 0:
-		# own kernels per rank and step: 4 quantised matmuls + attention per layer, embedding + first norm in one kernel,
+		# own kernels per rank and step: 4 quantised matmuls + attention per layer (batch 1: the QKV projection and the attention
+		# are one kernel), embedding + first norm in one kernel,
 		# final norm + lm_head + arg-max in one kernel; RMSNorm is otherwise folded into the matmul kernels.  The persistent
 		# kernel path: one chain kernel + lm_head.
 		if chain_used:
 			launches_per_step = 2
 		else:
-			launches_per_step = (5 * cfg.num_hidden_layers + 2) if folded_7b else (7 * cfg.num_hidden_layers + 1)
+			launches_per_step = ((4 if qa_used else 5) * cfg.num_hidden_layers + 2) if folded_7b else (7 * cfg.num_hidden_layers + 1)
 		line = {
 			'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
 			'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16',
 			'data': 'synthetic',
 			'config': {'workload': WORKLOAD if not big else 'llama65b-arch 4-bit g128 greedy decode, batch 16, 2048-token prompts', 'layers': cfg.num_hidden_layers, 'hidden': cfg.hidden_size, 'groupsize': GROUPSIZE,
 					   'parallelism': (('tp%d: QKV and gate/up by columns, o_proj and down by rows, ' % world) + ('all-reduce fused into those kernels over peer memory' if fused_ar else 'one NCCL all-reduce after each')) if world > 1 else 'single GPU',
-					   'step': 'persistent chain kernel' if chain_used else 'one kernel per projection, CUDA graph',
+					   'step': 'persistent chain kernel' if chain_used else ('QKV projection + attention in one kernel, one kernel per other projection, CUDA graph' if qa_used else 'one kernel per projection, CUDA graph'),
 					   'l2': 'inputs larger than L2: 3.6 GB of weights + KV cache are streamed every step'},
 			'e2e': {'value': e2e_tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 8 * batch, 'd2h_bytes_per_step': 8 * batch},
 			'gpu_launches': launches_per_step * args.steps,
@@ -725,6 +728,48 @@ def kernel_case(args):
 		print(json.dumps({'kernel_case': 'attn', 'batch': B, 'heads': H, 'ctx': 2101, 'us': us, 'gbs': alg / us / 1e3, 'frac': alg / us / 1e3 / peak,
 						  'peak_source': which, 'launches': ncache * (reps + 1)}))
 		return
+	if args.kernel_case == 'qkvattn':
+		# decode attention block of one sequence at 2100 tokens of context, 7B shapes: the one-kernel form (projection + rotary +
+		# cache append + attention, one cluster per head) against the pair qkv_rope + attn_decode, over rotating copies of the
+		# weights and caches (together larger than L2), timed with CUDA events
+		from gptq_triton_b200.fused_attention import attn_decode, qkv_attn_decode, qkv_rope, rope_tables
+		K, H, S, D, ctx = 4096, 32, 2200, 128, 2100
+		t = synth.quant_tensors(K, 3 * H * D, GROUPSIZE, seed=2)
+		ncopy = 8
+		ws = [tuple(v.to(dev).clone() for v in (t['qweight'], t['scales'], t['qzeros'])) for _ in range(ncopy)]
+		caches = [(torch.randn((1, H, S, D), device=dev).half(), torch.randn((1, H, S, D), device=dev).half()) for _ in range(ncopy)]
+		x = synth.activations((1, 1, K), seed=1).to(dev)
+		cos, sin = rope_tables(D, S, 10000.0, device=dev)
+		pos = torch.full((1, 1), ctx, dtype=torch.int32, device=dev)
+		def one(i):
+			qw, sc, qz = ws[i]
+			return qkv_attn_decode(GROUPSIZE, x, qw, sc, qz, cos, sin, pos.view(-1), caches[i][0], caches[i][1], H)
+		def pair(i):
+			qw, sc, qz = ws[i]
+			q, _, _ = qkv_rope(GROUPSIZE, x, qw, sc, qz, cos, sin, pos, H, D, kv_cache=caches[i])
+			return attn_decode(q, caches[i][0], caches[i][1], pos, ctx + 1)
+		out = {'kernel_case': 'qkvattn', 'heads': H, 'ctx': ctx + 1}
+		reps = 4
+		for name, fn in (('one_kernel_us', one), ('two_kernels_us', pair)):
+			for i in range(ncopy):
+				fn(i)
+			torch.cuda.synchronize()
+			e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+			e0.record()
+			for _ in range(reps):
+				for i in range(ncopy):
+					fn(i)
+			e1.record()
+			torch.cuda.synchronize()
+			out[name] = e0.elapsed_time(e1) * 1e3 / (reps * ncopy)
+		alg = K * 3 * H * D // 2 + (K // GROUPSIZE) * 3 * H * D * 5 // 2 + 2 * H * (ctx + 1) * D * 2
+		peak, which = measured_peaks()
+		out.update({'alg_bytes': alg, 'frac_one_kernel': alg / out['one_kernel_us'] / 1e3 / peak, 'frac_two_kernels': alg / out['two_kernels_us'] / 1e3 / peak,
+					'peak_source': which, 'max_abs_diff': float((one(0).float() - pair(0).float()).abs().max()), 'launches': 3 * ncopy * (reps + 1) + 3})
+		from gptq_triton_b200 import _lib
+		out['kernel_status'] = _lib.kernel_status()
+		print(json.dumps(out))
+		return
 	if args.kernel_case == 'gateup':
 		K, N = 4096, 11008
 		g, u = synth.quant_tensors(K, N, GROUPSIZE, seed=2), synth.quant_tensors(K, N, GROUPSIZE, seed=3)
@@ -756,7 +801,7 @@ def main():
 	ap.add_argument('--config4', default='auto', choices=['auto', 'on', 'off'], help='also measure the 65B-architecture batch-16 configuration as a sub-record (auto: with 2 or more GPUs)')
 	ap.add_argument('--workload', default='llama7b', choices=['llama7b', 'llama65b-b16'], help='llama65b-b16: 65B architecture, batch 16 (tensor-parallel runs)')
 	ap.add_argument('--no-graph', action='store_true', help='do not capture the decode step in a CUDA graph')
-	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down', 'prefill', 'attn', 'lmhead', 'chain'], help='profiling aid: run a few launches of one kernel and exit')
+	ap.add_argument('--kernel-case', default=None, choices=['gateup', 'qkv', 'o', 'down', 'prefill', 'attn', 'lmhead', 'chain', 'qkvattn'], help='profiling aid: run a few launches of one kernel and exit')
 	ap.add_argument('--m', type=int, default=1, help='batch rows for --kernel-case')
 	ap.add_argument('--heads', type=int, default=32, help='heads for --kernel-case attn')
 	args = ap.parse_args()

@@ -8,6 +8,7 @@
 
 #include "common.cuh"
 #include "attn_decode.cuh"
+#include "qkv_attn.cuh"
 #include "qmm_skinny.cuh"
 #include "qmm_tc.cuh"
 
@@ -552,6 +553,68 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
 		}
 	}
 	return launch_ex(attn_decode_kernel, dim3(splits, heads, batch), dim3(AT_THREADS, 1, 1), AT_SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream), p);
+}
+
+// Shared-memory layout of qkv_attn_kernel for nc chunks of 128 K-rows per CTA; returns the total.
+static size_t qkv_attn_layout(QkvAttnParams &p) {
+	size_t o = (size_t)8 * p.nstage * QA_SLOT;
+	p.off_bars = (int)o; o += 8 * 8 * 8;
+	p.off_xs = (int)o; o += (size_t)p.nc * 256;
+	p.off_zz = (int)o; o += (size_t)p.nc * QA_COLS * 2;
+	p.off_sc = (int)o; o += (size_t)p.nc * QA_COLS * 2;
+	p.off_part = (int)o; o += (size_t)p.nc * QA_COLS * 4;
+	p.off_gather = (int)o; o += (size_t)QA_CLUSTER * QA_COLS * 4;
+	p.off_merge = (int)o; o += (size_t)QA_CLUSTER * 130 * 4;
+	o = (o + 15) & ~(size_t)15;
+	p.off_attn = (int)o; o += QA_D * 4 + 2 * QA_D * 2 + 8 * QA_D * 4 + 64;
+	return o;
+}
+
+int gptq_qkv_attn_supported(int K, int n_heads, int head_dim, int groupsize) {
+	if (groupsize == -1) groupsize = K;
+	if (K <= 0 || n_heads <= 0 || groupsize <= 0 || head_dim != QA_D) return 0;
+	if (K % (QA_CLUSTER * 128) != 0 || K / (QA_CLUSTER * 128) > QA_MAX_NC) return 0;
+	if (groupsize % 128 != 0 || K % groupsize != 0) return 0;
+	return 1;
+}
+
+int gptq_qkv_attn_decode(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const void *cos, const void *sin,
+						 const int32_t *pos, int max_pos, void *kcache, void *vcache, int64_t kv_stride_h, void *out, int K, int n_heads,
+						 int head_dim, int groupsize, float scale, const void *rms_weight, const float *sumsq_in, int sumsq_tiles, float rms_eps,
+						 void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+	if (!x || !qweight || !qzeros || !scales || !cos || !sin || !pos || !kcache || !vcache || !out) return GPTQ_ERR_INVALID;
+	if (max_pos <= 0 || kv_stride_h < (int64_t)max_pos * QA_D) return GPTQ_ERR_INVALID;
+	if (groupsize == -1) groupsize = K;
+	if (!gptq_qkv_attn_supported(K, n_heads, head_dim, groupsize)) return GPTQ_ERR_UNSUPPORTED;
+	if (!aligned16(x) || !aligned16(qweight) || !aligned16(qzeros) || !aligned16(scales) || !aligned16(kcache) || !aligned16(vcache) ||
+		!aligned16(out) || kv_stride_h % 8)
+		return GPTQ_ERR_ALIGN;
+	if (rms_weight && (!sumsq_in || sumsq_tiles <= 0 || !aligned16(rms_weight))) return GPTQ_ERR_INVALID;
+	if (!workspace || workspace_bytes < (size_t)SK_TICKET_BYTES) return GPTQ_ERR_WORKSPACE;
+	QkvAttnParams p = {};
+	p.x = (const __half *)x; p.qz = qzeros; p.sc = (const __half *)scales;
+	p.K = K; p.N = 3 * n_heads * QA_D; p.sec_stride = n_heads * QA_D; p.groupsize = groupsize;
+	p.nc = K / (QA_CLUSTER * 128); p.nstage = 4;
+	p.rms_w = (const __half *)rms_weight; p.ss_in = sumsq_in; p.ss_tiles = sumsq_tiles; p.rms_eps = rms_eps;
+	p.cos_t = (const __half *)cos; p.sin_t = (const __half *)sin; p.pos = pos; p.max_pos = max_pos;
+	p.kc = (__half *)kcache; p.vc = (__half *)vcache; p.kv_stride_h = kv_stride_h;
+	p.scale = scale; p.out = (__half *)out;
+	p.status = reinterpret_cast<int *>(workspace) + SK_STATUS_SLOT;
+	const size_t smem = qkv_attn_layout(p);
+	if (smem > (size_t)SK_SMEM_LIMIT - 2048) return GPTQ_ERR_UNSUPPORTED;
+	{
+		static bool ready[64] = {false};
+		int dev = 0;
+		if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GPTQ_ERR_CUDA;
+		if (!ready[dev]) {
+			cudaError_t e = cudaFuncSetAttribute(qkv_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_LIMIT - 2048);      // the kernel has 1 KB of static shared memory
+			if (e != cudaSuccess) return cuda_status(e);
+			ready[dev] = true;
+		}
+	}
+	CUtensorMap tm;
+	if (int rc = weight_tensor_map(qweight, K, p.N, &tm)) return rc;
+	return launch_ex(qkv_attn_kernel, dim3(QA_CLUSTER, n_heads, 1), dim3(QA_THREADS, 1, 1), smem, reinterpret_cast<cudaStream_t>(stream), tm, p);
 }
 
 int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_t ldy, int M, int K, float eps, gptq_stream_t stream) {

@@ -1,0 +1,486 @@
+// Decode step, one sequence: fused QKV projection + rotary embedding + KV-cache append + single-query attention
+// in ONE kernel, one thread-block cluster of 8 CTAs per head.
+//
+// Why.  Attention of head h needs nothing but head h's q, k, v: the only all-to-all dependency between the QKV
+// projection and the attention is inside a head.  A cluster keeps that exchange in distributed shared memory, so the
+// kernel boundary between the two (a grid-wide dependency: drain, flush, re-launch, stage again) disappears.
+//
+//   phase 1  CTA r of the cluster takes K-slice r (K / 8 rows) of the head's 384 weight columns (q, k, v tiles of
+//            128): 12 strips of 32 columns x K / 1024 chunks of 128 rows, streamed through per-warp rings of 2 KB
+//            slots by 2-D TMA; raw-nibble MMA as in qmm_skinny.cuh; zero points, offsets and scales applied per chunk.
+//   exchange every CTA writes its partial sums of q into ALL CTAs of the cluster and of k, v into the last CTA
+//            (st.shared::cluster), cluster barrier, fixed-order sum: every CTA holds q, the last one also k, v.
+//   phase 2  rotary; the last CTA appends the K / V row to the cache; CTA r attends to key split r of the cache
+//            (8 keys x 256 bytes per ring slot, 1-D bulk copies, issued before the dependency wait like the weights),
+//            the last one also to the token's own key; online softmax in fp32.
+//   merge    (max, sum, 128 outputs) of every CTA go to CTA 0 through distributed shared memory, cluster barrier,
+//            CTA 0 folds the eight partials in order and writes the head's 128 outputs as fp16.
+// RMSNorm of the input is folded in as in the decode kernels (sums of squares from the producing projection).
+// Deterministic: every sum runs in a fixed order.  Waits on the rings are bounded (status 1); the cluster barriers are
+// hardware barriers between CTAs that are scheduled together, and no CTA leaves before the last one.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace gptq {
+
+constexpr int QA_THREADS = 256;
+constexpr int QA_CLUSTER = 8;
+constexpr int QA_D = 128;
+constexpr int QA_SLOT = 2048;
+constexpr int QA_COLS = 3 * QA_D;          // q, k, v columns of one head
+constexpr int QA_MAX_NC = 8;               // chunks of 128 K-rows per CTA (K <= 8192)
+
+struct QkvAttnParams {
+	const __half *x;              // [K] hidden state of the token
+	const int32_t *qz;            // [G, N / 8]
+	const __half *sc;             // [G, N]
+	int K, N, sec_stride, groupsize, nc, nstage;      // sec_stride: columns between the q, k and v sections (heads * 128)
+	const __half *rms_w;          // or nullptr: x is used as it is
+	const float *ss_in;
+	int ss_tiles;
+	float rms_eps;
+	const __half *cos_t, *sin_t;  // [max_pos, 128]
+	const int32_t *pos;           // [1]: position of the token = keys already cached
+	int max_pos;
+	__half *kc, *vc;              // [heads, max_pos, 128]
+	long long kv_stride_h;
+	float scale;
+	__half *out;                  // [heads * 128]
+	int *status;
+	int off_bars, off_xs, off_zz, off_sc, off_part, off_gather, off_merge, off_attn;     // shared-memory layout
+};
+
+__device__ __forceinline__ uint32_t qa_map_peer(uint32_t local_smem_addr, uint32_t rank) {
+	uint32_t r;
+	asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+	return r;
+}
+__device__ __forceinline__ void qa_st_peer(uint32_t addr, float v) { asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void qa_cluster_sync() {
+	asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void qa_bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+	asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+				 "r"(bar)
+				 : "memory");
+}
+
+__global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS, 2)
+	qkv_attn_kernel(const __grid_constant__ CUtensorMap tmw, const QkvAttnParams p) {
+	extern __shared__ __align__(1024) unsigned char smem[];
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+	const int rank = blockIdx.x, head = blockIdx.y;            // cluster rank = K-slice = key split
+	const int NST = p.nstage, nc = p.nc;
+	unsigned char *xs = smem + p.off_xs;
+	__half *s_zz = reinterpret_cast<__half *>(smem + p.off_zz);        // [nc][384] zero point (stored + 1)
+	__half *s_sc = reinterpret_cast<__half *>(smem + p.off_sc);        // [nc][384] scale
+	float *s_part = reinterpret_cast<float *>(smem + p.off_part);      // [nc][384] this CTA's sums per chunk
+	float *s_gather = reinterpret_cast<float *>(smem + p.off_gather);  // [8 ranks][384] written by the peers
+	float *s_merge = reinterpret_cast<float *>(smem + p.off_merge);    // [8 ranks][130] written by the peers (read on rank 0)
+	float *s_q = reinterpret_cast<float *>(smem + p.off_attn);         // [128] rotated, rounded, pre-scaled query
+	__half *s_kn = reinterpret_cast<__half *>(s_q + QA_D);             // [128] new key
+	__half *s_vn = s_kn + QA_D;                                        // [128] new value
+	float *s_wo = reinterpret_cast<float *>(s_vn + QA_D);              // [8 warps][128]
+	float *s_wm = s_wo + 8 * QA_D, *s_wl = s_wm + 8;
+	__shared__ float2 s_cs[QA_MAX_NC];                                 // per chunk: C = 1024 (SXe + SXo'), S = SXe + 16 SXo'
+	__shared__ float s_inv;
+
+	const uint32_t ring_w = smem_u32(smem + (size_t)warp * NST * QA_SLOT);
+	const uint32_t bar_w = smem_u32(smem + p.off_bars) + warp * NST * 8;
+	if (lane == 0) {
+		for (int s = 0; s < NST; ++s) mbar_init(bar_w + 8 * s, 1);
+		fence_mbar_init();
+		if (warp == 0) tma_prefetch_desc(&tmw);
+	}
+	pdl_trigger();
+	// the position comes from the previous decode step (several kernels ago), not from the kernel before this one
+	int pos = p.pos[0];
+	if (pos < 0 || pos >= p.max_pos) {            // never index the tables / the cache out of range
+		if (tid == 0) atomicExch(p.status, 4);
+		pos = -1;                                 // the token attends to nothing and its K / V row is dropped
+	}
+	const int n_old = max(pos, 0);                // keys 0 .. n_old - 1 are in the cache
+	// this warp's loads: weight chunks j = warp, warp + 8, ... < 12 * nc (strip j % 12 of chunk j / 12), then the K and V
+	// rows of its share of key split `rank`, 8 keys per load
+	const int n_wloads = (12 * nc - warp + 7) / 8;
+	const int per = ((n_old + QA_CLUSTER - 1) / QA_CLUSTER + 7) & ~7;
+	const int k_lo = min(rank * per, n_old), k_hi = min(k_lo + per, n_old);
+	const int per_w = (((k_hi - k_lo) + 7) / 8 + 7) & ~7;
+	const int wk_lo = min(k_lo + warp * per_w, k_hi), wk_hi = min(wk_lo + per_w, k_hi);
+	const int nkeys = wk_hi - wk_lo, n_aloads = 2 * ((nkeys + 7) >> 3);
+	const int n_loads = n_wloads + n_aloads;
+	const __half *kb = p.kc + (size_t)head * p.kv_stride_h + (size_t)wk_lo * QA_D, *vb = p.vc + (size_t)head * p.kv_stride_h + (size_t)wk_lo * QA_D;
+	int pr_j = 0, pr_stage = 0;
+	auto produce = [&]() {
+		if (pr_j >= n_loads) return;
+		if (lane == 0) {
+			const uint32_t bar = bar_w + 8 * pr_stage, dst = ring_w + pr_stage * QA_SLOT;
+			if (pr_j < n_wloads) {
+				const int j = warp + 8 * pr_j, cl = j / 12, strip = j - cl * 12;
+				const int n0w = (strip >> 2) * p.sec_stride + head * QA_D + (strip & 3) * 32;
+				mbar_arrive_expect_tx(bar, QA_SLOT);
+				tma_load_2d(dst, &tmw, n0w, (rank * nc + cl) * 16, bar);
+			} else {
+				const int a = pr_j - n_wloads, c = a >> 1;
+				const uint32_t bytes = (uint32_t)min(8, nkeys - 8 * c) * (QA_D * 2);
+				mbar_arrive_expect_tx(bar, bytes);
+				qa_bulk_load_1d(dst, ((a & 1) ? vb : kb) + (size_t)c * 8 * QA_D, bytes, bar);
+			}
+		}
+		++pr_j;
+		if (++pr_stage == NST) pr_stage = 0;
+	};
+	int cs = 0;
+	uint32_t cpar = 0;
+	bool failed = false;
+	auto slot_wait = [&]() -> bool {
+		if (!failed && !__all_sync(0xffffffffu, mbar_wait_bounded(bar_w + 8 * cs, cpar))) failed = true;
+		return !failed;
+	};
+	auto slot_done = [&]() {
+		__syncwarp();
+		if (++cs == NST) {
+			cs = 0;
+			cpar ^= 1u;
+		}
+		produce();
+	};
+	__syncwarp();
+#pragma unroll 1
+	for (int s = 0; s < NST; ++s) produce();
+	// first half of a cluster barrier whose second half sits in front of the exchange: no CTA writes into a peer's
+	// shared memory before every CTA of the cluster is running
+	asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+
+	// ---- before the dependency wait: zero / scale strips of the CTA's chunks and columns, rotary table entry ----
+	{
+		const int nz = p.N >> 3;
+#pragma unroll 1
+		for (int i = tid; i < nc * 48; i += QA_THREADS) {
+			const int cl = i / 48, u = i - cl * 48;                       // unit of 8 of the head's 384 columns
+			const int n = (u >> 4) * p.sec_stride + head * QA_D + (u & 15) * 8;
+			const int g = ((rank * nc + cl) * 128) / p.groupsize;
+			const uint32_t zv = (uint32_t)__ldg(p.qz + (size_t)g * nz + (n >> 3));
+			const uint4 sv = __ldg(reinterpret_cast<const uint4 *>(p.sc + (size_t)g * p.N + n));
+			uint4 ze;          // zero point (stored + 1) as fp16, two per word: (0x6401 + nibble) - 1024
+			ze.x = h2_sub(0x64016401u + ((zv & 0xFu) | ((zv & 0xF0u) << 12)), MAGIC_1024);
+			ze.y = h2_sub(0x64016401u + (((zv >> 8) & 0xFu) | (((zv >> 8) & 0xF0u) << 12)), MAGIC_1024);
+			ze.z = h2_sub(0x64016401u + (((zv >> 16) & 0xFu) | (((zv >> 16) & 0xF0u) << 12)), MAGIC_1024);
+			ze.w = h2_sub(0x64016401u + (((zv >> 24) & 0xFu) | (((zv >> 24) & 0xF0u) << 12)), MAGIC_1024);
+			*reinterpret_cast<uint4 *>(s_zz + (size_t)cl * QA_COLS + u * 8) = ze;
+			*reinterpret_cast<uint4 *>(s_sc + (size_t)cl * QA_COLS + u * 8) = sv;
+		}
+	}
+	float rc = 1.f, rs = 0.f;
+	if (tid < QA_D) {
+		rc = __half2float(__ldg(p.cos_t + (size_t)n_old * QA_D + tid));
+		rs = __half2float(__ldg(p.sin_t + (size_t)n_old * QA_D + tid));
+	}
+	uint4 wq = make_uint4(0u, 0u, 0u, 0u);
+	const int units = nc * 16;                                            // 16-byte units of the CTA's K-slice of x
+	const bool rms = p.rms_w != nullptr;
+	if (rms && tid < units) wq = __ldg(reinterpret_cast<const uint4 *>(p.rms_w + (rank * nc * 16 + tid) * 8));
+
+	pdl_wait();                                   // x (and the sums of squares) come from the kernel before this one
+
+	// ---- stage the K-slice of x (RMSNorm folded in), per-chunk sums of the staged values ----
+	if (rms) {
+		if (warp == 0) {
+			float t = 0.f;
+#pragma unroll 4
+			for (int i = lane; i < p.ss_tiles; i += 32) t += __ldcg(p.ss_in + i);
+#pragma unroll
+			for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
+			if (lane == 0) s_inv = rsqrtf(t / (float)p.K + p.rms_eps);
+		}
+		__syncthreads();
+	}
+	if (tid < 128) {                              // whole warps 0..3 (units <= 128): the shuffles below stay inside half-warps
+		float e = 0.f, o = 0.f;
+		if (tid < units) {
+			uint4 t = __ldcg(reinterpret_cast<const uint4 *>(p.x + (rank * nc * 16 + tid) * 8));
+			if (rms) {
+				const float inv = s_inv;
+				const uint32_t tv[4] = {t.x, t.y, t.z, t.w}, wv[4] = {wq.x, wq.y, wq.z, wq.w};
+				uint32_t ov[4];
+#pragma unroll
+				for (int i = 0; i < 4; ++i) {
+					const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&tv[i]));
+					const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(&wv[i]));
+					const __half2 h = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);      // x * inv_rms * w, one rounding
+					ov[i] = *reinterpret_cast<const uint32_t *>(&h);
+				}
+				t = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+			}
+			uint4 st;          // k order 0,4,1,5,2,6,3,7, the (1,5) and (3,7) pairs divided by 16
+			st.x = __byte_perm(t.x, t.z, 0x5410);
+			st.y = h2_mul(__byte_perm(t.x, t.z, 0x7632), 0x2C002C00u);
+			st.z = __byte_perm(t.y, t.w, 0x5410);
+			st.w = h2_mul(__byte_perm(t.y, t.w, 0x7632), 0x2C002C00u);
+			*reinterpret_cast<uint4 *>(xs + tid * 16) = st;
+			const float2 a0 = __half22float2(*reinterpret_cast<const __half2 *>(&st.x)), a1 = __half22float2(*reinterpret_cast<const __half2 *>(&st.y));
+			const float2 a2 = __half22float2(*reinterpret_cast<const __half2 *>(&st.z)), a3 = __half22float2(*reinterpret_cast<const __half2 *>(&st.w));
+			e = (a0.x + a0.y) + (a2.x + a2.y);
+			o = (a1.x + a1.y) + (a3.x + a3.y);
+		}
+#pragma unroll
+		for (int d = 1; d < 16; d <<= 1) {        // the 16 units of a chunk sit in one half-warp
+			e += __shfl_xor_sync(0xffffffffu, e, d);
+			o += __shfl_xor_sync(0xffffffffu, o, d);
+		}
+		if ((tid & 15) == 0 && tid < units) s_cs[tid >> 4] = make_float2(1024.f * (e + o), e + 16.f * o);
+	}
+	__syncthreads();
+
+	// ---- phase 1: this warp's weight chunks ----
+	{
+		const int row_a = 2 * tig, row_b = 2 * tig + 1;
+		const uint32_t ring_even = ring_w + row_a * 128 + ((gid ^ row_a) << 4);
+		const uint32_t ring_odd = ring_w + row_b * 128 + ((gid ^ row_b) << 4);
+		const bool have_row0 = gid == 0;                                // one batch row
+#pragma unroll 1
+		for (int i = 0; i < n_wloads; ++i) {
+			const int j = warp + 8 * i, cl = j / 12, strip = j - cl * 12;
+			float g[4][2];
+#pragma unroll
+			for (int c = 0; c < 4; ++c) g[c][0] = g[c][1] = 0.f;
+			if (!slot_wait()) break;
+			const uint32_t ring_c = cs * QA_SLOT;
+			const unsigned char *xc = xs + cl * 256 + tig * 32;
+#pragma unroll
+			for (int l = 0; l < 4; ++l) {
+				uint4 q;
+				asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+							 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+							 : "r"(((l & 1) ? ring_odd : ring_even) + ring_c + (l >> 1) * 1024));
+				uint4 xb0 = make_uint4(0u, 0u, 0u, 0u);
+				if (have_row0) xb0 = *reinterpret_cast<const uint4 *>(xc + ((l & 1) + 8 * (l >> 1)) * 16);
+				const uint32_t qv[4] = {q.x, q.y, q.z, q.w};
+				uint32_t a04[4], a15[4], a26[4], a37[4];
+#pragma unroll
+				for (int c = 0; c < 4; ++c) {
+					const uint32_t w = qv[c], w8 = w >> 8;
+					a04[c] = lop3_and_or(w, MASK_LO, MAGIC_1024);
+					a15[c] = lop3_and_or(w, MASK_HI, MAGIC_1024);
+					a26[c] = lop3_and_or(w8, MASK_LO, MAGIC_1024);
+					a37[c] = lop3_and_or(w8, MASK_HI, MAGIC_1024);
+				}
+#pragma unroll
+				for (int pr = 0; pr < 2; ++pr) {
+					float(&d0)[4] = *reinterpret_cast<float(*)[4]>(&g[2 * pr][0]);
+					mma16816(d0, a04[2 * pr], a04[2 * pr + 1], a15[2 * pr], a15[2 * pr + 1], xb0.x, xb0.y);
+					mma16816(d0, a26[2 * pr], a26[2 * pr + 1], a37[2 * pr], a37[2 * pr + 1], xb0.z, xb0.w);
+				}
+			}
+			slot_done();
+			if (tig == 0) {                       // batch row 0: columns strip * 32 + 4 * gid + 0..3
+				const int col = strip * 32 + gid * 4;
+				const float2 csv = s_cs[cl];
+				const uint2 zr = *reinterpret_cast<const uint2 *>(s_zz + (size_t)cl * QA_COLS + col);
+				const uint2 sr = *reinterpret_cast<const uint2 *>(s_sc + (size_t)cl * QA_COLS + col);
+				const float2 z01 = __half22float2(*reinterpret_cast<const __half2 *>(&zr.x)), z23 = __half22float2(*reinterpret_cast<const __half2 *>(&zr.y));
+				const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.x)), s23 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.y));
+				float4 o;
+				o.x = s01.x * (g[0][0] - fmaf(z01.x, csv.y, csv.x));
+				o.y = s01.y * (g[1][0] - fmaf(z01.y, csv.y, csv.x));
+				o.z = s23.x * (g[2][0] - fmaf(z23.x, csv.y, csv.x));
+				o.w = s23.y * (g[3][0] - fmaf(z23.y, csv.y, csv.x));
+				*reinterpret_cast<float4 *>(s_part + (size_t)cl * QA_COLS + col) = o;
+			}
+		}
+	}
+	__syncthreads();
+
+	// ---- exchange: q to every CTA of the cluster, k and v to the last one ----
+	asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+	{
+		const uint32_t gather_local = smem_u32(s_gather + (size_t)rank * QA_COLS);
+#pragma unroll 1
+		for (int t = tid; t < QA_COLS; t += QA_THREADS) {
+			float v = 0.f;
+#pragma unroll 1
+			for (int cl = 0; cl < nc; ++cl) v += s_part[(size_t)cl * QA_COLS + t];
+			if (t < QA_D) {
+#pragma unroll
+				for (uint32_t r = 0; r < QA_CLUSTER; ++r) qa_st_peer(qa_map_peer(gather_local + t * 4, r), v);
+			} else {
+				qa_st_peer(qa_map_peer(gather_local + t * 4, QA_CLUSTER - 1), v);
+			}
+		}
+	}
+	qa_cluster_sync();
+	const bool last = rank == QA_CLUSTER - 1;
+	if (tid < QA_D) {
+		float qv = 0.f, kv = 0.f, vv = 0.f;
+#pragma unroll
+		for (int r = 0; r < QA_CLUSTER; ++r) qv += s_gather[(size_t)r * QA_COLS + tid];
+		if (last) {
+#pragma unroll
+			for (int r = 0; r < QA_CLUSTER; ++r) {
+				kv += s_gather[(size_t)r * QA_COLS + QA_D + tid];
+				vv += s_gather[(size_t)r * QA_COLS + 2 * QA_D + tid];
+			}
+		}
+		// rotate-half through shared memory: out[d] = x[d] cos - x[d+64] sin (d < 64), x[d] cos + x[d-64] sin (d >= 64)
+		s_wo[tid] = qv;
+		s_wo[QA_D + tid] = kv;
+		s_wo[2 * QA_D + tid] = vv;
+	}
+	__syncthreads();
+	if (tid < QA_D) {
+		const int d = tid;
+		const float sgn = (d < 64) ? -rs : rs;
+		s_q[d] = __half2float(__float2half_rn(fmaf(s_wo[d ^ 64], sgn, s_wo[d] * rc))) * p.scale;
+		if (last) {
+			const __half kh = __float2half_rn(fmaf(s_wo[QA_D + (d ^ 64)], sgn, s_wo[QA_D + d] * rc)), vh = __float2half_rn(s_wo[2 * QA_D + d]);
+			s_kn[d] = kh;
+			s_vn[d] = vh;
+			if (pos >= 0) {
+				const size_t off = (size_t)head * p.kv_stride_h + (size_t)pos * QA_D + d;
+				p.kc[off] = kh;
+				p.vc[off] = vh;
+			}
+		}
+	}
+	__syncthreads();
+
+	// ---- phase 2: attention over this warp's keys; 8 lanes per key, a group takes keys g8 and g8 + 4 of a chunk ----
+	const int g8 = lane >> 3, sub = lane & 7, rotp = sub >> 2;
+	float qreg[2][8];
+#pragma unroll
+	for (int i = 0; i < 2; ++i)
+#pragma unroll
+		for (int e = 0; e < 8; ++e) qreg[i][e] = s_q[sub * 16 + ((i + rotp) & 1) * 8 + e];
+	float m = -INFINITY, l = 0.f, acc[2][8];
+#pragma unroll
+	for (int i = 0; i < 2; ++i)
+#pragma unroll
+		for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+	{
+		const int nchunk = (nkeys + 7) >> 3;
+		const int n_iter = nchunk + ((last && warp == 0 && pos >= 0) ? 1 : 0);      // + the token's own key / value from shared memory
+		const int row_off = g8 * (QA_D * 2) + sub * 32;
+#pragma unroll 1
+		for (int c = 0; c < n_iter; ++c) {
+			const bool from_ring = c < nchunk;
+			const int rows = from_ring ? min(8, nkeys - 8 * c) : 1;
+			float sc[2] = {0.f, 0.f};
+			if (from_ring && !slot_wait()) break;
+			{
+				const unsigned char *kp = (from_ring ? smem + (size_t)warp * NST * QA_SLOT + cs * QA_SLOT : reinterpret_cast<const unsigned char *>(s_kn)) + row_off;
+#pragma unroll
+				for (int h = 0; h < 2; ++h) {
+					if (g8 + 4 * h < rows) {
+#pragma unroll
+						for (int i = 0; i < 2; ++i) {
+							const uint4 kv4 = *reinterpret_cast<const uint4 *>(kp + h * 4 * (QA_D * 2) + ((i + rotp) & 1) * 16);
+							const __half2 *kh = reinterpret_cast<const __half2 *>(&kv4);
+#pragma unroll
+							for (int e = 0; e < 4; ++e) {
+								const float2 f = __half22float2(kh[e]);
+								sc[h] = fmaf(qreg[i][2 * e], f.x, fmaf(qreg[i][2 * e + 1], f.y, sc[h]));
+							}
+						}
+					}
+					sc[h] += __shfl_xor_sync(0xffffffffu, sc[h], 1);
+					sc[h] += __shfl_xor_sync(0xffffffffu, sc[h], 2);
+					sc[h] += __shfl_xor_sync(0xffffffffu, sc[h], 4);
+				}
+			}
+			if (from_ring) {
+				slot_done();
+				if (!slot_wait()) break;
+			}
+			{
+				const unsigned char *vp = (from_ring ? smem + (size_t)warp * NST * QA_SLOT + cs * QA_SLOT : reinterpret_cast<const unsigned char *>(s_vn)) + row_off;
+#pragma unroll
+				for (int h = 0; h < 2; ++h) {
+					if (g8 + 4 * h < rows) {
+						const float mn = fmaxf(m, sc[h]);
+						const float corr = __expf(m - mn), pw = __expf(sc[h] - mn);
+						l = l * corr + pw;
+#pragma unroll
+						for (int i = 0; i < 2; ++i) {
+							const uint4 vv4 = *reinterpret_cast<const uint4 *>(vp + h * 4 * (QA_D * 2) + ((i + rotp) & 1) * 16);
+							const __half2 *vh = reinterpret_cast<const __half2 *>(&vv4);
+#pragma unroll
+							for (int e = 0; e < 4; ++e) {
+								const float2 f = __half22float2(vh[e]);
+								acc[i][2 * e] = fmaf(pw, f.x, acc[i][2 * e] * corr);
+								acc[i][2 * e + 1] = fmaf(pw, f.y, acc[i][2 * e + 1] * corr);
+							}
+						}
+						m = mn;
+					}
+				}
+			}
+			if (from_ring) slot_done();
+		}
+	}
+	if (failed && lane == 0) atomicExch(p.status, 1);          // a load never arrived
+	// merge the 4 key slots of the warp (lane bits 3, 4), then the 8 warps through shared memory
+	{
+		float mw = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+		mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, 16));
+		const float f = (m == -INFINITY) ? 0.f : __expf(m - mw);
+		l *= f;
+		l += __shfl_xor_sync(0xffffffffu, l, 8);
+		l += __shfl_xor_sync(0xffffffffu, l, 16);
+		__syncthreads();                          // s_wo was the rotary scratch
+#pragma unroll
+		for (int i = 0; i < 2; ++i) {
+			const int piece = (i + rotp) & 1;
+#pragma unroll
+			for (int e = 0; e < 8; ++e) {
+				float av = acc[i][e] * f;
+				av += __shfl_xor_sync(0xffffffffu, av, 8);
+				av += __shfl_xor_sync(0xffffffffu, av, 16);
+				if (g8 == 0) s_wo[warp * QA_D + sub * 16 + piece * 8 + e] = av;
+			}
+		}
+		if (lane == 0) {
+			s_wm[warp] = mw;
+			s_wl[warp] = l;
+		}
+	}
+	__syncthreads();
+	// ---- merge of the cluster: every CTA's (max, sum, outputs) to CTA 0 ----
+	if (tid < QA_D) {
+		float Mx = -INFINITY;
+#pragma unroll
+		for (int w = 0; w < 8; ++w) Mx = fmaxf(Mx, s_wm[w]);
+		float o = 0.f, Lx = 0.f;
+#pragma unroll
+		for (int w = 0; w < 8; ++w) {
+			const float g = (s_wm[w] == -INFINITY) ? 0.f : __expf(s_wm[w] - Mx);
+			o = fmaf(s_wo[w * QA_D + tid], g, o);
+			Lx = fmaf(s_wl[w], g, Lx);
+		}
+		const uint32_t dst = qa_map_peer(smem_u32(s_merge + (size_t)rank * 130), 0);
+		qa_st_peer(dst + (2 + tid) * 4, o);
+		if (tid == 0) {
+			qa_st_peer(dst, Mx);
+			qa_st_peer(dst + 4, Lx);
+		}
+	}
+	qa_cluster_sync();
+	if (rank == 0 && tid < QA_D) {
+		float Mg = -INFINITY;
+#pragma unroll
+		for (int r = 0; r < QA_CLUSTER; ++r) Mg = fmaxf(Mg, s_merge[r * 130]);
+		float Lg = 0.f, og = 0.f;
+#pragma unroll
+		for (int r = 0; r < QA_CLUSTER; ++r) {
+			const float ms = s_merge[r * 130];
+			const float w = (ms == -INFINITY) ? 0.f : __expf(ms - Mg);
+			Lg = fmaf(s_merge[r * 130 + 1], w, Lg);
+			og = fmaf(s_merge[r * 130 + 2 + tid], w, og);
+		}
+		p.out[head * QA_D + tid] = __float2half_rn(Lg > 0.f ? og / Lg : 0.f);
+	}
+}
+
+}   // namespace gptq

@@ -225,6 +225,43 @@ class QuantLlamaAttention(nn.Module):
 		return attn_output, attn_weights, past_key_value
 
 
+def qkv_attn_supported(K: int, n_heads: int, head_dim: int, groupsize: int) -> bool:
+	"""True when one sequence's decode step can run QKV projection + rotary + cache append + attention as one kernel."""
+	return bool(_lib.lib().gptq_qkv_attn_supported(K, n_heads, head_dim, groupsize))
+
+
+def qkv_attn_decode(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin, pos: torch.Tensor, kcache: torch.Tensor,
+					vcache: torch.Tensor, n_heads: int, rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6,
+					sumsq_in: Optional[torch.Tensor] = None) -> torch.Tensor:
+	"""One sequence, one new token: attention output [1, 1, n_heads * 128] from the hidden state `a` [1, 1, K].
+
+	One kernel does what QuantLlamaAttention.forward does up to o_proj (fused_attention.py:79-146 of the reference):
+	a x deq(Wqkv), rotary on q and k, K / V row written to the static cache at `pos`, softmax(q K^T / sqrt(d)) V over
+	positions 0..pos.  A cluster of 8 CTAs per head splits the K dimension of the projection and the keys of the
+	attention, and exchanges q / k / v and the softmax partials through distributed shared memory.
+	With rms_weight, `a` is RMS-normalised inside the kernel from `sumsq_in` (fp32 [K // 32], left by the projection
+	that produced `a`).  pos: int32 [1] on the device.
+	"""
+	_lib.require_cuda(a, qweight, scales, qzeros, cos, sin, pos, kcache, vcache)
+	K = a.shape[-1]
+	assert a.numel() == K and a.is_contiguous() and a.dtype == torch.float16
+	assert pos.dtype == torch.int32 and pos.numel() == 1
+	assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape == vcache.shape and kcache.shape[-3] == n_heads and kcache.shape[-1] == 128
+	S = kcache.shape[-2]
+	assert (rms_weight is None) == (sumsq_in is None)
+	if sumsq_in is not None:
+		assert sumsq_in.dtype == torch.float32 and sumsq_in.is_contiguous() and sumsq_in.numel() >= K // 32
+	out = torch.empty((1, 1, n_heads * 128), dtype=torch.float16, device=a.device)
+	ws = _lib.workspace(a.device, 1, K, 3 * n_heads * 128)
+	rc = _lib.lib().gptq_qkv_attn_decode(
+		_lib.ptr(a), _lib.ptr(qweight), _lib.ptr(qzeros), _lib.ptr(scales), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), min(cos.shape[0], S),
+		_lib.ptr(kcache), _lib.ptr(vcache), S * 128, _lib.ptr(out), K, n_heads, 128, groupsize, 1.0 / math.sqrt(128),
+		_lib.ptr(rms_weight) if rms_weight is not None else None, _lib.ptr(sumsq_in) if sumsq_in is not None else None, K // 32, float(rms_eps),
+		_lib.ptr(ws), ws.numel(), _lib.stream_ptr(a.device))
+	_lib.check(rc, 'gptq_qkv_attn_decode')
+	return out
+
+
 def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: torch.Tensor, len_hint: int) -> torch.Tensor:
 	"""Attention of one new token per sequence over a static cache.
 	q [b, heads, 1, 128] or [b, 1, heads, 128] memory as produced by qkv_rope (any view whose

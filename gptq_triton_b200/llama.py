@@ -21,7 +21,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .fused_attention import QuantLlamaAttention, attn_decode
+from .fused_attention import QuantLlamaAttention, attn_decode, qkv_attn_decode, qkv_attn_supported
 from .fused_attention import rmsnorm as rmsnorm_kernel
 from .fused_mlp import QuantLlamaMLP
 from .tp import all_reduce_
@@ -226,6 +226,7 @@ class DecodeEngine:
 		self.len_hint = max_seq
 		self.graph = None
 		self.launches_per_step = None
+		self.used_qkv_attn = False          # set when a decode step ran the one-kernel QKV + attention path
 		self.next_pos = 0          # host-side copy of the position the next step() writes (the cache has max_seq rows)
 		# One persistent kernel per decode step (gptq_decode_chain) + the lm_head / arg-max kernel, where the model
 		# allows it (one GPU, batch <= 8, no act-order, no bias, one group size); opt-in with GPTQ_B200_CHAIN=1 (default: the
@@ -324,7 +325,17 @@ class DecodeEngine:
 		# hidden state (and its sums of squares); with NCCL the norms stay separate kernels
 		fused_ar = decode and self.ar_o is not None and b <= 16
 		fold = self.fuse_norm and decode and (self.tp_world == 1 or fused_ar) and b <= 16 and self.cfg.hidden_size % 128 == 0 and self.cfg.hidden_size // 32 <= 256
-		if x_normed is not None:
+		o = None
+		if decode and b == 1 and self.batch == 1 and self._one_kernel_attention(attn) and (x_normed is not None or (fold and ss_in is not None)):
+			# one sequence: projection, rotary, cache append and attention in one kernel (a cluster of 8 CTAs per head)
+			self.used_qkv_attn = True
+			qw, _, _ = attn.qkv_proj.kernel_operands()
+			cos, sin = attn.tables(h.device, self.max_seq)
+			src = x_normed if x_normed is not None else h.contiguous()
+			o = qkv_attn_decode(attn.qkv_proj.groupsize, src, qw, attn.qkv_proj.scales, attn.qkv_proj.qzeros, cos, sin, pos.view(-1), self.kcache[i],
+								self.vcache[i], attn.num_heads, rms_weight=None if x_normed is not None else ln1.weight,
+								rms_eps=ln1.variance_epsilon, sumsq_in=None if x_normed is not None else ss_in)
+		elif x_normed is not None:
 			q, _, _ = attn.project_qkv(x_normed, pos, kv_cache=(self.kcache[i], self.vcache[i]))
 		elif fold:
 			q, _, _ = attn.project_qkv(h.contiguous(), pos, kv_cache=(self.kcache[i], self.vcache[i]), rms_weight=ln1.weight,
@@ -332,7 +343,9 @@ class DecodeEngine:
 		else:
 			x = rmsnorm_kernel(h.contiguous(), ln1.weight, ln1.variance_epsilon)
 			q, _, _ = attn.project_qkv(x, pos, kv_cache=(self.kcache[i], self.vcache[i]))
-		if decode:
+		if o is not None:
+			pass
+		elif decode:
 			# own single-query kernel over the static cache (length read from `pos` on the device)
 			o = attn_decode(q, self.kcache[i], self.vcache[i], pos, self.len_hint)
 		else:
@@ -386,6 +399,17 @@ class DecodeEngine:
 		self.mask.fill_(float('-inf'))
 		self.mask[..., :t + 1] = 0
 		return self.tok.clone()
+
+	def _one_kernel_attention(self, attn) -> bool:
+		"""Whether the layer's QKV projection and attention run as one kernel in a decode step of one sequence
+		(plain group layout, no bias, head_dim 128, hidden a multiple of 1024; GPTQ_B200_QKV_ATTN=0 turns it off)."""
+		if os.environ.get('GPTQ_B200_QKV_ATTN', '1') == '0':
+			return False
+		qp = attn.qkv_proj
+		_, g_idx, perm = qp.kernel_operands()
+		if g_idx is not None or perm is not None or qp.bias is not None or attn.head_dim != 128:
+			return False
+		return qkv_attn_supported(qp.infeatures, attn.num_heads, attn.head_dim, qp.groupsize)
 
 	def _own_ends(self):
 		"""Buffers for the first and last kernel of a decode step when both ends run as own kernels: embedding

@@ -153,6 +153,28 @@ int gptq_attn_decode(const void *q, int64_t q_stride_b, const void *kcache, cons
                      int len_hint, float scale, void *workspace, size_t workspace_bytes,
                      gptq_stream_t stream);
 
+/*
+ * One sequence, one new token: QKV projection + rotary + KV-cache append + single-query attention in ONE kernel.
+ * Replaces, for that case, the pair gptq_qkv_rope(_rms) + gptq_attn_decode, i.e. QuantLlamaAttention.forward up to
+ * o_proj (src/gptq_triton/fused_attention.py:79-146: fused qkv_proj, rotary on q and k, cache concat, QK^T / sqrt(d),
+ * fp32 softmax, .V).  A thread-block cluster of 8 CTAs per head splits the K dimension of the projection and the keys
+ * of the attention; q / k / v and the softmax partials cross between the CTAs in distributed shared memory.
+ * x fp16 [K]; qweight int32 [K/8, 3*n_heads*128] (q, k, v sections of n_heads*128 columns), qzeros, scales as for
+ * gptq_qmatmul (no g_idx / perm); cos, sin fp16 [>= max_pos, 128]; pos int32 [1] on the device = keys already cached
+ * (a value outside [0, max_pos) sets status 4, drops the K / V row and attends to nothing); kcache / vcache fp16
+ * [n_heads, max_seq, 128] with kv_stride_h elements between heads; out fp16 [n_heads*128].
+ * rms_weight (optional, fp16 [K]) with sumsq_in (fp32 [sumsq_tiles], sums of squares of x per 32 columns): x is
+ * RMS-normalised inside the kernel.  Needs K % 1024 == 0, K <= 8192, head_dim == 128, groupsize % 128 == 0
+ * (gptq_qkv_attn_supported); workspace: the one of gptq_qmatmul (only its status word is used).
+ */
+int gptq_qkv_attn_supported(int K, int n_heads, int head_dim, int groupsize);
+int gptq_qkv_attn_decode(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales,
+                         const void *cos, const void *sin, const int32_t *pos, int max_pos, void *kcache,
+                         void *vcache, int64_t kv_stride_h, void *out, int K, int n_heads, int head_dim,
+                         int groupsize, float scale, const void *rms_weight, const float *sumsq_in,
+                         int sumsq_tiles, float rms_eps, void *workspace, size_t workspace_bytes,
+                         gptq_stream_t stream);
+
 /* y = x * rsqrt(mean(x^2) + eps) * weight, per row, fp32 inside.  The RMSNorm that the HF
  * decoder layer applies in front of the attention and MLP blocks (third-party code the
  * reference model is built from, src/gptq_triton/__init__.py:47). */
