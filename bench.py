@@ -562,7 +562,7 @@ def gpu_arm(args):
 	if want4 and not big and not args.layers:
 		launches_7b = None
 		chain_used = engine.chain is not None
-		qa_used = engine.used_qkv_attn
+		qa_used = int(engine.used_qkv_attn) + int(engine.used_fused_oproj)
 		fused_ar = engine.ar_o is not None
 		folded_7b = engine.fuse_norm and batch <= 16 and (world == 1 or engine.ar_o is not None)
 		barrier()
@@ -573,27 +573,27 @@ def gpu_arm(args):
 		engine = None
 	else:
 		chain_used = engine.chain is not None
-		qa_used = engine.used_qkv_attn
+		qa_used = int(engine.used_qkv_attn) + int(engine.used_fused_oproj)
 		fused_ar = engine.ar_o is not None
 		folded_7b = engine.fuse_norm and batch <= 16 and (world == 1 or engine.ar_o is not None)
 
 	rc = 0
 	if rank == 0:
 		# own kernels per rank and step: 4 quantised matmuls + attention per layer (batch 1: the QKV projection and the attention
-		# are one kernel), embedding + first norm in one kernel,
+		# and on one GPU also o_proj are one kernel), embedding + first norm in one kernel,
 		# final norm + lm_head + arg-max in one kernel; RMSNorm is otherwise folded into the matmul kernels.  The persistent
 		# kernel path: one chain kernel + lm_head.
 		if chain_used:
 			launches_per_step = 2
 		else:
-			launches_per_step = ((4 if qa_used else 5) * cfg.num_hidden_layers + 2) if folded_7b else (7 * cfg.num_hidden_layers + 1)
+			launches_per_step = ((5 - qa_used) * cfg.num_hidden_layers + 2) if folded_7b else (7 * cfg.num_hidden_layers + 1)
 		line = {
 			'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
 			'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16',
 			'data': 'synthetic',
 			'config': {'workload': WORKLOAD if not big else 'llama65b-arch 4-bit g128 greedy decode, batch 16, 2048-token prompts', 'layers': cfg.num_hidden_layers, 'hidden': cfg.hidden_size, 'groupsize': GROUPSIZE,
 					   'parallelism': (('tp%d: QKV and gate/up by columns, o_proj and down by rows, ' % world) + ('all-reduce fused into those kernels over peer memory' if fused_ar else 'one NCCL all-reduce after each')) if world > 1 else 'single GPU',
-					   'step': 'persistent chain kernel' if chain_used else ('QKV projection + attention in one kernel, one kernel per other projection, CUDA graph' if qa_used else 'one kernel per projection, CUDA graph'),
+					   'step': 'persistent chain kernel' if chain_used else (('attention block (QKV projection, rotary, attention, o_proj, residual) in one kernel, gate/up and down_proj one kernel each, CUDA graph' if qa_used == 2 else 'QKV projection + attention in one kernel, one kernel per other projection, CUDA graph') if qa_used else 'one kernel per projection, CUDA graph'),
 					   'l2': 'inputs larger than L2: 3.6 GB of weights + KV cache are streamed every step'},
 			'e2e': {'value': e2e_tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 8 * batch, 'd2h_bytes_per_step': 8 * batch},
 			'gpu_launches': launches_per_step * args.steps,

@@ -202,6 +202,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 			score -= 0.02 * std::max(0, 4 - nstage);
 			if (cps < kwarps) score -= 0.25;
 			if (kwarps == 4) score -= 0.03;
+			if (eff > 8) score -= 0.15;      // measured (7B down_proj, 11008 -> 4096): 8 splits 9.6 us, 9 splits 10.9 us
 			if (score > best_score) {
 				best_score = score;
 				best_sk = sk;
@@ -567,6 +568,8 @@ static size_t qkv_attn_layout(QkvAttnParams &p) {
 	p.off_merge = (int)o; o += (size_t)QA_CLUSTER * 130 * 4;
 	o = (o + 15) & ~(size_t)15;
 	p.off_attn = (int)o; o += QA_D * 4 + 2 * QA_D * 2 + 8 * QA_D * 4 + 64;
+	p.off_o = (int)o;
+	if (p.o_enable) o += 256 + 2 * 256 * 4 * 2;      // staged attention output, zero / scale strips of up to 1024 o_proj columns
 	return o;
 }
 
@@ -578,16 +581,32 @@ int gptq_qkv_attn_supported(int K, int n_heads, int head_dim, int groupsize) {
 	return 1;
 }
 
-int gptq_qkv_attn_decode(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const void *cos, const void *sin,
+size_t gptq_qkv_attn_oproj_scratch_bytes(int n_heads, int N) {
+	if (n_heads <= 0 || N <= 0) return 0;
+	return 256 + (size_t)n_heads * N * sizeof(float);
+}
+
+// o: optional fused output projection
+struct QaOproj {
+	const int32_t *qweight, *qzeros;
+	const void *scales, *residual;
+	void *y;
+	float *sumsq_out;
+	int N, groupsize;
+	void *scratch;
+	size_t scratch_bytes;
+};
+
+static int qkv_attn_impl(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const void *cos, const void *sin,
 						 const int32_t *pos, int max_pos, void *kcache, void *vcache, int64_t kv_stride_h, void *out, int K, int n_heads,
 						 int head_dim, int groupsize, float scale, const void *rms_weight, const float *sumsq_in, int sumsq_tiles, float rms_eps,
-						 void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
-	if (!x || !qweight || !qzeros || !scales || !cos || !sin || !pos || !kcache || !vcache || !out) return GPTQ_ERR_INVALID;
+						 void *workspace, size_t workspace_bytes, gptq_stream_t stream, const QaOproj *o) {
+	if (!x || !qweight || !qzeros || !scales || !cos || !sin || !pos || !kcache || !vcache || (!out && !o)) return GPTQ_ERR_INVALID;
 	if (max_pos <= 0 || kv_stride_h < (int64_t)max_pos * QA_D) return GPTQ_ERR_INVALID;
 	if (groupsize == -1) groupsize = K;
 	if (!gptq_qkv_attn_supported(K, n_heads, head_dim, groupsize)) return GPTQ_ERR_UNSUPPORTED;
 	if (!aligned16(x) || !aligned16(qweight) || !aligned16(qzeros) || !aligned16(scales) || !aligned16(kcache) || !aligned16(vcache) ||
-		!aligned16(out) || kv_stride_h % 8)
+		(out && !aligned16(out)) || kv_stride_h % 8)
 		return GPTQ_ERR_ALIGN;
 	if (rms_weight && (!sumsq_in || sumsq_tiles <= 0 || !aligned16(rms_weight))) return GPTQ_ERR_INVALID;
 	if (!workspace || workspace_bytes < (size_t)SK_TICKET_BYTES) return GPTQ_ERR_WORKSPACE;
@@ -600,6 +619,26 @@ int gptq_qkv_attn_decode(const void *x, const int32_t *qweight, const int32_t *q
 	p.kc = (__half *)kcache; p.vc = (__half *)vcache; p.kv_stride_h = kv_stride_h;
 	p.scale = scale; p.out = (__half *)out;
 	p.status = reinterpret_cast<int *>(workspace) + SK_STATUS_SLOT;
+	CUtensorMap tm, tmo;
+	if (int rc = weight_tensor_map(qweight, K, p.N, &tm)) return rc;
+	tmo = tm;
+	if (o) {
+		int ogs = o->groupsize == -1 ? n_heads * QA_D : o->groupsize;
+		if (!o->qweight || !o->qzeros || !o->scales || !o->y || !o->scratch) return GPTQ_ERR_INVALID;
+		if (o->N <= 0 || o->N % 32 != 0 || o->N > 8192 || ogs <= 0 || ogs % 128 != 0 || (n_heads * QA_D) % ogs != 0) return GPTQ_ERR_UNSUPPORTED;
+		if (!aligned16(o->qweight) || !aligned16(o->qzeros) || !aligned16(o->scales) || !aligned16(o->y) || !aligned16(o->scratch) ||
+			(o->residual && !aligned16(o->residual)))
+			return GPTQ_ERR_ALIGN;
+		if (o->scratch_bytes < gptq_qkv_attn_oproj_scratch_bytes(n_heads, o->N)) return GPTQ_ERR_WORKSPACE;
+		p.o_enable = 1; p.o_N = o->N; p.o_groupsize = ogs;
+		p.o_spw = (o->N / 32 + 63) / 64;
+		if (p.o_spw == 3) p.o_spw = 4;          // the reduction divides 256 threads by 64 spw column quads
+		p.o_qz = o->qzeros; p.o_sc = (const __half *)o->scales; p.o_res = (const __half *)o->residual;
+		p.o_tickets = reinterpret_cast<int *>(o->scratch);
+		p.o_part = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(o->scratch) + 256);
+		p.o_y = (__half *)o->y; p.o_ss = o->sumsq_out;
+		if (int rc = weight_tensor_map(o->qweight, n_heads * QA_D, o->N, &tmo)) return rc;
+	}
 	const size_t smem = qkv_attn_layout(p);
 	if (smem > (size_t)SK_SMEM_LIMIT - 2048) return GPTQ_ERR_UNSUPPORTED;
 	{
@@ -612,9 +651,27 @@ int gptq_qkv_attn_decode(const void *x, const int32_t *qweight, const int32_t *q
 			ready[dev] = true;
 		}
 	}
-	CUtensorMap tm;
-	if (int rc = weight_tensor_map(qweight, K, p.N, &tm)) return rc;
-	return launch_ex(qkv_attn_kernel, dim3(QA_CLUSTER, n_heads, 1), dim3(QA_THREADS, 1, 1), smem, reinterpret_cast<cudaStream_t>(stream), tm, p);
+	return launch_ex(qkv_attn_kernel, dim3(QA_CLUSTER, n_heads, 1), dim3(QA_THREADS, 1, 1), smem, reinterpret_cast<cudaStream_t>(stream), tm, tmo, p);
+}
+
+int gptq_qkv_attn_decode(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const void *cos, const void *sin,
+						 const int32_t *pos, int max_pos, void *kcache, void *vcache, int64_t kv_stride_h, void *out, int K, int n_heads,
+						 int head_dim, int groupsize, float scale, const void *rms_weight, const float *sumsq_in, int sumsq_tiles, float rms_eps,
+						 void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+	if (!out) return GPTQ_ERR_INVALID;
+	return qkv_attn_impl(x, qweight, qzeros, scales, cos, sin, pos, max_pos, kcache, vcache, kv_stride_h, out, K, n_heads, head_dim, groupsize,
+						 scale, rms_weight, sumsq_in, sumsq_tiles, rms_eps, workspace, workspace_bytes, stream, nullptr);
+}
+
+int gptq_qkv_attn_oproj_decode(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const void *cos,
+							   const void *sin, const int32_t *pos, int max_pos, void *kcache, void *vcache, int64_t kv_stride_h, int K,
+							   int n_heads, int head_dim, int groupsize, float scale, const void *rms_weight, const float *sumsq_in,
+							   int sumsq_tiles, float rms_eps, const int32_t *o_qweight, const int32_t *o_qzeros, const void *o_scales,
+							   int o_N, int o_groupsize, const void *residual, void *y, float *sumsq_out, void *attn_out, void *scratch,
+							   size_t scratch_bytes, void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
+	QaOproj o = {o_qweight, o_qzeros, o_scales, residual, y, sumsq_out, o_N, o_groupsize, scratch, scratch_bytes};
+	return qkv_attn_impl(x, qweight, qzeros, scales, cos, sin, pos, max_pos, kcache, vcache, kv_stride_h, attn_out, K, n_heads, head_dim,
+						 groupsize, scale, rms_weight, sumsq_in, sumsq_tiles, rms_eps, workspace, workspace_bytes, stream, &o);
 }
 
 int gptq_rmsnorm(const void *x, int64_t ldx, const void *weight, void *y, int64_t ldy, int M, int K, float eps, gptq_stream_t stream) {

@@ -15,6 +15,10 @@
 //            the last one also to the token's own key; online softmax in fp32.
 //   merge    (max, sum, 128 outputs) of every CTA go to CTA 0 through distributed shared memory, cluster barrier,
 //            CTA 0 folds the eight partials in order and writes the head's 128 outputs as fp16.
+//   o_proj   (optional) every CTA receives the partials instead, forms the head's 128 outputs and multiplies them with its
+//            share of the head's 128 rows of the output projection (K-slice = head, columns split over the 8 CTAs); the
+//            per-head partial sums meet in global memory, where the last CTA to arrive for a column range adds them in
+//            head order, adds the residual and writes the new hidden state with its sums of squares.
 // RMSNorm of the input is folded in as in the decode kernels (sums of squares from the producing projection).
 // Deterministic: every sum runs in a fixed order.  Waits on the rings are bounded (status 1); the cluster barriers are
 // hardware barriers between CTAs that are scheduled together, and no CTA leaves before the last one.
@@ -50,7 +54,19 @@ struct QkvAttnParams {
 	float scale;
 	__half *out;                  // [heads * 128]
 	int *status;
-	int off_bars, off_xs, off_zz, off_sc, off_part, off_gather, off_merge, off_attn;     // shared-memory layout
+	int off_bars, off_xs, off_zz, off_sc, off_part, off_gather, off_merge, off_attn, off_o;     // shared-memory layout
+	// Optional third phase: the output projection (o_proj) of the block, y = residual + attn x deq(Wo).  The cluster of
+	// head h owns the K-slice h (rows 128 h .. 128 h + 127 of Wo); its CTA r the columns [256 spw r, 256 spw (r + 1)).
+	// Partial sums per head go to o_part [heads][o_N] (fp32); the last of the `heads` CTAs with the same r to arrive at
+	// o_tickets[r] adds them in head order, adds the residual, writes y (fp16) and the sums of squares of y per 32 columns.
+	int o_enable, o_N, o_groupsize, o_spw;          // o_spw: 32-column strips per warp = ceil(o_N / 32 / 64), at most 4
+	const int32_t *o_qz;
+	const __half *o_sc;
+	const __half *o_res;
+	float *o_part;
+	int *o_tickets;
+	__half *o_y;
+	float *o_ss;
 };
 
 __device__ __forceinline__ uint32_t qa_map_peer(uint32_t local_smem_addr, uint32_t rank) {
@@ -69,7 +85,7 @@ __device__ __forceinline__ void qa_bulk_load_1d(uint32_t dst, const void *src, u
 }
 
 __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS, 2)
-	qkv_attn_kernel(const __grid_constant__ CUtensorMap tmw, const QkvAttnParams p) {
+	qkv_attn_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ CUtensorMap tmo, const QkvAttnParams p) {
 	extern __shared__ __align__(1024) unsigned char smem[];
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
 	const int rank = blockIdx.x, head = blockIdx.y;            // cluster rank = K-slice = key split
@@ -94,6 +110,7 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 		for (int s = 0; s < NST; ++s) mbar_init(bar_w + 8 * s, 1);
 		fence_mbar_init();
 		if (warp == 0) tma_prefetch_desc(&tmw);
+		if (warp == 1 && p.o_enable) tma_prefetch_desc(&tmo);
 	}
 	pdl_trigger();
 	// the position comes from the previous decode step (several kernels ago), not from the kernel before this one
@@ -111,7 +128,10 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 	const int per_w = (((k_hi - k_lo) + 7) / 8 + 7) & ~7;
 	const int wk_lo = min(k_lo + warp * per_w, k_hi), wk_hi = min(wk_lo + per_w, k_hi);
 	const int nkeys = wk_hi - wk_lo, n_aloads = 2 * ((nkeys + 7) >> 3);
-	const int n_loads = n_wloads + n_aloads;
+	// o_proj: strips (rank * 8 + warp) * spw + j of the head's 128 rows of Wo
+	const int o_strip0 = (rank * 8 + warp) * p.o_spw;
+	const int n_oloads = p.o_enable ? max(0, min(p.o_spw, (p.o_N >> 5) - o_strip0)) : 0;
+	const int n_loads = n_wloads + n_aloads + n_oloads;
 	const __half *kb = p.kc + (size_t)head * p.kv_stride_h + (size_t)wk_lo * QA_D, *vb = p.vc + (size_t)head * p.kv_stride_h + (size_t)wk_lo * QA_D;
 	int pr_j = 0, pr_stage = 0;
 	auto produce = [&]() {
@@ -123,6 +143,9 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 				const int n0w = (strip >> 2) * p.sec_stride + head * QA_D + (strip & 3) * 32;
 				mbar_arrive_expect_tx(bar, QA_SLOT);
 				tma_load_2d(dst, &tmw, n0w, (rank * nc + cl) * 16, bar);
+			} else if (pr_j >= n_wloads + n_aloads) {
+				mbar_arrive_expect_tx(bar, QA_SLOT);
+				tma_load_2d(dst, &tmo, (o_strip0 + pr_j - n_wloads - n_aloads) * 32, head * 16, bar);
 			} else {
 				const int a = pr_j - n_wloads, c = a >> 1;
 				const uint32_t bytes = (uint32_t)min(8, nkeys - 8 * c) * (QA_D * 2);
@@ -172,6 +195,27 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 			ze.w = h2_sub(0x64016401u + (((zv >> 24) & 0xFu) | (((zv >> 24) & 0xF0u) << 12)), MAGIC_1024);
 			*reinterpret_cast<uint4 *>(s_zz + (size_t)cl * QA_COLS + u * 8) = ze;
 			*reinterpret_cast<uint4 *>(s_sc + (size_t)cl * QA_COLS + u * 8) = sv;
+		}
+	}
+	unsigned char *xs2 = smem + p.off_o;                                  // [256 B] attention output of the head, staged like xs
+	__half *s_ozz = reinterpret_cast<__half *>(xs2 + 256);                // [256 spw] zero point (stored + 1) of this CTA's o_proj columns
+	__half *s_osc = s_ozz + 256 * 4;                                      // [256 spw] scale
+	if (p.o_enable) {
+		const int nz = p.o_N >> 3, g = (head * QA_D) / p.o_groupsize;
+#pragma unroll 1
+		for (int i = tid; i < 32 * p.o_spw; i += QA_THREADS) {            // units of 8 columns
+			const int n = rank * 256 * p.o_spw + i * 8;
+			if (n < p.o_N) {
+				const uint32_t zv = (uint32_t)__ldg(p.o_qz + (size_t)g * nz + (n >> 3));
+				const uint4 sv = __ldg(reinterpret_cast<const uint4 *>(p.o_sc + (size_t)g * p.o_N + n));
+				uint4 ze;
+				ze.x = h2_sub(0x64016401u + ((zv & 0xFu) | ((zv & 0xF0u) << 12)), MAGIC_1024);
+				ze.y = h2_sub(0x64016401u + (((zv >> 8) & 0xFu) | (((zv >> 8) & 0xF0u) << 12)), MAGIC_1024);
+				ze.z = h2_sub(0x64016401u + (((zv >> 16) & 0xFu) | (((zv >> 16) & 0xF0u) << 12)), MAGIC_1024);
+				ze.w = h2_sub(0x64016401u + (((zv >> 24) & 0xFu) | (((zv >> 24) & 0xF0u) << 12)), MAGIC_1024);
+				*reinterpret_cast<uint4 *>(s_ozz + i * 8) = ze;
+				*reinterpret_cast<uint4 *>(s_osc + i * 8) = sv;
+			}
 		}
 	}
 	float rc = 1.f, rs = 0.f;
@@ -235,12 +279,41 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 	}
 	__syncthreads();
 
+	// one chunk (128 k x 32 columns in ring slot `cs`) times the staged x of that chunk: g[c][0] = raw sum of column 4 gid + c
+	const int row_a = 2 * tig, row_b = 2 * tig + 1;
+	const uint32_t ring_even = ring_w + row_a * 128 + ((gid ^ row_a) << 4);
+	const uint32_t ring_odd = ring_w + row_b * 128 + ((gid ^ row_b) << 4);
+	const bool have_row0 = gid == 0;                                    // one batch row
+	auto chunk_mma = [&](const unsigned char *xc, float(&g)[4][2]) {
+		const uint32_t ring_c = cs * QA_SLOT;
+#pragma unroll
+		for (int l = 0; l < 4; ++l) {
+			uint4 q;
+			asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+						 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+						 : "r"(((l & 1) ? ring_odd : ring_even) + ring_c + (l >> 1) * 1024));
+			uint4 xb0 = make_uint4(0u, 0u, 0u, 0u);
+			if (have_row0) xb0 = *reinterpret_cast<const uint4 *>(xc + ((l & 1) + 8 * (l >> 1)) * 16);
+			const uint32_t qv[4] = {q.x, q.y, q.z, q.w};
+			uint32_t a04[4], a15[4], a26[4], a37[4];
+#pragma unroll
+			for (int c = 0; c < 4; ++c) {
+				const uint32_t w = qv[c], w8 = w >> 8;
+				a04[c] = lop3_and_or(w, MASK_LO, MAGIC_1024);
+				a15[c] = lop3_and_or(w, MASK_HI, MAGIC_1024);
+				a26[c] = lop3_and_or(w8, MASK_LO, MAGIC_1024);
+				a37[c] = lop3_and_or(w8, MASK_HI, MAGIC_1024);
+			}
+#pragma unroll
+			for (int pr = 0; pr < 2; ++pr) {
+				float(&d0)[4] = *reinterpret_cast<float(*)[4]>(&g[2 * pr][0]);
+				mma16816(d0, a04[2 * pr], a04[2 * pr + 1], a15[2 * pr], a15[2 * pr + 1], xb0.x, xb0.y);
+				mma16816(d0, a26[2 * pr], a26[2 * pr + 1], a37[2 * pr], a37[2 * pr + 1], xb0.z, xb0.w);
+			}
+		}
+	};
 	// ---- phase 1: this warp's weight chunks ----
 	{
-		const int row_a = 2 * tig, row_b = 2 * tig + 1;
-		const uint32_t ring_even = ring_w + row_a * 128 + ((gid ^ row_a) << 4);
-		const uint32_t ring_odd = ring_w + row_b * 128 + ((gid ^ row_b) << 4);
-		const bool have_row0 = gid == 0;                                // one batch row
 #pragma unroll 1
 		for (int i = 0; i < n_wloads; ++i) {
 			const int j = warp + 8 * i, cl = j / 12, strip = j - cl * 12;
@@ -248,33 +321,7 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 #pragma unroll
 			for (int c = 0; c < 4; ++c) g[c][0] = g[c][1] = 0.f;
 			if (!slot_wait()) break;
-			const uint32_t ring_c = cs * QA_SLOT;
-			const unsigned char *xc = xs + cl * 256 + tig * 32;
-#pragma unroll
-			for (int l = 0; l < 4; ++l) {
-				uint4 q;
-				asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-							 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-							 : "r"(((l & 1) ? ring_odd : ring_even) + ring_c + (l >> 1) * 1024));
-				uint4 xb0 = make_uint4(0u, 0u, 0u, 0u);
-				if (have_row0) xb0 = *reinterpret_cast<const uint4 *>(xc + ((l & 1) + 8 * (l >> 1)) * 16);
-				const uint32_t qv[4] = {q.x, q.y, q.z, q.w};
-				uint32_t a04[4], a15[4], a26[4], a37[4];
-#pragma unroll
-				for (int c = 0; c < 4; ++c) {
-					const uint32_t w = qv[c], w8 = w >> 8;
-					a04[c] = lop3_and_or(w, MASK_LO, MAGIC_1024);
-					a15[c] = lop3_and_or(w, MASK_HI, MAGIC_1024);
-					a26[c] = lop3_and_or(w8, MASK_LO, MAGIC_1024);
-					a37[c] = lop3_and_or(w8, MASK_HI, MAGIC_1024);
-				}
-#pragma unroll
-				for (int pr = 0; pr < 2; ++pr) {
-					float(&d0)[4] = *reinterpret_cast<float(*)[4]>(&g[2 * pr][0]);
-					mma16816(d0, a04[2 * pr], a04[2 * pr + 1], a15[2 * pr], a15[2 * pr + 1], xb0.x, xb0.y);
-					mma16816(d0, a26[2 * pr], a26[2 * pr + 1], a37[2 * pr], a37[2 * pr + 1], xb0.z, xb0.w);
-				}
-			}
+			chunk_mma(xs + cl * 256 + tig * 32, g);
 			slot_done();
 			if (tig == 0) {                       // batch row 0: columns strip * 32 + 4 * gid + 0..3
 				const int col = strip * 32 + gid * 4;
@@ -447,7 +494,7 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 		}
 	}
 	__syncthreads();
-	// ---- merge of the cluster: every CTA's (max, sum, outputs) to CTA 0 ----
+	// ---- merge of the cluster: every CTA's (max, sum, outputs) goes to every CTA; all of them form the same result ----
 	if (tid < QA_D) {
 		float Mx = -INFINITY;
 #pragma unroll
@@ -459,15 +506,20 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 			o = fmaf(s_wo[w * QA_D + tid], g, o);
 			Lx = fmaf(s_wl[w], g, Lx);
 		}
-		const uint32_t dst = qa_map_peer(smem_u32(s_merge + (size_t)rank * 130), 0);
-		qa_st_peer(dst + (2 + tid) * 4, o);
-		if (tid == 0) {
-			qa_st_peer(dst, Mx);
-			qa_st_peer(dst + 4, Lx);
+		const uint32_t mine = smem_u32(s_merge + (size_t)rank * 130);
+		const uint32_t r_hi = p.o_enable ? (uint32_t)QA_CLUSTER : 1u;      // without o_proj only CTA 0 needs it
+		for (uint32_t r = 0; r < r_hi; ++r) {
+			const uint32_t dst = qa_map_peer(mine, r);
+			qa_st_peer(dst + (2 + tid) * 4, o);
+			if (tid == 0) {
+				qa_st_peer(dst, Mx);
+				qa_st_peer(dst + 4, Lx);
+			}
 		}
 	}
 	qa_cluster_sync();
-	if (rank == 0 && tid < QA_D) {
+	__half *s_ah = s_kn;                                                  // [128] attention output of the head (fp16), over the new key
+	if ((rank == 0 || p.o_enable) && tid < QA_D) {
 		float Mg = -INFINITY;
 #pragma unroll
 		for (int r = 0; r < QA_CLUSTER; ++r) Mg = fmaxf(Mg, s_merge[r * 130]);
@@ -479,7 +531,123 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 			Lg = fmaf(s_merge[r * 130 + 1], w, Lg);
 			og = fmaf(s_merge[r * 130 + 2 + tid], w, og);
 		}
-		p.out[head * QA_D + tid] = __float2half_rn(Lg > 0.f ? og / Lg : 0.f);
+		const __half ah = __float2half_rn(Lg > 0.f ? og / Lg : 0.f);
+		if (rank == 0 && p.out) p.out[head * QA_D + tid] = ah;
+		s_ah[tid] = ah;
+	}
+	if (!p.o_enable) return;
+
+	// ---- phase 3: o_proj.  x = the head's attention output (128 values), this warp's strips of the head's rows of Wo ----
+	__shared__ float2 s_cs2;
+	__shared__ int s_last;
+	__syncthreads();
+	if (warp == 0) {                              // stage like xs: 16 units of 8 k, permuted, odd pairs / 16; (C, S) of the chunk
+		float e = 0.f, o = 0.f;
+		if (lane < 16) {
+			const uint4 t = *reinterpret_cast<const uint4 *>(s_ah + lane * 8);
+			uint4 st;
+			st.x = __byte_perm(t.x, t.z, 0x5410);
+			st.y = h2_mul(__byte_perm(t.x, t.z, 0x7632), 0x2C002C00u);
+			st.z = __byte_perm(t.y, t.w, 0x5410);
+			st.w = h2_mul(__byte_perm(t.y, t.w, 0x7632), 0x2C002C00u);
+			*reinterpret_cast<uint4 *>(xs2 + lane * 16) = st;
+			const float2 a0 = __half22float2(*reinterpret_cast<const __half2 *>(&st.x)), a1 = __half22float2(*reinterpret_cast<const __half2 *>(&st.y));
+			const float2 a2 = __half22float2(*reinterpret_cast<const __half2 *>(&st.z)), a3 = __half22float2(*reinterpret_cast<const __half2 *>(&st.w));
+			e = (a0.x + a0.y) + (a2.x + a2.y);
+			o = (a1.x + a1.y) + (a3.x + a3.y);
+		}
+#pragma unroll
+		for (int d = 1; d < 16; d <<= 1) {
+			e += __shfl_xor_sync(0xffffffffu, e, d);
+			o += __shfl_xor_sync(0xffffffffu, o, d);
+		}
+		if (lane == 0) s_cs2 = make_float2(1024.f * (e + o), e + 16.f * o);
+	}
+	__syncthreads();
+#pragma unroll 1
+	for (int j = 0; j < n_oloads; ++j) {
+		float g[4][2];
+#pragma unroll
+		for (int c = 0; c < 4; ++c) g[c][0] = g[c][1] = 0.f;
+		if (!slot_wait()) break;
+		chunk_mma(xs2 + tig * 32, g);
+		slot_done();
+		if (tig == 0) {
+			const int lc = (warp * p.o_spw + j) * 32 + gid * 4;          // column inside this CTA's range
+			const float2 csv = s_cs2;
+			const uint2 zr = *reinterpret_cast<const uint2 *>(s_ozz + lc);
+			const uint2 sr = *reinterpret_cast<const uint2 *>(s_osc + lc);
+			const float2 z01 = __half22float2(*reinterpret_cast<const __half2 *>(&zr.x)), z23 = __half22float2(*reinterpret_cast<const __half2 *>(&zr.y));
+			const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.x)), s23 = __half22float2(*reinterpret_cast<const __half2 *>(&sr.y));
+			float4 o;
+			o.x = s01.x * (g[0][0] - fmaf(z01.x, csv.y, csv.x));
+			o.y = s01.y * (g[1][0] - fmaf(z01.y, csv.y, csv.x));
+			o.z = s23.x * (g[2][0] - fmaf(z23.x, csv.y, csv.x));
+			o.w = s23.y * (g[3][0] - fmaf(z23.y, csv.y, csv.x));
+			__stcg(reinterpret_cast<float4 *>(p.o_part + (size_t)head * p.o_N + rank * 256 * p.o_spw + lc), o);
+		}
+	}
+	if (failed && lane == 0) atomicExch(p.status, 1);
+	// the ticket is an acquire-release atomic at GPU scope after the CTA barrier: it releases the partial sums this CTA
+	// stored and acquires those of the CTAs (same rank, other heads) that arrived earlier
+	__syncthreads();
+	if (tid == 0) {
+		int t;
+		asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(t) : "l"(p.o_tickets + rank) : "memory");
+		const int last_one = (t == (int)gridDim.y - 1);
+		if (last_one) p.o_tickets[rank] = 0;      // ready for the next launch
+		s_last = last_one;
+	}
+	__syncthreads();
+	if (!s_last) return;
+	// The last CTA of this column range adds the heads' partial sums.  256 threads = (64 spw column quads) x (4 / spw head
+	// groups): every thread has the float4 loads of its heads in flight at once (one trip to L2), the head groups are then
+	// added in order through shared memory (the ring is idle by now), so the sum has a fixed order.
+	{
+		float *s_red = reinterpret_cast<float *>(smem);                   // [head group][256 spw]
+		const int ncol = 256 * p.o_spw, quads = ncol >> 2, hsplit = QA_THREADS / quads;
+		const int quad = tid % quads, hg = tid / quads;
+		const int H = (int)gridDim.y, hper = (H + hsplit - 1) / hsplit;
+		const int h_lo = min(hg * hper, H), h_hi = min(h_lo + hper, H);
+		const int n4 = rank * ncol + quad * 4;
+		float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+		if (n4 < p.o_N) {
+#pragma unroll 1
+			for (int h0 = h_lo; h0 < h_hi; h0 += 16) {
+				float4 part[16];
+#pragma unroll
+				for (int k = 0; k < 16; ++k)
+					part[k] = (h0 + k < h_hi) ? __ldcg(reinterpret_cast<const float4 *>(p.o_part + (size_t)(h0 + k) * p.o_N + n4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+				for (int k = 0; k < 16; ++k) {
+					v.x += part[k].x;
+					v.y += part[k].y;
+					v.z += part[k].z;
+					v.w += part[k].w;
+				}
+			}
+		}
+		*reinterpret_cast<float4 *>(s_red + (size_t)hg * ncol + quad * 4) = v;
+		__syncthreads();
+#pragma unroll 1
+		for (int j = 0; j < p.o_spw; ++j) {       // a warp takes 32 consecutive columns = one sum-of-squares tile
+			const int c = j * 256 + tid, n = rank * ncol + c;
+			float sq = 0.f;
+			if (n < p.o_N) {
+				float t = 0.f;
+				for (int g = 0; g < hsplit; ++g) t += s_red[(size_t)g * ncol + c];
+				if (p.o_res) t += __half2float(p.o_res[n]);
+				const __half hv = __float2half_rn(t);
+				p.o_y[n] = hv;
+				const float f = __half2float(hv);
+				sq = f * f;
+			}
+			if (p.o_ss) {
+#pragma unroll
+				for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+				if (lane == 0 && n < p.o_N) p.o_ss[n >> 5] = sq;
+			}
+		}
 	}
 }
 

@@ -262,6 +262,48 @@ def qkv_attn_decode(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, co
 	return out
 
 
+def qkv_attn_oproj_decode(groupsize: int, a: torch.Tensor, qweight, scales, qzeros, cos, sin, pos: torch.Tensor, kcache: torch.Tensor,
+						  vcache: torch.Tensor, n_heads: int, o_groupsize: int, o_qweight, o_scales, o_qzeros, scratch: torch.Tensor,
+						  residual: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None,
+						  rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6, sumsq_in: Optional[torch.Tensor] = None,
+						  attn_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+	"""qkv_attn_decode + o_proj + residual add in the same kernel: returns residual + attention(a) x deq(Wo) as [1, 1, o_N].
+
+	The whole attention block of a decoder layer for one new token of one sequence (fused_attention.py:79-153 of the
+	reference plus the residual add around it).  `scratch`: uint8 tensor of gptq_qkv_attn_oproj_scratch_bytes, zeroed once,
+	private to this call site; `sumsq_out`: fp32 [o_N // 32] receives the sums of squares of the result per 32 columns.
+	"""
+	_lib.require_cuda(a, qweight, scales, qzeros, cos, sin, pos, kcache, vcache, o_qweight, o_scales, o_qzeros, scratch, residual)
+	K = a.shape[-1]
+	o_N = o_qweight.shape[1]
+	assert a.numel() == K and a.is_contiguous() and a.dtype == torch.float16
+	assert pos.dtype == torch.int32 and pos.numel() == 1
+	assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape == vcache.shape and kcache.shape[-3] == n_heads and kcache.shape[-1] == 128
+	assert o_qweight.shape[0] * 8 == n_heads * 128
+	assert (rms_weight is None) == (sumsq_in is None)
+	if residual is not None:
+		assert residual.numel() == o_N and residual.is_contiguous() and residual.dtype == torch.float16
+	if sumsq_out is not None:
+		assert sumsq_out.dtype == torch.float32 and sumsq_out.is_contiguous() and sumsq_out.numel() >= o_N // 32
+	S = kcache.shape[-2]
+	y = torch.empty((1, 1, o_N), dtype=torch.float16, device=a.device)
+	ws = _lib.workspace(a.device, 1, K, 3 * n_heads * 128)
+	P = _lib.ptr
+	opt = lambda t: P(t) if t is not None else None
+	rc = _lib.lib().gptq_qkv_attn_oproj_decode(
+		P(a), P(qweight), P(qzeros), P(scales), P(cos), P(sin), P(pos), min(cos.shape[0], S), P(kcache), P(vcache), S * 128,
+		K, n_heads, 128, groupsize, 1.0 / math.sqrt(128), opt(rms_weight), opt(sumsq_in), K // 32, float(rms_eps),
+		P(o_qweight), P(o_qzeros), P(o_scales), o_N, o_groupsize, opt(residual), P(y), opt(sumsq_out), opt(attn_out),
+		P(scratch), scratch.numel(), P(ws), ws.numel(), _lib.stream_ptr(a.device))
+	_lib.check(rc, 'gptq_qkv_attn_oproj_decode')
+	return y
+
+
+def qkv_attn_oproj_scratch(n_heads: int, o_N: int, device) -> torch.Tensor:
+	"""Zeroed scratch area for qkv_attn_oproj_decode (arrival counters + per-head partial sums)."""
+	return torch.zeros(_lib.lib().gptq_qkv_attn_oproj_scratch_bytes(n_heads, o_N), dtype=torch.uint8, device=device)
+
+
 def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: torch.Tensor, len_hint: int) -> torch.Tensor:
 	"""Attention of one new token per sequence over a static cache.
 	q [b, heads, 1, 128] or [b, 1, heads, 128] memory as produced by qkv_rope (any view whose

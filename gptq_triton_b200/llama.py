@@ -21,7 +21,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .fused_attention import QuantLlamaAttention, attn_decode, qkv_attn_decode, qkv_attn_supported
+from .fused_attention import (QuantLlamaAttention, attn_decode, qkv_attn_decode, qkv_attn_oproj_decode, qkv_attn_oproj_scratch,
+							  qkv_attn_supported)
 from .fused_attention import rmsnorm as rmsnorm_kernel
 from .fused_mlp import QuantLlamaMLP
 from .tp import all_reduce_
@@ -226,7 +227,9 @@ class DecodeEngine:
 		self.len_hint = max_seq
 		self.graph = None
 		self.launches_per_step = None
+		self._qao_scratch = None
 		self.used_qkv_attn = False          # set when a decode step ran the one-kernel QKV + attention path
+		self.used_fused_oproj = False       # ... with o_proj and the residual add in the same kernel
 		self.next_pos = 0          # host-side copy of the position the next step() writes (the cache has max_seq rows)
 		# One persistent kernel per decode step (gptq_decode_chain) + the lm_head / arg-max kernel, where the model
 		# allows it (one GPU, batch <= 8, no act-order, no bias, one group size); opt-in with GPTQ_B200_CHAIN=1 (default: the
@@ -325,16 +328,28 @@ class DecodeEngine:
 		# hidden state (and its sums of squares); with NCCL the norms stay separate kernels
 		fused_ar = decode and self.ar_o is not None and b <= 16
 		fold = self.fuse_norm and decode and (self.tp_world == 1 or fused_ar) and b <= 16 and self.cfg.hidden_size % 128 == 0 and self.cfg.hidden_size // 32 <= 256
-		o = None
+		o = h_attn = None
 		if decode and b == 1 and self.batch == 1 and self._one_kernel_attention(attn) and (x_normed is not None or (fold and ss_in is not None)):
 			# one sequence: projection, rotary, cache append and attention in one kernel (a cluster of 8 CTAs per head)
 			self.used_qkv_attn = True
 			qw, _, _ = attn.qkv_proj.kernel_operands()
 			cos, sin = attn.tables(h.device, self.max_seq)
 			src = x_normed if x_normed is not None else h.contiguous()
-			o = qkv_attn_decode(attn.qkv_proj.groupsize, src, qw, attn.qkv_proj.scales, attn.qkv_proj.qzeros, cos, sin, pos.view(-1), self.kcache[i],
-								self.vcache[i], attn.num_heads, rms_weight=None if x_normed is not None else ln1.weight,
-								rms_eps=ln1.variance_epsilon, sumsq_in=None if x_normed is not None else ss_in)
+			rms_w, rms_ss = (None, None) if x_normed is not None else (ln1.weight, ss_in)
+			op = attn.o_proj
+			if self._fused_oproj(attn):
+				# ... and the output projection with the residual add as well: the whole attention block is one kernel
+				self.used_fused_oproj = True
+				if self._qao_scratch is None:
+					self._qao_scratch = qkv_attn_oproj_scratch(attn.num_heads, op.outfeatures, h.device)
+				h_attn = qkv_attn_oproj_decode(attn.qkv_proj.groupsize, src, qw, attn.qkv_proj.scales, attn.qkv_proj.qzeros, cos, sin, pos.view(-1),
+											   self.kcache[i], self.vcache[i], attn.num_heads, op.groupsize, op.qweight, op.scales, op.qzeros,
+											   self._qao_scratch, residual=h.contiguous(), sumsq_out=self.ss_attn, rms_weight=rms_w,
+											   rms_eps=ln1.variance_epsilon, sumsq_in=rms_ss)
+				o = h_attn
+			else:
+				o = qkv_attn_decode(attn.qkv_proj.groupsize, src, qw, attn.qkv_proj.scales, attn.qkv_proj.qzeros, cos, sin, pos.view(-1), self.kcache[i],
+									self.vcache[i], attn.num_heads, rms_weight=rms_w, rms_eps=ln1.variance_epsilon, sumsq_in=rms_ss)
 		elif x_normed is not None:
 			q, _, _ = attn.project_qkv(x_normed, pos, kv_cache=(self.kcache[i], self.vcache[i]))
 		elif fold:
@@ -358,7 +373,9 @@ class DecodeEngine:
 		res = h if (self.tp_rank == 0 or fused_ar) else None          # the fused exchange adds the residual on every rank
 		fold_mlp = fold and isinstance(mlp, QuantLlamaMLP) and attn.o_proj.g_idx is None
 		ar_o = self.ar_o if fused_ar else None
-		if fold_mlp:
+		if h_attn is not None:
+			h = h_attn
+		elif fold_mlp:
 			h = attn.o_proj(o, residual=res, sumsq_out=self.ss_attn, ar=ar_o)
 		else:
 			h = attn.o_proj(o, residual=res, ar=ar_o)
@@ -410,6 +427,16 @@ class DecodeEngine:
 		if g_idx is not None or perm is not None or qp.bias is not None or attn.head_dim != 128:
 			return False
 		return qkv_attn_supported(qp.infeatures, attn.num_heads, attn.head_dim, qp.groupsize)
+
+	def _fused_oproj(self, attn) -> bool:
+		"""Whether the one-kernel attention also does o_proj and the residual add (one GPU, plain group layout, no bias,
+		at most 8192 outputs; GPTQ_B200_QKV_ATTN_O=0 turns it off)."""
+		if self.tp_world != 1 or os.environ.get('GPTQ_B200_QKV_ATTN_O', '1') == '0':
+			return False
+		op = attn.o_proj
+		_, g_idx, perm = op.kernel_operands()
+		return (g_idx is None and perm is None and op.bias is None and op.infeatures == attn.num_heads * 128 and op.outfeatures % 32 == 0
+				and op.outfeatures <= 8192 and op.groupsize % 128 == 0 and op.infeatures % op.groupsize == 0)
 
 	def _own_ends(self):
 		"""Buffers for the first and last kernel of a decode step when both ends run as own kernels: embedding

@@ -175,6 +175,27 @@ int gptq_qkv_attn_decode(const void *x, const int32_t *qweight, const int32_t *q
                          int sumsq_tiles, float rms_eps, void *workspace, size_t workspace_bytes,
                          gptq_stream_t stream);
 
+/*
+ * gptq_qkv_attn_decode followed by the block's output projection and the residual add, still ONE kernel:
+ * y = residual + attention_output x deq(Wo) (src/gptq_triton/fused_attention.py:148, o_proj, and the residual add of
+ * the HF decoder layer around it).  The cluster of head h multiplies the head's 128 attention outputs with rows
+ * 128 h .. 128 h + 127 of Wo (o_qweight int32 [n_heads*128/8, o_N], o_qzeros, o_scales; no g_idx / perm / bias;
+ * o_groupsize % 128 == 0; o_N % 32 == 0, o_N <= 8192); the per-head partial sums are added in head order by the last
+ * CTA to arrive, so the result does not depend on timing.  residual (optional) fp16 [o_N]; y fp16 [o_N];
+ * sumsq_out (optional) fp32 [o_N / 32]: sums of squares of y per 32 columns (input of the folded RMSNorm of the next
+ * projection); attn_out (optional) fp16 [n_heads*128]: the attention output itself.  scratch: device memory of
+ * gptq_qkv_attn_oproj_scratch_bytes(n_heads, o_N) bytes, zeroed once, private to this call site.
+ */
+size_t gptq_qkv_attn_oproj_scratch_bytes(int n_heads, int N);
+int gptq_qkv_attn_oproj_decode(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales,
+                               const void *cos, const void *sin, const int32_t *pos, int max_pos, void *kcache,
+                               void *vcache, int64_t kv_stride_h, int K, int n_heads, int head_dim, int groupsize,
+                               float scale, const void *rms_weight, const float *sumsq_in, int sumsq_tiles,
+                               float rms_eps, const int32_t *o_qweight, const int32_t *o_qzeros,
+                               const void *o_scales, int o_N, int o_groupsize, const void *residual, void *y,
+                               float *sumsq_out, void *attn_out, void *scratch, size_t scratch_bytes,
+                               void *workspace, size_t workspace_bytes, gptq_stream_t stream);
+
 /* y = x * rsqrt(mean(x^2) + eps) * weight, per row, fp32 inside.  The RMSNorm that the HF
  * decoder layer applies in front of the attention and MLP blocks (third-party code the
  * reference model is built from, src/gptq_triton/__init__.py:47). */

@@ -104,6 +104,51 @@ def test_qkv_attn_equals_two_kernel_path_with_folded_rmsnorm(G):
 	assert torch.equal(o1, o3) and torch.equal(k1, k3) and torch.equal(v1, v3)
 
 
+@pytest.mark.parametrize('K,H,gs,S,pos,resid', [(1024, 8, 128, 96, 7, True), (4096, 32, 128, 2304, 2111, True), (2048, 16, 256, 300, 130, False),
+												(1024, 8, -1, 64, 0, True)])
+def test_qkv_attn_oproj_against_oracle(G, K, H, gs, S, pos, resid):
+	"""The whole attention block in one kernel: y = residual + attention x deq(Wo), with the sums of squares of y."""
+	from gptq_triton_b200.fused_attention import qkv_attn_oproj_decode, qkv_attn_oproj_scratch
+	from gptq_triton_b200 import _lib
+	D = 128
+	hidden = H * D
+	assert hidden == K
+	w = synth(K, 3 * hidden, gs, seed=K + H)
+	wo = synth(hidden, hidden, gs, seed=K + H + 1)
+	x = acts((1, 1, K), seed=pos + 5)
+	g = torch.Generator().manual_seed(S + pos)
+	kc = torch.randn((1, H, S, D), generator=g).half()
+	vc = torch.randn((1, H, S, D), generator=g).half()
+	cos, sin = O.rope_tables(D, S)
+	kd, vd = kc.cuda(), vc.cuda()
+	scratch = qkv_attn_oproj_scratch(H, hidden, 'cuda')
+	ss = torch.zeros(hidden // 32, dtype=torch.float32, device='cuda')
+	attn_out = torch.zeros((1, 1, hidden), dtype=torch.float16, device='cuda')
+	xd = x.cuda()
+	outs = []
+	for _ in range(2):          # the second call finds the arrival counters as the first one left them
+		kd.copy_(kc), vd.copy_(vc)
+		y = qkv_attn_oproj_decode(gs, xd, w['qweight'].cuda(), w['scales'].cuda(), w['qzeros'].cuda(), cos.cuda(), sin.cuda(),
+								  torch.tensor([pos], dtype=torch.int32).cuda(), kd, vd, H, gs, wo['qweight'].cuda(), wo['scales'].cuda(),
+								  wo['qzeros'].cuda(), scratch, residual=xd if resid else None, sumsq_out=ss, attn_out=attn_out)
+		outs.append((y.clone(), ss.clone()))
+	torch.cuda.synchronize()
+	assert _lib.kernel_status() == 0
+	assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+	ref_attn, rk, rv = oracle_attention(x, w, gs, cos, sin, pos, H, D, kc[0], vc[0])
+	assert O.max_rel_err(attn_out.view(-1).cpu(), ref_attn) <= TOL
+	# o_proj on the kernel's own fp16 attention output, fp32 accumulation, then the residual
+	a16 = attn_out.view(1, -1).cpu()
+	ref = O.qmatmul_r32(a16, wo['qweight'], wo['qzeros'], wo['scales'], gs).view(-1)
+	if resid:
+		ref = ref + x.view(-1).float()
+	assert y.shape == (1, 1, hidden)
+	assert O.max_rel_err(y.view(-1).cpu(), ref) <= TOL
+	yf = y.view(-1).float().cpu()
+	assert torch.allclose(ss.cpu(), (yf.view(-1, 32) ** 2).sum(-1), rtol=1e-5, atol=1e-6)
+	assert O.max_rel_err(kd[0, :, pos].cpu(), rk) <= TOL and O.max_rel_err(vd[0, :, pos].cpu(), rv) <= TOL
+
+
 def test_qkv_attn_position_outside_the_cache_is_reported(G):
 	from gptq_triton_b200.fused_attention import qkv_attn_decode
 	from gptq_triton_b200 import _lib
