@@ -228,6 +228,8 @@ class DecodeEngine:
 		self.graph = None
 		self.launches_per_step = None
 		self._qao_scratch = None
+		# captures of the decode step to choose from (see step()); 1 = take the first
+		self.graph_candidates = int(os.environ.get('GPTQ_B200_GRAPH_CANDIDATES', '4'))
 		self.used_qkv_attn = False          # set when a decode step ran the one-kernel QKV + attention path
 		self.used_fused_oproj = False       # ... with o_proj and the residual add in the same kernel
 		self.next_pos = 0          # host-side copy of the position the next step() writes (the cache has max_seq rows)
@@ -515,18 +517,44 @@ class DecodeEngine:
 			saved = (self.tok.clone(), self.pos.clone(), self.mask.clone())
 			s = torch.cuda.Stream()
 			s.wait_stream(torch.cuda.current_stream())
+			best, best_ms = None, None
 			with torch.cuda.stream(s):
 				for _ in range(2):
 					self._step_body()
 					self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
 				s.synchronize()
-				g = torch.cuda.CUDAGraph()
-				with torch.cuda.graph(g, stream=s):
-					self._step_body()
+				# The activations of a step live in the graph's private memory pool.  Where that pool lands decides how the
+				# few lines every CTA reads right after a kernel boundary spread over the L2 slices: the same graph replays
+				# 7 % faster or slower from one capture to the next (two modes, measured).  So the step is captured several
+				# times, every candidate is timed on a few replays, and the fastest one is kept.  The replays write cache rows
+				# at the current position onwards, which the real steps write again; token and position are restored.
+				n_cand = max(1, self.graph_candidates if self.tp_world == 1 else 1)
+				alive = []          # every candidate keeps its pool until the choice is made: a freed pool would be handed to the next capture
+				for _ in range(n_cand):
+					g = torch.cuda.CUDAGraph()
+					with torch.cuda.graph(g, stream=s):
+						self._step_body()
+					alive.append(g)
+					if n_cand == 1:
+						best = g
+						break
+					reps = max(1, min(8, self.max_seq - 1 - int(saved[1].max().item())))
+					e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+					g.replay()
+					e0.record(s)
+					for _ in range(reps):
+						self.tok.copy_(saved[0]); self.pos.copy_(saved[1])
+						g.replay()
+					e1.record(s)
+					s.synchronize()
+					ms = e0.elapsed_time(e1) / reps
+					if best_ms is None or ms < best_ms:
+						best, best_ms = g, ms
+				del alive
 			torch.cuda.current_stream().wait_stream(s)
-			# capture does not execute: state is still the saved one
+			# capture does not execute (and the timed replays started from the saved state): restore it
 			self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
-			self.graph = g
+			self.graph = best
 		self.graph.replay()
 		return self.tok
 
