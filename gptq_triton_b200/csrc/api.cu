@@ -18,6 +18,7 @@ thread_local int g_last_cuda_error = 0;
 
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
 static int g_max_stages = 4;     // tuning hook: upper bound of the ring depth of the decode kernel
+static int g_soft_max_splits = 8;  // the planner avoids more splits than this (gptq_debug_soft_max_splits)
 static int g_pdl = 1;             // programmatic dependent launch for the decode-step kernels (+3 % on the decode step)
 
 static int sm_count() {
@@ -202,7 +203,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 			score -= 0.02 * std::max(0, 4 - nstage);
 			if (cps < kwarps) score -= 0.25;
 			if (kwarps == 4) score -= 0.03;
-			if (eff > 8) score -= 0.15;      // measured (7B down_proj, 11008 -> 4096): 8 splits 9.6 us, 9 splits 10.9 us
+			if (eff > g_soft_max_splits) score -= 0.15;      // measured (7B down_proj, 11008 -> 4096): 8 splits 9.6 us, 9 splits 10.9 us
 			if (score > best_score) {
 				best_score = score;
 				best_sk = sk;
@@ -422,6 +423,7 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
 void gptq_debug_max_stages(int n) { g_max_stages = std::max(2, std::min(n, 8)); }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+void gptq_debug_soft_max_splits(int n) { g_soft_max_splits = n; }
 void gptq_debug_allow_narrow(int on) { g_allow_narrow = on ? 1 : 0; }
 size_t gptq_workspace_bytes(int M, int K, int N) {
 	if (M <= 0 || N <= 0) return SK_TICKET_BYTES;
