@@ -517,7 +517,7 @@ class DecodeEngine:
 			saved = (self.tok.clone(), self.pos.clone(), self.mask.clone())
 			s = torch.cuda.Stream()
 			s.wait_stream(torch.cuda.current_stream())
-			best, best_ms = None, None
+			best, best_ms, best_logits = None, None, None
 			with torch.cuda.stream(s):
 				for _ in range(2):
 					self._step_body()
@@ -528,15 +528,16 @@ class DecodeEngine:
 				# 7 % faster or slower from one capture to the next (two modes, measured).  So the step is captured several
 				# times, every candidate is timed on a few replays, and the fastest one is kept.  The replays write cache rows
 				# at the current position onwards, which the real steps write again; token and position are restored.
-				n_cand = max(1, self.graph_candidates if self.tp_world == 1 else 1)
+				n_cand = max(1, self.graph_candidates)          # tensor parallel: every rank replays the same number of times, the choice is per rank
 				alive = []          # every candidate keeps its pool until the choice is made: a freed pool would be handed to the next capture
 				for _ in range(n_cand):
 					g = torch.cuda.CUDAGraph()
 					with torch.cuda.graph(g, stream=s):
 						self._step_body()
 					alive.append(g)
+					cand_logits = self.logits          # the capture's own output tensor (it lives in that graph's pool)
 					if n_cand == 1:
-						best = g
+						best, best_logits = g, cand_logits
 						break
 					reps = max(1, min(8, self.max_seq - 1 - int(saved[1].max().item())))
 					e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -549,12 +550,13 @@ class DecodeEngine:
 					s.synchronize()
 					ms = e0.elapsed_time(e1) / reps
 					if best_ms is None or ms < best_ms:
-						best, best_ms = g, ms
+						best, best_ms, best_logits = g, ms, cand_logits
 				del alive
 			torch.cuda.current_stream().wait_stream(s)
 			# capture does not execute (and the timed replays started from the saved state): restore it
 			self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
 			self.graph = best
+			self.logits = best_logits
 		self.graph.replay()
 		return self.tok
 

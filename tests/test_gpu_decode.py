@@ -58,6 +58,24 @@ def test_greedy_tokens_identical_for_32_steps():
 	assert _lib.kernel_status() == 0
 
 
+@pytest.mark.parametrize('batch', [1, 9])
+def test_graph_engine_logits_equal_eager_engine_logits(batch):
+	"""The engine captures the step several times and keeps the fastest capture: `engine.logits` must be the output of
+	the capture that is replayed (batch 9 takes the path whose logits live in the graph's own pool), and the replays
+	that choose the capture must leave token, position and cache as they were."""
+	import gptq_triton_b200 as G
+	cfg, model, dense = build_pair(2)
+	prompt = torch.randint(0, cfg.vocab_size, (batch, 20), generator=torch.Generator().manual_seed(7)).cuda()
+	outs = []
+	for use_graph in (False, True):
+		engine = G.DecodeEngine(model, batch=batch, max_seq=64, use_graph=use_graph)
+		assert engine.graph_candidates > 1
+		toks = engine.generate(prompt, 6)
+		outs.append((toks.clone(), engine.logits.float().clone(), engine.pos.clone()))
+	assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][2], outs[1][2])
+	assert torch.equal(outs[0][1], outs[1][1])          # same kernels, same order of sums: identical bits
+
+
 def test_reference_style_forward_matches_engine_logits():
 	"""The drop-in module path (tuples of concatenated K/V, attention mask) and the static-cache
 	engine produce the same logits up to fp16 rounding."""
