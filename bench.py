@@ -732,11 +732,15 @@ def kernel_case(args):
 		# decode attention block of one sequence at 2100 tokens of context, 7B shapes: the one-kernel form (projection + rotary +
 		# cache append + attention, one cluster per head) against the pair qkv_rope + attn_decode, over rotating copies of the
 		# weights and caches (together larger than L2), timed with CUDA events
-		from gptq_triton_b200.fused_attention import attn_decode, qkv_attn_decode, qkv_rope, rope_tables
+		from gptq_triton_b200.fused_attention import attn_decode, qkv_attn_decode, qkv_attn_oproj_decode, qkv_attn_oproj_scratch, qkv_rope, rope_tables
 		K, H, S, D, ctx = 4096, 32, 2200, 128, 2100
 		t = synth.quant_tensors(K, 3 * H * D, GROUPSIZE, seed=2)
 		ncopy = 8
 		ws = [tuple(v.to(dev).clone() for v in (t['qweight'], t['scales'], t['qzeros'])) for _ in range(ncopy)]
+		to = synth.quant_tensors(K, K, GROUPSIZE, seed=3)
+		wo = [tuple(v.to(dev).clone() for v in (to['qweight'], to['scales'], to['qzeros'])) for _ in range(ncopy)]
+		scratch = qkv_attn_oproj_scratch(H, K, dev)
+		ss = torch.zeros(K // 32, dtype=torch.float32, device=dev)
 		caches = [(torch.randn((1, H, S, D), device=dev).half(), torch.randn((1, H, S, D), device=dev).half()) for _ in range(ncopy)]
 		x = synth.activations((1, 1, K), seed=1).to(dev)
 		cos, sin = rope_tables(D, S, 10000.0, device=dev)
@@ -748,9 +752,15 @@ def kernel_case(args):
 			qw, sc, qz = ws[i]
 			q, _, _ = qkv_rope(GROUPSIZE, x, qw, sc, qz, cos, sin, pos, H, D, kv_cache=caches[i])
 			return attn_decode(q, caches[i][0], caches[i][1], pos, ctx + 1)
-		out = {'kernel_case': 'qkvattn', 'heads': H, 'ctx': ctx + 1}
+		def block(i):          # the whole attention block: + o_proj + residual, still one kernel
+			qw, sc, qz = ws[i]
+			return qkv_attn_oproj_decode(GROUPSIZE, x, qw, sc, qz, cos, sin, pos.view(-1), caches[i][0], caches[i][1], H, GROUPSIZE, wo[i][0], wo[i][1],
+										 wo[i][2], scratch, residual=x, sumsq_out=ss)
+		def pair_o(i):
+			return G.qmatmul(GROUPSIZE, pair(i).view(1, K), *wo[i], residual=x.view(1, K), sumsq_out=ss.view(1, -1))
+		out = {'kernel_case': 'qkvattn', 'heads': H, 'ctx': ctx + 1, 'timing': 'eager launches, CUDA events (includes launch gaps)'}
 		reps = 4
-		for name, fn in (('one_kernel_us', one), ('two_kernels_us', pair)):
+		for name, fn in (('one_kernel_us', one), ('two_kernels_us', pair), ('block_one_kernel_us', block), ('block_three_kernels_us', pair_o)):
 			for i in range(ncopy):
 				fn(i)
 			torch.cuda.synchronize()
@@ -763,9 +773,10 @@ def kernel_case(args):
 			torch.cuda.synchronize()
 			out[name] = e0.elapsed_time(e1) * 1e3 / (reps * ncopy)
 		alg = K * 3 * H * D // 2 + (K // GROUPSIZE) * 3 * H * D * 5 // 2 + 2 * H * (ctx + 1) * D * 2
+		alg_block = alg + K * K // 2 + (K // GROUPSIZE) * K * 5 // 2
 		peak, which = measured_peaks()
-		out.update({'alg_bytes': alg, 'frac_one_kernel': alg / out['one_kernel_us'] / 1e3 / peak, 'frac_two_kernels': alg / out['two_kernels_us'] / 1e3 / peak,
-					'peak_source': which, 'max_abs_diff': float((one(0).float() - pair(0).float()).abs().max()), 'launches': 3 * ncopy * (reps + 1) + 3})
+		out.update({'alg_bytes_block': alg_block, 'frac_block_one_kernel': alg_block / out['block_one_kernel_us'] / 1e3 / peak, 'alg_bytes': alg, 'frac_one_kernel': alg / out['one_kernel_us'] / 1e3 / peak, 'frac_two_kernels': alg / out['two_kernels_us'] / 1e3 / peak,
+					'peak_source': which, 'max_abs_diff': float((one(0).float() - pair(0).float()).abs().max()), 'launches': 8 * ncopy * (reps + 1) + 3})
 		from gptq_triton_b200 import _lib
 		out['kernel_status'] = _lib.kernel_status()
 		print(json.dumps(out))

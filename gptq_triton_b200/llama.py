@@ -229,7 +229,7 @@ class DecodeEngine:
 		self.launches_per_step = None
 		self._qao_scratch = None
 		# captures of the decode step to choose from (see step()); 1 = take the first
-		self.graph_candidates = int(os.environ.get('GPTQ_B200_GRAPH_CANDIDATES', '4'))
+		self.graph_candidates = int(os.environ.get('GPTQ_B200_GRAPH_CANDIDATES', '6'))
 		self.used_qkv_attn = False          # set when a decode step ran the one-kernel QKV + attention path
 		self.used_fused_oproj = False       # ... with o_proj and the residual add in the same kernel
 		self.next_pos = 0          # host-side copy of the position the next step() writes (the cache has max_seq rows)
