@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 	const int ng = (c_hi * 128 - 1) / p.groupsize - g_lo + 1;
 	const int n_strip = NSTREAM * ng * SU;              // items of 8 columns
 	const int units = (c_hi - c_lo) * 16;               // 16-byte units per x row
-	constexpr int SB = 2, XB = 4;
+	constexpr int SB = 2, XB = M8 ? 4 : 8;      // 16 rows: eight 16-byte loads of x in flight per thread (two passes instead of four)
 	// strips: item -> (stream, group, 8-column unit) without a division (NSTREAM <= 2)
 	auto strip_load = [&](int base, uint32_t(&z)[SB], uint4(&sv)[SB]) {
 		const int nz = p.N >> 3;
@@ -734,15 +734,20 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			}
 		} else {
 #pragma unroll 1
-			for (int e0 = tid; e0 < nelem; e0 += NT * 4) {        // four elements in flight per thread; fixed split order
+			for (int e0 = tid; e0 < nelem; e0 += NT * 4) {        // four elements x eight splits in flight per thread; fixed split order
 				float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-				for (int k = 0; k < p.splitk; ++k) {
-					float t[4];
+				for (int k0 = 0; k0 < p.splitk; k0 += 8) {
+					float t[8][4];
 #pragma unroll
-					for (int j = 0; j < 4; ++j) t[j] = (e0 + j * NT < nelem) ? __ldcg(wt + (size_t)k * nelem + e0 + j * NT) : 0.f;
+					for (int kk = 0; kk < 8; ++kk)
 #pragma unroll
-					for (int j = 0; j < 4; ++j) v[j] += t[j];
+						for (int j = 0; j < 4; ++j)
+							t[kk][j] = (k0 + kk < p.splitk && e0 + j * NT < nelem) ? __ldcg(wt + (size_t)(k0 + kk) * nelem + e0 + j * NT) : 0.f;
+#pragma unroll
+					for (int kk = 0; kk < 8; ++kk)
+#pragma unroll
+						for (int j = 0; j < 4; ++j) v[j] += t[kk][j];
 				}
 #pragma unroll
 				for (int j = 0; j < 4; ++j) {
