@@ -523,9 +523,9 @@ class DecodeEngine:
 					self._step_body()
 					self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
 				s.synchronize()
-				# The activations of a step live in the graph's private memory pool.  Where that pool lands decides how the
-				# few lines every CTA reads right after a kernel boundary spread over the L2 slices: the same graph replays
-				# 7 % faster or slower from one capture to the next (two modes, measured).  So the step is captured several
+				# The activations of a step live in the graph's private memory pool.  Where that pool lands (which physical
+				# 2 MB page) decides how fast the few lines that every CTA reads right after a kernel boundary arrive: the same
+				# graph replays 7 % faster or slower from one capture to the next (two modes, measured).  So the step is captured several
 				# times, every candidate is timed on a few replays, and the fastest one is kept.  The replays write cache rows
 				# at the current position onwards, which the real steps write again; token and position are restored.
 				n_cand = max(1, self.graph_candidates)          # tensor parallel: every rank replays the same number of times, the choice is per rank
