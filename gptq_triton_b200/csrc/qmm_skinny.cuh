@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			if (valid && sub == 0) s_cs[gi * 16 + row] = make_float2(1024.f * (e + o), e + 16.f * o);
 		}
 	}
-	__syncthreads();
+	// no barrier here: the sums are read only after the main loop, behind the barrier that ends it
 
 	// ---- main loop ---------------------------------------------------------------------
 	// acc[stream][batch block][column 0..3 of this lane][batch row 2*tig + {0,1}]
