@@ -53,6 +53,8 @@ _SIGNATURES = {
 	'gptq_qkv_attn_oproj_scratch_bytes': (c_size_t, [c_int, c_int]),
 	'gptq_qkv_attn_oproj_decode': (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int64, c_int, c_int, c_int, c_int, ctypes.c_float, _P, _P, c_int,
 										   ctypes.c_float, _P, _P, _P, c_int, c_int, _P, _P, _P, _P, _P, c_size_t, _P, c_size_t, _P]),
+	'gptq_qkv_attn_oproj_decode_ar': (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int64, c_int, c_int, c_int, c_int, ctypes.c_float, _P, _P, c_int,
+											  ctypes.c_float, _P, _P, _P, c_int, c_int, _P, _P, _P, _P, _P, c_size_t, _P, c_size_t, _P, c_int, c_int, _P, _P]),
 	'gptq_attn_decode': (c_int, [_P, c_int64, _P, _P, c_int64, c_int64, _P, _P, c_int64, c_int, c_int, c_int, c_int, ctypes.c_float, _P, c_size_t, _P]),
 	'gptq_rmsnorm': (c_int, [_P, c_int64, _P, _P, c_int64, c_int, c_int, ctypes.c_float, _P]),
 	'gptq_embed_rmsnorm': (c_int, [_P, c_int64, c_int64, _P, _P, _P, c_int64, _P, c_int64, c_int, c_int, ctypes.c_float, _P]),

@@ -597,6 +597,9 @@ struct QaOproj {
 	int N, groupsize;
 	void *scratch;
 	size_t scratch_bytes;
+	int ar_world, ar_rank;          // > 1: o_proj is this rank's row shard, the all-reduce runs inside the kernel
+	void *const *ar_partials;
+	void *const *ar_flags;
 };
 
 static int qkv_attn_impl(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const void *cos, const void *sin,
@@ -639,6 +642,14 @@ static int qkv_attn_impl(const void *x, const int32_t *qweight, const int32_t *q
 		p.o_tickets = reinterpret_cast<int *>(o->scratch);
 		p.o_part = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(o->scratch) + 256);
 		p.o_y = (__half *)o->y; p.o_ss = o->sumsq_out;
+		if (o->ar_world > 1) {
+			if (o->ar_world > 8 || o->ar_rank < 0 || o->ar_rank >= o->ar_world || !o->ar_partials || !o->ar_flags || o->N % 128 != 0) return GPTQ_ERR_INVALID;
+			for (int r = 0; r < o->ar_world; ++r)
+				if (!o->ar_partials[r] || !o->ar_flags[r] || !aligned16(o->ar_partials[r])) return GPTQ_ERR_INVALID;
+			p.ar_world = o->ar_world; p.ar_rank = o->ar_rank; p.ar_tiles = o->N / 128;
+			for (int r = 0; r < o->ar_world; ++r) p.ar_buf[r] = reinterpret_cast<unsigned long long *>(o->ar_partials[r]);
+			p.ar_seq = reinterpret_cast<unsigned *>(o->ar_flags[o->ar_rank]);
+		}
 		if (int rc = weight_tensor_map(o->qweight, n_heads * QA_D, o->N, &tmo)) return rc;
 	}
 	const size_t smem = qkv_attn_layout(p);
@@ -648,12 +659,16 @@ static int qkv_attn_impl(const void *x, const int32_t *qweight, const int32_t *q
 		int dev = 0;
 		if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GPTQ_ERR_CUDA;
 		if (!ready[dev]) {
-			cudaError_t e = cudaFuncSetAttribute(qkv_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_LIMIT - 2048);      // the kernel has 1 KB of static shared memory
+			cudaError_t e = cudaFuncSetAttribute(qkv_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_LIMIT - 2048);      // the kernel has 1 KB of static shared memory
+			if (e != cudaSuccess) return cuda_status(e);
+			e = cudaFuncSetAttribute(qkv_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_LIMIT - 2048);
 			if (e != cudaSuccess) return cuda_status(e);
 			ready[dev] = true;
 		}
 	}
-	return launch_ex(qkv_attn_kernel, dim3(QA_CLUSTER, n_heads, 1), dim3(QA_THREADS, 1, 1), smem, reinterpret_cast<cudaStream_t>(stream), tm, tmo, p);
+	if (p.ar_world > 1)
+		return launch_ex(qkv_attn_kernel<true>, dim3(QA_CLUSTER, n_heads, 1), dim3(QA_THREADS, 1, 1), smem, reinterpret_cast<cudaStream_t>(stream), tm, tmo, p);
+	return launch_ex(qkv_attn_kernel<false>, dim3(QA_CLUSTER, n_heads, 1), dim3(QA_THREADS, 1, 1), smem, reinterpret_cast<cudaStream_t>(stream), tm, tmo, p);
 }
 
 int gptq_qkv_attn_decode(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const void *cos, const void *sin,
@@ -671,7 +686,20 @@ int gptq_qkv_attn_oproj_decode(const void *x, const int32_t *qweight, const int3
 							   int sumsq_tiles, float rms_eps, const int32_t *o_qweight, const int32_t *o_qzeros, const void *o_scales,
 							   int o_N, int o_groupsize, const void *residual, void *y, float *sumsq_out, void *attn_out, void *scratch,
 							   size_t scratch_bytes, void *workspace, size_t workspace_bytes, gptq_stream_t stream) {
-	QaOproj o = {o_qweight, o_qzeros, o_scales, residual, y, sumsq_out, o_N, o_groupsize, scratch, scratch_bytes};
+	QaOproj o = {o_qweight, o_qzeros, o_scales, residual, y, sumsq_out, o_N, o_groupsize, scratch, scratch_bytes, 0, 0, nullptr, nullptr};
+	return qkv_attn_impl(x, qweight, qzeros, scales, cos, sin, pos, max_pos, kcache, vcache, kv_stride_h, attn_out, K, n_heads, head_dim,
+						 groupsize, scale, rms_weight, sumsq_in, sumsq_tiles, rms_eps, workspace, workspace_bytes, stream, &o);
+}
+
+int gptq_qkv_attn_oproj_decode_ar(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales, const void *cos,
+								  const void *sin, const int32_t *pos, int max_pos, void *kcache, void *vcache, int64_t kv_stride_h, int K,
+								  int n_heads, int head_dim, int groupsize, float scale, const void *rms_weight, const float *sumsq_in,
+								  int sumsq_tiles, float rms_eps, const int32_t *o_qweight, const int32_t *o_qzeros, const void *o_scales,
+								  int o_N, int o_groupsize, const void *residual, void *y, float *sumsq_out, void *attn_out, void *scratch,
+								  size_t scratch_bytes, void *workspace, size_t workspace_bytes, gptq_stream_t stream, int world, int rank,
+								  void *const *partials, void *const *flags) {
+	if (world < 2) return GPTQ_ERR_INVALID;
+	QaOproj o = {o_qweight, o_qzeros, o_scales, residual, y, sumsq_out, o_N, o_groupsize, scratch, scratch_bytes, world, rank, partials, flags};
 	return qkv_attn_impl(x, qweight, qzeros, scales, cos, sin, pos, max_pos, kcache, vcache, kv_stride_h, attn_out, K, n_heads, head_dim,
 						 groupsize, scale, rms_weight, sumsq_in, sumsq_tiles, rms_eps, workspace, workspace_bytes, stream, &o);
 }

@@ -67,6 +67,13 @@ struct QkvAttnParams {
 	int *o_tickets;
 	__half *o_y;
 	float *o_ss;
+	// Tensor parallelism (o_proj is the row shard of this rank's heads): the all-reduce over the ranks is part of the final
+	// reduction, with the protocol and the buffers of the decode kernel's fused exchange (qmm_skinny.cuh): the CTA that
+	// holds a column range PUSHES its sums into every peer's receive buffer as {value, sequence} words, polls its own
+	// buffer for the peers' words (bounded: two seconds, status 5) and adds in rank order; the residual is added on every rank.
+	int ar_world, ar_rank, ar_tiles;              // ar_tiles = o_N / 128
+	unsigned long long *ar_buf[8];
+	unsigned *ar_seq;
 };
 
 __device__ __forceinline__ uint32_t qa_map_peer(uint32_t local_smem_addr, uint32_t rank) {
@@ -84,6 +91,9 @@ __device__ __forceinline__ void qa_bulk_load_1d(uint32_t dst, const void *src, u
 				 : "memory");
 }
 
+// AR: with the all-reduce over tensor-parallel ranks in the final reduction (its own instance: the one-GPU kernel keeps
+// its register allocation)
+template <bool AR>
 __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS, 2)
 	qkv_attn_kernel(const __grid_constant__ CUtensorMap tmw, const __grid_constant__ CUtensorMap tmo, const QkvAttnParams p) {
 	extern __shared__ __align__(1024) unsigned char smem[];
@@ -628,14 +638,63 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 			}
 		}
 		*reinterpret_cast<float4 *>(s_red + (size_t)hg * ncol + quad * 4) = v;
+		__shared__ unsigned s_seq[8];
+		const int tile0 = (rank * ncol) >> 7;     // first 128-column tile of this CTA's range; the range holds 2 spw tiles
+		if (AR && tid < 2 * p.o_spw && tile0 + tid < p.ar_tiles) s_seq[tid] = p.ar_seq[tile0 + tid] + 1u;      // left by the previous launch on these buffers
 		__syncthreads();
+		float tsum[4] = {0.f, 0.f, 0.f, 0.f};
+		if (AR) {
+			// own sums first, pushed to every peer before anything is waited for
+#pragma unroll
+			for (int j = 0; j < 4; ++j) {
+				const int c = j * 256 + tid, n = rank * ncol + c;
+				if (j < p.o_spw && n < p.o_N) {
+					float t = 0.f;
+					for (int g = 0; g < hsplit; ++g) t += s_red[(size_t)g * ncol + c];
+					tsum[j] = t;
+					const unsigned seq = s_seq[(n >> 7) - tile0];
+					const size_t slot = (size_t)(seq & 1u) * ((size_t)8 * p.ar_tiles * 2048) + ((size_t)p.ar_rank * p.ar_tiles + (n >> 7)) * 2048 + (n & 127);
+					const unsigned long long w = ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(t);
 #pragma unroll 1
-		for (int j = 0; j < p.o_spw; ++j) {       // a warp takes 32 consecutive columns = one sum-of-squares tile
+					for (int r = 0; r < p.ar_world; ++r)
+						if (r != p.ar_rank) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.ar_buf[r] + slot), "l"(w) : "memory");
+				}
+			}
+		}
+		const unsigned long long t_start = global_timer_ns();
+		bool peers_ok = true;
+#pragma unroll(AR ? 4 : 1)
+		for (int j = 0; j < 4; ++j) {             // a warp takes 32 consecutive columns = one sum-of-squares tile
+			if (j >= p.o_spw) break;
 			const int c = j * 256 + tid, n = rank * ncol + c;
 			float sq = 0.f;
 			if (n < p.o_N) {
 				float t = 0.f;
-				for (int g = 0; g < hsplit; ++g) t += s_red[(size_t)g * ncol + c];
+				if (AR) {
+					const unsigned seq = s_seq[(n >> 7) - tile0];
+					const size_t half = (size_t)(seq & 1u) * ((size_t)8 * p.ar_tiles * 2048);
+#pragma unroll 1
+					for (int r = 0; r < p.ar_world; ++r) {           // rank order: identical sums on every rank
+						if (r == p.ar_rank) {
+							t += tsum[j];
+							continue;
+						}
+						const unsigned long long *src = p.ar_buf[p.ar_rank] + half + ((size_t)r * p.ar_tiles + (n >> 7)) * 2048 + (n & 127);
+						unsigned long long w;
+#pragma unroll 1
+						for (;;) {
+							asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+							if ((unsigned)(w >> 32) == seq) break;
+							if (global_timer_ns() - t_start > 2000000000ull) {      // a peer never arrived
+								peers_ok = false;
+								break;
+							}
+						}
+						t += __uint_as_float((unsigned)w);
+					}
+				} else {
+					for (int g = 0; g < hsplit; ++g) t += s_red[(size_t)g * ncol + c];
+				}
 				if (p.o_res) t += __half2float(p.o_res[n]);
 				const __half hv = __float2half_rn(t);
 				p.o_y[n] = hv;
@@ -647,6 +706,10 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 				for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
 				if (lane == 0 && n < p.o_N) p.o_ss[n >> 5] = sq;
 			}
+		}
+		if (AR) {
+			if (!peers_ok) atomicExch(p.status, 5);
+			if (tid < 2 * p.o_spw && tile0 + tid < p.ar_tiles) p.ar_seq[tile0 + tid] = s_seq[tid];
 		}
 	}
 }

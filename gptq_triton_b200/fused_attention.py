@@ -266,12 +266,14 @@ def qkv_attn_oproj_decode(groupsize: int, a: torch.Tensor, qweight, scales, qzer
 						  vcache: torch.Tensor, n_heads: int, o_groupsize: int, o_qweight, o_scales, o_qzeros, scratch: torch.Tensor,
 						  residual: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None,
 						  rms_weight: Optional[torch.Tensor] = None, rms_eps: float = 1e-6, sumsq_in: Optional[torch.Tensor] = None,
-						  attn_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+						  attn_out: Optional[torch.Tensor] = None, ar=None) -> torch.Tensor:
 	"""qkv_attn_decode + o_proj + residual add in the same kernel: returns residual + attention(a) x deq(Wo) as [1, 1, o_N].
 
 	The whole attention block of a decoder layer for one new token of one sequence (fused_attention.py:79-153 of the
 	reference plus the residual add around it).  `scratch`: uint8 tensor of gptq_qkv_attn_oproj_scratch_bytes, zeroed once,
 	private to this call site; `sumsq_out`: fp32 [o_N // 32] receives the sums of squares of the result per 32 columns.
+	`ar` (tp.PeerExchange sized for o_N): this call is one rank's share (its heads, its row shard of o_proj); the
+	all-reduce over the ranks runs inside the kernel and every rank gets residual + the sum.
 	"""
 	_lib.require_cuda(a, qweight, scales, qzeros, cos, sin, pos, kcache, vcache, o_qweight, o_scales, o_qzeros, scratch, residual)
 	K = a.shape[-1]
@@ -281,6 +283,7 @@ def qkv_attn_oproj_decode(groupsize: int, a: torch.Tensor, qweight, scales, qzer
 	assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape == vcache.shape and kcache.shape[-3] == n_heads and kcache.shape[-1] == 128
 	assert o_qweight.shape[0] * 8 == n_heads * 128
 	assert (rms_weight is None) == (sumsq_in is None)
+	assert ar is None or o_N % 128 == 0
 	if residual is not None:
 		assert residual.numel() == o_N and residual.is_contiguous() and residual.dtype == torch.float16
 	if sumsq_out is not None:
@@ -290,12 +293,16 @@ def qkv_attn_oproj_decode(groupsize: int, a: torch.Tensor, qweight, scales, qzer
 	ws = _lib.workspace(a.device, 1, K, 3 * n_heads * 128)
 	P = _lib.ptr
 	opt = lambda t: P(t) if t is not None else None
-	rc = _lib.lib().gptq_qkv_attn_oproj_decode(
-		P(a), P(qweight), P(qzeros), P(scales), P(cos), P(sin), P(pos), min(cos.shape[0], S), P(kcache), P(vcache), S * 128,
-		K, n_heads, 128, groupsize, 1.0 / math.sqrt(128), opt(rms_weight), opt(sumsq_in), K // 32, float(rms_eps),
-		P(o_qweight), P(o_qzeros), P(o_scales), o_N, o_groupsize, opt(residual), P(y), opt(sumsq_out), opt(attn_out),
-		P(scratch), scratch.numel(), P(ws), ws.numel(), _lib.stream_ptr(a.device))
-	_lib.check(rc, 'gptq_qkv_attn_oproj_decode')
+	args = (P(a), P(qweight), P(qzeros), P(scales), P(cos), P(sin), P(pos), min(cos.shape[0], S), P(kcache), P(vcache), S * 128,
+			K, n_heads, 128, groupsize, 1.0 / math.sqrt(128), opt(rms_weight), opt(sumsq_in), K // 32, float(rms_eps),
+			P(o_qweight), P(o_qzeros), P(o_scales), o_N, o_groupsize, opt(residual), P(y), opt(sumsq_out), opt(attn_out),
+			P(scratch), scratch.numel(), P(ws), ws.numel(), _lib.stream_ptr(a.device))
+	if ar is not None:
+		rc = _lib.lib().gptq_qkv_attn_oproj_decode_ar(*args, ar.world, ar.rank, ar.partials, ar.flags)
+		_lib.check(rc, 'gptq_qkv_attn_oproj_decode_ar')
+	else:
+		rc = _lib.lib().gptq_qkv_attn_oproj_decode(*args)
+		_lib.check(rc, 'gptq_qkv_attn_oproj_decode')
 	return y
 
 

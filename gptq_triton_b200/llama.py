@@ -347,7 +347,7 @@ class DecodeEngine:
 				h_attn = qkv_attn_oproj_decode(attn.qkv_proj.groupsize, src, qw, attn.qkv_proj.scales, attn.qkv_proj.qzeros, cos, sin, pos.view(-1),
 											   self.kcache[i], self.vcache[i], attn.num_heads, op.groupsize, op.qweight, op.scales, op.qzeros,
 											   self._qao_scratch, residual=h.contiguous(), sumsq_out=self.ss_attn, rms_weight=rms_w,
-											   rms_eps=ln1.variance_epsilon, sumsq_in=rms_ss)
+											   rms_eps=ln1.variance_epsilon, sumsq_in=rms_ss, ar=self.ar_o if self.tp_world > 1 else None)
 				o = h_attn
 			else:
 				o = qkv_attn_decode(attn.qkv_proj.groupsize, src, qw, attn.qkv_proj.scales, attn.qkv_proj.qzeros, cos, sin, pos.view(-1), self.kcache[i],
@@ -431,9 +431,13 @@ class DecodeEngine:
 		return qkv_attn_supported(qp.infeatures, attn.num_heads, attn.head_dim, qp.groupsize)
 
 	def _fused_oproj(self, attn) -> bool:
-		"""Whether the one-kernel attention also does o_proj and the residual add (one GPU, plain group layout, no bias,
-		at most 8192 outputs; GPTQ_B200_QKV_ATTN_O=0 turns it off)."""
-		if self.tp_world != 1 or os.environ.get('GPTQ_B200_QKV_ATTN_O', '1') == '0':
+		"""Whether the one-kernel attention also does o_proj and the residual add (plain group layout, no bias, at most
+		8192 outputs; under tensor parallelism with the all-reduce inside the kernel; GPTQ_B200_QKV_ATTN_O=0 turns it off)."""
+		if os.environ.get('GPTQ_B200_QKV_ATTN_O', '1') == '0':
+			return False
+		if self.tp_world != 1 and (self.ar_o is None or attn.o_proj.outfeatures % 128 != 0 or os.environ.get('GPTQ_B200_QKV_ATTN_O_TP', '0') == '0'):
+			# tensor parallel: needs the exchange buffers of the fused all-reduce; opt-in, because on 2 GPUs it is exactly as fast
+			# as the attention kernel followed by o_proj with its own fused all-reduce (632 vs 631 tokens/s)
 			return False
 		op = attn.o_proj
 		_, g_idx, perm = op.kernel_operands()

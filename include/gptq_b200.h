@@ -196,6 +196,23 @@ int gptq_qkv_attn_oproj_decode(const void *x, const int32_t *qweight, const int3
                                float *sumsq_out, void *attn_out, void *scratch, size_t scratch_bytes,
                                void *workspace, size_t workspace_bytes, gptq_stream_t stream);
 
+/*
+ * gptq_qkv_attn_oproj_decode for one rank of a tensor-parallel layer: the kernel works on the rank's heads (qweight =
+ * column shard of the fused QKV weight, o_qweight = row shard of o_proj) and the all-reduce over the ranks runs inside
+ * its final reduction, with the buffers and the protocol of gptq_qmatmul_ar (partials / flags of a buffer set sized for
+ * o_N, gptq_ar_partial_bytes / gptq_ar_flag_bytes).  Every rank ends with the same y = residual + sum over ranks.
+ * No reference counterpart (the reference has no multi-GPU code).
+ */
+int gptq_qkv_attn_oproj_decode_ar(const void *x, const int32_t *qweight, const int32_t *qzeros, const void *scales,
+                                  const void *cos, const void *sin, const int32_t *pos, int max_pos, void *kcache,
+                                  void *vcache, int64_t kv_stride_h, int K, int n_heads, int head_dim, int groupsize,
+                                  float scale, const void *rms_weight, const float *sumsq_in, int sumsq_tiles,
+                                  float rms_eps, const int32_t *o_qweight, const int32_t *o_qzeros,
+                                  const void *o_scales, int o_N, int o_groupsize, const void *residual, void *y,
+                                  float *sumsq_out, void *attn_out, void *scratch, size_t scratch_bytes,
+                                  void *workspace, size_t workspace_bytes, gptq_stream_t stream, int world, int rank,
+                                  void *const *partials, void *const *flags);
+
 /* y = x * rsqrt(mean(x^2) + eps) * weight, per row, fp32 inside.  The RMSNorm that the HF
  * decoder layer applies in front of the attention and MLP blocks (third-party code the
  * reference model is built from, src/gptq_triton/__init__.py:47). */

@@ -37,12 +37,12 @@ def main():
 		G.make_quant_attn(part)
 		G.make_fused_mlp(part)
 		prompt = torch.randint(0, cfg.vocab_size, (2, prompt_len), generator=torch.Generator().manual_seed(seed)).to(dev)
-		def run(model, use_graph):
+		def run(model, use_graph, batch=2):
 			"""Greedy generation; returns tokens [b, steps] and the top-1/top-2 logit margin before every
 			token."""
-			e = G.DecodeEngine(model, batch=2, max_seq=prompt_len + steps + 4, use_graph=use_graph)
+			e = G.DecodeEngine(model, batch=batch, max_seq=prompt_len + steps + 4, use_graph=use_graph)
 			engines.append(e)
-			toks = [e.prefill(prompt)]
+			toks = [e.prefill(prompt[:batch])]
 			top2 = e.logits.float().topk(2, dim=-1).values
 			margins = [float((top2[..., 0] - top2[..., 1]).min())]
 			for _ in range(steps - 1):
@@ -74,6 +74,31 @@ def main():
 					  f' -> {"identical" if first < 0 else ("tie" if tie else "MISMATCH")}', flush=True)
 			if first >= 0 and not tie:
 				ok = False
+		# one sequence: the attention block runs as the cluster kernel on the rank's heads, once followed by o_proj with its
+		# fused all-reduce and once with o_proj and the all-reduce inside the same kernel
+		if seed < 3:
+			t1, margins, logits1 = run(whole, True, batch=1)
+			os.environ['GPTQ_B200_TP_FUSED'] = '1'
+			for inside in ('0', '1'):
+				os.environ['GPTQ_B200_QKV_ATTN_O_TP'] = inside
+				t2, _, logits2 = run(part, True, batch=1)
+				assert engines[-1].used_qkv_attn and engines[-1].used_fused_oproj == (inside == '1')
+				diff = (t1 != t2).any(dim=0).nonzero()
+				first = int(diff[0]) if diff.numel() else -1
+				tie = first >= 0 and margins[first] < 0.05
+				if first < 0:
+					scale = float(logits1.abs().max())
+					err = float((logits1 - logits2).abs().max())
+					if err > 4e-3 * scale:
+						ok = False
+						if rank == 0:
+							print(f'seed {seed} batch 1 o_proj inside={inside}: last-step logits differ by {err:.4g} (scale {scale:.4g})', flush=True)
+				if rank == 0:
+					print(f'seed {seed} batch 1, o_proj + all-reduce inside the attention kernel={inside}: first differing step {first} -> '
+						  f'{"identical" if first < 0 else ("tie" if tie else "MISMATCH")}', flush=True)
+				if first >= 0 and not tie:
+					ok = False
+			os.environ.pop('GPTQ_B200_QKV_ATTN_O_TP', None)
 		del whole, part
 	torch.cuda.synchronize()
 	status = _lib.kernel_status(dev)
