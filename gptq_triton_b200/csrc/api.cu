@@ -571,7 +571,7 @@ static size_t qkv_attn_layout(QkvAttnParams &p) {
 	o = (o + 15) & ~(size_t)15;
 	p.off_attn = (int)o; o += QA_D * 4 + 2 * QA_D * 2 + 8 * QA_D * 4 + 64;
 	p.off_o = (int)o;
-	if (p.o_enable) o += 256 + 2 * 256 * 4 * 2;      // staged attention output, zero / scale strips of up to 1024 o_proj columns
+	if (p.o_enable) o += 8 * 256 + 2 * 256 * 4 * 2;      // staged attention output (one copy per warp), zero / scale strips of up to 1024 o_proj columns
 	return o;
 }
 

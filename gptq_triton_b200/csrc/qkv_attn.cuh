@@ -207,8 +207,8 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 			*reinterpret_cast<uint4 *>(s_sc + (size_t)cl * QA_COLS + u * 8) = sv;
 		}
 	}
-	unsigned char *xs2 = smem + p.off_o;                                  // [256 B] attention output of the head, staged like xs
-	__half *s_ozz = reinterpret_cast<__half *>(xs2 + 256);                // [256 spw] zero point (stored + 1) of this CTA's o_proj columns
+	unsigned char *xs2 = smem + p.off_o;                                  // [8 warps][256 B] attention output of the head, staged like xs
+	__half *s_ozz = reinterpret_cast<__half *>(xs2 + 8 * 256);                // [256 spw] zero point (stored + 1) of this CTA's o_proj columns
 	__half *s_osc = s_ozz + 256 * 4;                                      // [256 spw] scale
 	if (p.o_enable) {
 		const int nz = p.o_N >> 3, g = (head * QA_D) / p.o_groupsize;
@@ -239,6 +239,15 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 	if (rms && tid < units) wq = __ldg(reinterpret_cast<const uint4 *>(p.rms_w + (rank * nc * 16 + tid) * 8));
 
 	pdl_wait();                                   // x (and the sums of squares) come from the kernel before this one
+	// the residual values that the last CTA of a column range adds at the very end: fetched now by every CTA, so that the
+	// reduction does not end with two dependent trips to L2
+	unsigned long long pre_res = 0ull;            // four fp16 values, column j * 256 + tid of the range in bits 16 j .. 16 j + 15
+#pragma unroll
+	for (int j = 0; j < 4; ++j) {
+		const int n = rank * 256 * p.o_spw + j * 256 + tid;
+		if (p.o_enable && p.o_res && j < p.o_spw && n < p.o_N)
+			pre_res |= (unsigned long long)__half_as_ushort(p.o_res[n]) << (16 * j);
+	}
 
 	// ---- stage the K-slice of x (RMSNorm folded in), per-chunk sums of the staged values ----
 	if (rms) {
@@ -548,10 +557,13 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 	if (!p.o_enable) return;
 
 	// ---- phase 3: o_proj.  x = the head's attention output (128 values), this warp's strips of the head's rows of Wo ----
-	__shared__ float2 s_cs2;
 	__shared__ int s_last;
 	__syncthreads();
-	if (warp == 0) {                              // stage like xs: 16 units of 8 k, permuted, odd pairs / 16; (C, S) of the chunk
+	// every warp stages its own copy like xs (16 units of 8 k, permuted, odd pairs / 16) and forms (C, S) of the chunk for
+	// itself: 256 bytes and a few shuffles, and no second CTA barrier
+	unsigned char *xs2w = xs2 + warp * 256;
+	float2 cs2;
+	{
 		float e = 0.f, o = 0.f;
 		if (lane < 16) {
 			const uint4 t = *reinterpret_cast<const uint4 *>(s_ah + lane * 8);
@@ -560,7 +572,7 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 			st.y = h2_mul(__byte_perm(t.x, t.z, 0x7632), 0x2C002C00u);
 			st.z = __byte_perm(t.y, t.w, 0x5410);
 			st.w = h2_mul(__byte_perm(t.y, t.w, 0x7632), 0x2C002C00u);
-			*reinterpret_cast<uint4 *>(xs2 + lane * 16) = st;
+			*reinterpret_cast<uint4 *>(xs2w + lane * 16) = st;
 			const float2 a0 = __half22float2(*reinterpret_cast<const __half2 *>(&st.x)), a1 = __half22float2(*reinterpret_cast<const __half2 *>(&st.y));
 			const float2 a2 = __half22float2(*reinterpret_cast<const __half2 *>(&st.z)), a3 = __half22float2(*reinterpret_cast<const __half2 *>(&st.w));
 			e = (a0.x + a0.y) + (a2.x + a2.y);
@@ -571,20 +583,22 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 			e += __shfl_xor_sync(0xffffffffu, e, d);
 			o += __shfl_xor_sync(0xffffffffu, o, d);
 		}
-		if (lane == 0) s_cs2 = make_float2(1024.f * (e + o), e + 16.f * o);
+		e = __shfl_sync(0xffffffffu, e, 0);
+		o = __shfl_sync(0xffffffffu, o, 0);
+		cs2 = make_float2(1024.f * (e + o), e + 16.f * o);
+		__syncwarp();
 	}
-	__syncthreads();
 #pragma unroll 1
 	for (int j = 0; j < n_oloads; ++j) {
 		float g[4][2];
 #pragma unroll
 		for (int c = 0; c < 4; ++c) g[c][0] = g[c][1] = 0.f;
 		if (!slot_wait()) break;
-		chunk_mma(xs2 + tig * 32, g);
+		chunk_mma(xs2w + tig * 32, g);
 		slot_done();
 		if (tig == 0) {
 			const int lc = (warp * p.o_spw + j) * 32 + gid * 4;          // column inside this CTA's range
-			const float2 csv = s_cs2;
+			const float2 csv = cs2;
 			const uint2 zr = *reinterpret_cast<const uint2 *>(s_ozz + lc);
 			const uint2 sr = *reinterpret_cast<const uint2 *>(s_osc + lc);
 			const float2 z01 = __half22float2(*reinterpret_cast<const __half2 *>(&zr.x)), z23 = __half22float2(*reinterpret_cast<const __half2 *>(&zr.y));
@@ -695,7 +709,7 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 				} else {
 					for (int g = 0; g < hsplit; ++g) t += s_red[(size_t)g * ncol + c];
 				}
-				if (p.o_res) t += __half2float(p.o_res[n]);
+				t += __half2float(__ushort_as_half((unsigned short)(pre_res >> (16 * j))));
 				const __half hv = __float2half_rn(t);
 				p.o_y[n] = hv;
 				const float f = __half2float(hv);
