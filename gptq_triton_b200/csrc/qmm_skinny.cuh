@@ -248,34 +248,34 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 			}
 		}
 	};
+	// one 16-byte unit of x: [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7, the (1,5) and (3,7) pairs divided by 16
+	auto store_item = [&](int r, int unit, uint4 t, const uint4 &w) {
+		if (rms) {
+			// x * inv_rms * w: fp32 product, one fp16 rounding (same expression as rmsnorm_kernel)
+			const float inv = s_inv[r];
+			const uint32_t tv[4] = {t.x, t.y, t.z, t.w}, wv[4] = {w.x, w.y, w.z, w.w};
+			uint32_t ov[4];
+#pragma unroll
+			for (int i = 0; i < 4; ++i) {
+				const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&tv[i]));
+				const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(&wv[i]));
+				const __half2 h = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
+				ov[i] = *reinterpret_cast<const uint32_t *>(&h);
+			}
+			t = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+		}
+		uint4 o;
+		o.x = __byte_perm(t.x, t.z, 0x5410);                          // (x0, x4)
+		o.y = h2_mul(__byte_perm(t.x, t.z, 0x7632), 0x2C002C00u);    // (x1, x5) / 16
+		o.z = __byte_perm(t.y, t.w, 0x5410);                          // (x2, x6)
+		o.w = h2_mul(__byte_perm(t.y, t.w, 0x7632), 0x2C002C00u);    // (x3, x7) / 16
+		*reinterpret_cast<uint4 *>(xs + (size_t)r * p.xs_stride + unit * 16) = o;
+	};
 	auto x_store = [&](int &r, int &ub, const uint4(&v)[XB], const uint4(&wq)[XB]) {
-		// [row < M][unit of 8 k] in k order 0,4,1,5,2,6,3,7, the (1,5) and (3,7) pairs divided by 16
 #pragma unroll
 		for (int j = 0; j < XB; ++j) {
 			const int unit = ub * NT + tid;
-			if (r < p.M && unit < units) {
-				uint4 t = v[j];
-				if (rms) {
-					// x * inv_rms * w: fp32 product, one fp16 rounding (same expression as rmsnorm_kernel)
-					const float inv = s_inv[r];
-					const uint32_t tv[4] = {t.x, t.y, t.z, t.w}, wv[4] = {wq[j].x, wq[j].y, wq[j].z, wq[j].w};
-					uint32_t ov[4];
-#pragma unroll
-					for (int i = 0; i < 4; ++i) {
-						const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&tv[i]));
-						const float2 g = __half22float2(*reinterpret_cast<const __half2 *>(&wv[i]));
-						const __half2 h = __floats2half2_rn(f.x * inv * g.x, f.y * inv * g.y);
-						ov[i] = *reinterpret_cast<const uint32_t *>(&h);
-					}
-					t = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-				}
-				uint4 o;
-				o.x = __byte_perm(t.x, t.z, 0x5410);                          // (x0, x4)
-				o.y = h2_mul(__byte_perm(t.x, t.z, 0x7632), 0x2C002C00u);    // (x1, x5) / 16
-				o.z = __byte_perm(t.y, t.w, 0x5410);                          // (x2, x6)
-				o.w = h2_mul(__byte_perm(t.y, t.w, 0x7632), 0x2C002C00u);    // (x3, x7) / 16
-				*reinterpret_cast<uint4 *>(xs + (size_t)r * p.xs_stride + unit * 16) = o;
-			}
+			if (r < p.M && unit < units) store_item(r, unit, v[j], wq[j]);
 			if (++ub == u_blocks) {
 				ub = 0;
 				++r;
@@ -290,6 +290,43 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 		const int x_passes = (p.M * u_blocks + XB - 1) / XB;
 		const int n_it = max(max(1, x_passes), (n_strip + NT * SB - 1) / (NT * SB));
 		int xr = 0, xub = 0;                                 // first (row, unit block) item of the current x pass
+		if (p.M == 1 && u_blocks == 1 && p.pdl) {
+			// One row, one unit per thread, dependent launch: the shortest chain between the dependency wait and the
+			// first MMA.  Everything that does not depend on the previous kernel (strips, the norm weight) is finished
+			// before the wait; behind it: one load, the norm factor, one store.
+			const bool have = tid < units;
+			const int k = (c_lo * 16 + tid) * 8;
+			uint4 w1 = make_uint4(0u, 0u, 0u, 0u);
+			{
+				uint32_t z0[SB];
+				uint4 sv0[SB];
+				strip_load(tid, z0, sv0);
+				if (rms && have) w1 = __ldg(reinterpret_cast<const uint4 *>(p.rms_w + k));
+#pragma unroll 1
+				for (int s = 0; s < p.nstage; ++s) produce();    // weight prefetch: nstage chunks per warp
+				strip_store(tid, z0, sv0);
+#pragma unroll 1
+				for (int it = 1; it * NT * SB < n_strip; ++it) {
+					strip_load(tid + it * NT * SB, z0, sv0);
+					strip_store(tid + it * NT * SB, z0, sv0);
+				}
+			}
+			pdl_wait();
+			uint4 v1 = make_uint4(0u, 0u, 0u, 0u);
+			if (have) v1 = __ldg(reinterpret_cast<const uint4 *>(p.x + k));
+			if (rms) {
+				if (warp == 0) {
+					float t = 0.f;
+#pragma unroll 4
+					for (int i = lane; i < p.ss_tiles; i += 32) t += __ldcg(p.ss_in + i);
+#pragma unroll
+					for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
+					if (lane == 0) s_inv[0] = rsqrtf(t / (float)p.K + p.rms_eps);
+				}
+				__syncthreads();
+			}
+			if (have) store_item(0, tid, v1, w1);
+		} else
 #pragma unroll 1
 		for (int it = 0; it < n_it; ++it) {
 			uint32_t z0[SB];
