@@ -239,16 +239,6 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 	if (rms && tid < units) wq = __ldg(reinterpret_cast<const uint4 *>(p.rms_w + (rank * nc * 16 + tid) * 8));
 
 	pdl_wait();                                   // x (and the sums of squares) come from the kernel before this one
-	// the residual values that the last CTA of a column range adds at the very end: fetched now by every CTA, so that the
-	// reduction does not end with two dependent trips to L2
-	unsigned long long pre_res = 0ull;            // four fp16 values, column j * 256 + tid of the range in bits 16 j .. 16 j + 15
-#pragma unroll
-	for (int j = 0; j < 4; ++j) {
-		const int n = rank * 256 * p.o_spw + j * 256 + tid;
-		if (p.o_enable && p.o_res && j < p.o_spw && n < p.o_N)
-			pre_res |= (unsigned long long)__half_as_ushort(p.o_res[n]) << (16 * j);
-	}
-
 	// ---- stage the K-slice of x (RMSNorm folded in), per-chunk sums of the staged values ----
 	if (rms) {
 		if (warp == 0) {
@@ -297,6 +287,18 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 		if ((tid & 15) == 0 && tid < units) s_cs[tid >> 4] = make_float2(1024.f * (e + o), e + 16.f * o);
 	}
 	__syncthreads();
+
+	// the residual values that the last CTA of a column range adds at the very end: fetched by every CTA while its
+	// first weight chunks are on their way (not between the dependency wait and the first MMA), so that the reduction does not
+	// end with two dependent trips to L2
+	unsigned short pre_res0 = 0, pre_res1 = 0, pre_res2 = 0, pre_res3 = 0;      // column j * 256 + tid of the range; only looked at in the reduction
+	if (p.o_enable && p.o_res) {
+		const int n = rank * 256 * p.o_spw + tid;
+		if (0 < p.o_spw && n < p.o_N) pre_res0 = __half_as_ushort(p.o_res[n]);
+		if (1 < p.o_spw && n + 256 < p.o_N) pre_res1 = __half_as_ushort(p.o_res[n + 256]);
+		if (2 < p.o_spw && n + 512 < p.o_N) pre_res2 = __half_as_ushort(p.o_res[n + 512]);
+		if (3 < p.o_spw && n + 768 < p.o_N) pre_res3 = __half_as_ushort(p.o_res[n + 768]);
+	}
 
 	// one chunk (128 k x 32 columns in ring slot `cs`) times the staged x of that chunk: g[c][0] = raw sum of column 4 gid + c
 	const int row_a = 2 * tig, row_b = 2 * tig + 1;
@@ -709,7 +711,7 @@ __global__ void __cluster_dims__(QA_CLUSTER, 1, 1) __launch_bounds__(QA_THREADS,
 				} else {
 					for (int g = 0; g < hsplit; ++g) t += s_red[(size_t)g * ncol + c];
 				}
-				t += __half2float(__ushort_as_half((unsigned short)(pre_res >> (16 * j))));
+				t += __half2float(__ushort_as_half(j == 0 ? pre_res0 : (j == 1 ? pre_res1 : (j == 2 ? pre_res2 : pre_res3))));
 				const __half hv = __float2half_rn(t);
 				p.o_y[n] = hv;
 				const float f = __half2float(hv);

@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(KW == 8 ? 256 : KW * 128, KW == 8 ? 2 : 4 / KW
 		for (int it0 = 0; it0 < total; it0 += NWARP * 8) {       // uniform trip count: shuffles below
 			const int item = it0 + warp * 8 + (lane >> 2);
 			const bool valid = item < total;
-			const int gi = valid ? item / p.M : 0, row = valid ? item - gi * p.M : 0;
+			const int gi = !valid ? 0 : (p.M == 1 ? item : item / p.M), row = !valid ? 0 : (p.M == 1 ? 0 : item - gi * p.M);      // no division on the one-row path
 			const int ka = max((g_lo + gi) * p.groupsize, k_lo), kb = min((g_lo + gi + 1) * p.groupsize, k_hi);
 			float e = 0.f, o = 0.f;
 			if (valid) {
