@@ -318,6 +318,55 @@ def prefill_record(G, model, cfg, dev, peak_tflops):
 	return out
 
 
+def measure_exchange(G, tp, dev, rank, world, barrier, dist):
+	"""The all-reduce that is fused into the row-parallel decode kernel, alone: a projection with a one-chunk K-slice
+	(128 rows per rank, 4096 outputs, one row of x) with and without the exchange over peer memory, 64 launches per CUDA
+	graph, CUDA events, max over ranks.  The difference is what one exchange adds to a kernel; a 7B decode step has 64."""
+	import torch
+	from gptq_triton_b200 import synth
+	N, K = 4096, 128
+	t = synth.quant_tensors(K, N, 128, seed=77 + rank)
+	w = tuple(v.to(dev) for v in (t['qweight'], t['scales'], t['qzeros']))
+	x = synth.activations((1, K), seed=5).to(dev)
+	res = torch.zeros((1, N), dtype=torch.float16, device=dev)
+	try:
+		ex = tp.PeerExchange(N, rank, world, group=None)
+	except RuntimeError:
+		return None
+	out = {}
+	for name, ar in (('with_exchange_us', ex), ('without_exchange_us', None)):
+		fn = lambda: G.qmatmul(128, x, *w, residual=res, ar=ar)
+		s = torch.cuda.Stream()
+		with torch.cuda.stream(s):
+			for _ in range(3):
+				fn()
+			s.synchronize()
+			barrier()
+			g = torch.cuda.CUDAGraph()
+			with torch.cuda.graph(g, stream=s):
+				for _ in range(64):
+					fn()
+			barrier()
+			g.replay()
+			s.synchronize()
+			barrier()
+			e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+			e0.record(s)
+			for _ in range(5):
+				g.replay()
+			e1.record(s)
+			s.synchronize()
+		us = torch.tensor([e0.elapsed_time(e1) * 1e3 / (5 * 64)], device=dev)
+		dist.all_reduce(us, op=dist.ReduceOp.MAX)
+		out[name] = float(us.item())
+		del g
+	barrier()
+	ex.close()
+	out['exchange_us'] = out['with_exchange_us'] - out['without_exchange_us']
+	out['what'] = 'o_proj-shaped decode kernel (M = 1, 128 rows per rank -> 4096) inside a CUDA graph, with and without the fused all-reduce'
+	return out
+
+
 def measure_config4(G, tp, dev, rank, world, barrier, dist, steps=16, warmup=4):
 	"""Benchmark configuration 4: LLaMA-65B architecture, 4-bit g128, batch 16, 2048-token prompts, greedy decode,
 	tensor parallel over the ranks of this run.  Device-timed like the main measurement (barrier, CUDA events, max over
@@ -556,6 +605,7 @@ def gpu_arm(args):
 		cpu = cpu_baseline_record(9)
 		cpu['config0'] = cpu_config0()
 
+	exchange = None
 	# ---- benchmark configuration 4 as a sub-record: 65B architecture, batch 16, tensor parallel (N >= 2 by default) ----
 	config4 = None
 	want4 = (args.config4 == 'on') or (args.config4 == 'auto' and world > 1)
@@ -569,6 +619,7 @@ def gpu_arm(args):
 		engine.close()
 		del engine, model
 		torch.cuda.empty_cache()
+		exchange = measure_exchange(G, tp, dev, rank, world, barrier, dist) if (world > 1 and fused_ar) else None
 		config4 = measure_config4(G, tp, dev, rank, world, barrier, dist if world > 1 else None)
 		engine = None
 	else:
@@ -597,7 +648,7 @@ def gpu_arm(args):
 					   'l2': 'inputs larger than L2: 3.6 GB of weights + KV cache are streamed every step'},
 			'e2e': {'value': e2e_tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 8 * batch, 'd2h_bytes_per_step': 8 * batch},
 			'gpu_launches': launches_per_step * args.steps,
-			'roofline': roof, 'prefill': prefill, 'parity': parity, 'config4': config4, 'cpu_baseline': cpu, 'clocks': clocks, 'kernel_status': status,
+			'roofline': roof, 'prefill': prefill, 'parity': parity, 'config4': config4, 'exchange': exchange, 'cpu_baseline': cpu, 'clocks': clocks, 'kernel_status': status,
 		}
 		print(json.dumps(line), flush=True)
 		if config4 is not None and config4.get('kernel_status'):

@@ -377,7 +377,8 @@ def test_empty_batch(G):
 
 
 # ---------------------------------------------------------------- decode attention + RMSNorm kernels
-@pytest.mark.parametrize('b,heads,S,positions', [(1, 4, 300, [0]), (1, 32, 2100, [2047]), (3, 4, 513, [5, 512, 63]), (2, 2, 64, [63, 1])])
+@pytest.mark.parametrize('b,heads,S,positions', [(1, 4, 300, [0]), (1, 32, 2100, [2047]), (3, 4, 513, [5, 512, 63]), (2, 2, 64, [63, 1]),
+												  (16, 8, 2200, [2100 - 37 * i for i in range(16)])])
 def test_attn_decode_matches_fp32_reference(G, b, heads, S, positions):
 	"""softmax(q K^T / sqrt(d)) V over cache positions 0..pos, fp32 softmax as in
 	fused_attention.py:119-137 of the reference, against a float64 evaluation."""
