@@ -11,7 +11,8 @@
 //   exchange every CTA writes its partial sums of q into ALL CTAs of the cluster and of k, v into the last CTA
 //            (st.shared::cluster), cluster barrier, fixed-order sum: every CTA holds q, the last one also k, v.
 //   phase 2  rotary; the last CTA appends the K / V row to the cache; CTA r attends to key split r of the cache
-//            (8 keys x 256 bytes per ring slot, 1-D bulk copies, issued before the dependency wait like the weights),
+//            (8 keys x 256 bytes per ring slot, 1-D bulk copies queued in the same ring behind the weight chunks, so they
+//            are in flight while phase 1 still runs; these rows were written by earlier decode steps or the prefill),
 //            the last one also to the token's own key; online softmax in fp32.
 //   merge    (max, sum, 128 outputs) of every CTA go to CTA 0 through distributed shared memory, cluster barrier,
 //            CTA 0 folds the eight partials in order and writes the head's 128 outputs as fp16.
@@ -21,7 +22,7 @@
 //            head order, adds the residual and writes the new hidden state with its sums of squares.
 // RMSNorm of the input is folded in as in the decode kernels (sums of squares from the producing projection).
 // Deterministic: every sum runs in a fixed order.  Waits on the rings are bounded (status 1); the cluster barriers are
-// hardware barriers between CTAs that are scheduled together, and no CTA leaves before the last one.
+// hardware barriers between CTAs that are scheduled together, and no CTA leaves before the last of them.
 #pragma once
 
 #include <cuda.h>
