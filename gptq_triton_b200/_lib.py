@@ -75,6 +75,7 @@ _OPTIONAL = {
 	'gptq_debug_force_splitk': (None, [c_int]),
 	'gptq_debug_max_stages': (None, [c_int]),
 	'gptq_debug_set_pdl': (None, [c_int]),
+	'gptq_debug_qa_stages': (None, [c_int]),
 	'gptq_debug_soft_max_splits': (None, [c_int]),
 	'gptq_debug_allow_narrow': (None, [c_int]),
 	'gptq_debug_tc_force': (None, [c_int]),

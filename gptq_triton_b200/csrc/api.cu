@@ -19,6 +19,7 @@ thread_local int g_last_cuda_error = 0;
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
 static int g_max_stages = 4;     // tuning hook: upper bound of the ring depth of the decode kernel
 static int g_soft_max_splits = 8;  // the planner avoids more splits than this (gptq_debug_soft_max_splits)
+static int g_qa_stages = 3;       // ring depth of the attention-block kernel (gptq_debug_qa_stages); measured on the 7B step: 4 stages 582, 3 stages 593, 2 stages 592 tokens/s
 static int g_pdl = 1;             // programmatic dependent launch for the decode-step kernels (+3 % on the decode step)
 
 static int sm_count() {
@@ -423,6 +424,7 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
 void gptq_debug_max_stages(int n) { g_max_stages = std::max(2, std::min(n, 8)); }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+void gptq_debug_qa_stages(int n) { g_qa_stages = n; }
 void gptq_debug_soft_max_splits(int n) { g_soft_max_splits = n; }
 void gptq_debug_allow_narrow(int on) { g_allow_narrow = on ? 1 : 0; }
 size_t gptq_workspace_bytes(int M, int K, int N) {
@@ -618,7 +620,7 @@ static int qkv_attn_impl(const void *x, const int32_t *qweight, const int32_t *q
 	QkvAttnParams p = {};
 	p.x = (const __half *)x; p.qz = qzeros; p.sc = (const __half *)scales;
 	p.K = K; p.N = 3 * n_heads * QA_D; p.sec_stride = n_heads * QA_D; p.groupsize = groupsize;
-	p.nc = K / (QA_CLUSTER * 128); p.nstage = 4;
+	p.nc = K / (QA_CLUSTER * 128); p.nstage = std::max(2, std::min(4, g_qa_stages));
 	p.rms_w = (const __half *)rms_weight; p.ss_in = sumsq_in; p.ss_tiles = sumsq_tiles; p.rms_eps = rms_eps;
 	p.cos_t = (const __half *)cos; p.sin_t = (const __half *)sin; p.pos = pos; p.max_pos = max_pos;
 	p.kc = (__half *)kcache; p.vc = (__half *)vcache; p.kv_stride_h = kv_stride_h;
