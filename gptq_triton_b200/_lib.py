@@ -74,6 +74,7 @@ _SIGNATURES = {
 _OPTIONAL = {
 	'gptq_debug_force_splitk': (None, [c_int]),
 	'gptq_debug_max_stages': (None, [c_int]),
+	'gptq_debug_max_stages2': (None, [c_int]),
 	'gptq_debug_set_pdl': (None, [c_int]),
 	'gptq_debug_qa_stages': (None, [c_int]),
 	'gptq_debug_soft_max_splits': (None, [c_int]),

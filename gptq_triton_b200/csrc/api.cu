@@ -17,9 +17,10 @@ namespace gptq {
 thread_local int g_last_cuda_error = 0;
 
 static int g_force_splitk = 0;   // test / tuning hook, 0 = automatic
+static int g_max_stages2 = 3;    // the same for the two-stream (gate/up) form (gptq_debug_max_stages2): 3 stages 598, 4 stages 593, 2 stages 593 tokens/s on the 7B step
 static int g_max_stages = 4;     // tuning hook: upper bound of the ring depth of the decode kernel
 static int g_soft_max_splits = 8;  // the planner avoids more splits than this (gptq_debug_soft_max_splits)
-static int g_qa_stages = 3;       // ring depth of the attention-block kernel (gptq_debug_qa_stages); measured on the 7B step: 4 stages 582, 3 stages 593, 2 stages 592 tokens/s
+static int g_qa_stages = 2;       // ring depth of the attention-block kernel (gptq_debug_qa_stages); 7B step, gate/up at 3 stages: 4 / 3 / 2 stages 589 / 596 / 600 tokens/s at 2.1 k context, 453 / 457 / 457 at 8 k, 660 / 676 / 681 at 300
 static int g_pdl = 1;             // programmatic dependent launch for the decode-step kernels (+3 % on the decode step)
 
 static int sm_count() {
@@ -190,7 +191,7 @@ static void plan_skinny(SkinnyParams &p, int nstream, int &kw, dim3 &grid, size_
 		const int slots = sms * per_sm;
 		for (int sk = 1; sk <= std::min(p.total_chunks, SK_MAX_SPLITK); ++sk) {
 			int cps, eff, a, b, c;
-			int nstage = g_max_stages;
+			int nstage = nstream == 2 ? g_max_stages2 : g_max_stages;
 			while (nstage > 2 && layout(sk, kwarps, nstage, cps, eff, a, b, c) > cap) --nstage;
 			if (layout(sk, kwarps, nstage, cps, eff, a, b, c) > cap) continue;
 			if (eff != sk) continue;
@@ -423,6 +424,7 @@ int gptq_last_cuda_error(void) { return g_last_cuda_error; }
 // Tuning / test hook: force the split-K factor of the decode kernel (0 restores the heuristic).
 void gptq_debug_force_splitk(int splitk) { g_force_splitk = splitk; }
 void gptq_debug_max_stages(int n) { g_max_stages = std::max(2, std::min(n, 8)); }
+void gptq_debug_max_stages2(int n) { g_max_stages2 = std::max(2, std::min(n, 8)); }
 void gptq_debug_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 void gptq_debug_qa_stages(int n) { g_qa_stages = n; }
 void gptq_debug_soft_max_splits(int n) { g_soft_max_splits = n; }
