@@ -81,6 +81,28 @@ def test_extension_entry_points_validate_on_the_host(lib):
 	assert lib.gptq_peer_free(None) == 0 and lib.gptq_peer_close(None) == 0
 
 
+def test_attention_block_entry_points_validate_on_the_host(lib):
+	"""The one-kernel attention block (gptq_qkv_attn_*): shape rule, scratch size and argument checks are host
+	arithmetic; nothing is launched."""
+	assert lib.gptq_qkv_attn_supported(4096, 32, 128, 128) == 1
+	assert lib.gptq_qkv_attn_supported(4096, 4, 128, -1) == 1          # a tensor-parallel shard: few heads, full K
+	assert lib.gptq_qkv_attn_supported(8192, 64, 128, 256) == 1
+	assert lib.gptq_qkv_attn_supported(5120, 40, 128, 128) == 1
+	assert lib.gptq_qkv_attn_supported(4096 + 512, 32, 128, 128) == 0  # K not a multiple of 1024
+	assert lib.gptq_qkv_attn_supported(16384, 32, 128, 128) == 0       # more than 8 chunks of 128 rows per CTA
+	assert lib.gptq_qkv_attn_supported(4096, 32, 64, 128) == 0         # head_dim
+	assert lib.gptq_qkv_attn_supported(4096, 32, 128, 64) == 0         # groups smaller than a chunk
+	assert lib.gptq_qkv_attn_oproj_scratch_bytes(32, 4096) == 256 + 32 * 4096 * 4
+	assert lib.gptq_qkv_attn_oproj_scratch_bytes(0, 4096) == 0
+	buf = (ctypes.c_ubyte * 64)()
+	p = ctypes.cast(buf, ctypes.c_void_p)
+	# null pointers and an unsupported shape are refused before anything touches the device
+	assert lib.gptq_qkv_attn_decode(None, p, p, p, p, p, p, 64, p, p, 64 * 128, p, 4096, 32, 128, 128, 0.088, None, None, 0, 0.0, p, 1 << 20, None) == -1
+	assert lib.gptq_qkv_attn_decode(p, p, p, p, p, p, p, 64, p, p, 64 * 128, p, 4608, 36, 128, 128, 0.088, None, None, 0, 0.0, p, 1 << 20, None) == -6
+	assert lib.gptq_qkv_attn_oproj_decode_ar(p, p, p, p, p, p, p, 64, p, p, 64 * 128, 4096, 32, 128, 128, 0.088, None, None, 0, 0.0, p, p, p, 4096, 128,
+											 None, p, None, None, p, 1 << 20, p, 1 << 20, None, 1, 0, None, None) == -1          # a world of one rank
+
+
 def test_python_ops_refuse_cpu_tensors():
 	import torch
 	import gptq_triton_b200 as g
