@@ -640,8 +640,9 @@ static int qkv_attn_impl(const void *x, const int32_t *qweight, const int32_t *q
 			return GPTQ_ERR_ALIGN;
 		if (o->scratch_bytes < gptq_qkv_attn_oproj_scratch_bytes(n_heads, o->N)) return GPTQ_ERR_WORKSPACE;
 		p.o_enable = 1; p.o_N = o->N; p.o_groupsize = ogs;
-		p.o_spw = (o->N / 32 + 63) / 64;
+		p.o_spw = (o->N / 32 + QA_CLUSTER * 8 - 1) / (QA_CLUSTER * 8);
 		if (p.o_spw == 3) p.o_spw = 4;          // the reduction divides 256 threads by 64 spw column quads
+		if (p.o_spw > 4) return GPTQ_ERR_UNSUPPORTED;
 		p.o_qz = o->qzeros; p.o_sc = (const __half *)o->scales; p.o_res = (const __half *)o->residual;
 		p.o_tickets = reinterpret_cast<int *>(o->scratch);
 		p.o_part = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(o->scratch) + 256);

@@ -32,7 +32,10 @@
 namespace gptq {
 
 constexpr int QA_THREADS = 256;
-constexpr int QA_CLUSTER = 8;
+#ifndef QA_CLUSTER_SIZE
+#define QA_CLUSTER_SIZE 8
+#endif
+constexpr int QA_CLUSTER = QA_CLUSTER_SIZE;          // CTAs per head (8: measured; 4 halves the CTA count and doubles the K-slice)
 constexpr int QA_D = 128;
 constexpr int QA_SLOT = 2048;
 constexpr int QA_COLS = 3 * QA_D;          // q, k, v columns of one head
